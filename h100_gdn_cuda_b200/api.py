@@ -1,0 +1,235 @@
+"""Python mirror of the reference's `gdn_cuda` module (csrc/python_api.cpp:17-393).
+
+Same function names, argument order, keywords and defaults; every function runs on the
+current CUDA stream by calling the C ABI of libgdn_b200.so (include/gdn_b200.h).  Errors
+raise RuntimeError (the reference's docstrings promise that; its code exits the process).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi as cabi
+
+CHUNK = 64
+
+
+class InferenceMode(enum.IntEnum):
+    """gdn_cuda/include/gdn_cuda/types.h:5 (SpecDecode is declared there but unused)."""
+    Prefill = 0
+    Decode = 1
+    SpecVerify = 2
+
+
+Prefill, Decode, SpecVerify = InferenceMode.Prefill, InferenceMode.Decode, InferenceMode.SpecVerify
+
+_state = {"library_root": None, "cuda_home": None}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return cabi.GDN_BF16
+    if t.dtype == torch.float32:
+        return cabi.GDN_F32
+    raise RuntimeError("unsupported dtype %s (bf16 or fp32 expected)" % t.dtype)
+
+
+def _require(cond: bool, msg: str):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _cuda_bf16(t: torch.Tensor, name: str):
+    _require(t.is_cuda, "%s must be a CUDA tensor" % name)
+    _require(t.dtype == torch.bfloat16, "%s must be bf16 (got %s)" % (name, t.dtype))
+
+
+def _token_tensor(t: torch.Tensor, varlen: bool) -> cabi.TokenTensor:
+    """(B,T,H,D) or (N,H,D) view with contiguous last dim -> strides in elements."""
+    _require(t.stride(-1) == 1, "head dimension must be contiguous")
+    if varlen:
+        _require(t.dim() == 3, "packed tensors are rank 3 (tokens, heads, dim)")
+        return cabi.TokenTensor(t.data_ptr(), 0, t.stride(0), t.stride(1))
+    _require(t.dim() == 4, "padded tensors are rank 4 (batch, tokens, heads, dim)")
+    return cabi.TokenTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _token_scalar(t: Optional[torch.Tensor], varlen: bool) -> cabi.TokenScalar:
+    if t is None:
+        return cabi.TokenScalar(None, 0, 0, 0, 0)
+    if varlen:
+        _require(t.dim() == 2, "packed beta/gate are rank 2 (tokens, heads)")
+        return cabi.TokenScalar(t.data_ptr(), _dt(t), 0, t.stride(0), t.stride(1))
+    _require(t.dim() == 3, "padded beta/gate are rank 3 (batch, tokens, heads)")
+    return cabi.TokenScalar(t.data_ptr(), _dt(t), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _state_desc(t: Optional[torch.Tensor]) -> cabi.State:
+    if t is None:
+        return cabi.State(None, 0, 0)
+    _require(t.stride(-1) == 1 and t.stride(-2) == t.shape[-1], "state (dv, dk) block must be contiguous")
+    return cabi.State(t.data_ptr(), t.stride(0), t.stride(1))
+
+
+def _i32(t: Optional[torch.Tensor], name: str):
+    if t is None:
+        return None
+    _require(t.is_cuda and t.dtype == torch.int32 and t.is_contiguous(), "%s must be a contiguous int32 CUDA tensor" % name)
+    return t.data_ptr()
+
+
+def _shape(batch, seq_len, total_tokens, kh, vh, dk, dv, cu_seqlens=None, chunk_indices=None,
+           cu_chunks=None, total_chunks=0) -> cabi.Shape:
+    return cabi.Shape(batch, seq_len, total_tokens, kh, vh, dk, dv, _i32(cu_seqlens, "cu_seqlens"),
+                      _i32(chunk_indices, "chunk_indices"), _i32(cu_chunks, "cu_chunks"), int(total_chunks))
+
+
+def _pad_last(t: torch.Tensor, to: int) -> torch.Tensor:
+    return t if t.shape[-1] == to else torch.nn.functional.pad(t, (0, to - t.shape[-1]))
+
+
+def _pad_state(t: Optional[torch.Tensor], to: int) -> Optional[torch.Tensor]:
+    if t is None or (t.shape[-1] == to and t.shape[-2] == to):
+        return t
+    return torch.nn.functional.pad(t, (0, to - t.shape[-1], 0, to - t.shape[-2]))
+
+
+def _aligned_dim(d: int) -> int:
+    return (d + 63) // 64 * 64
+
+
+# --------------------------------------------------------------------------
+def init(library_root: str, cuda_home: str) -> None:
+    """Record the repository root (holding the kernel headers) and the CUDA toolkit root
+    for the run-time kernel compiler.  Mirrors gdn_cuda.init (python_api.cpp:20)."""
+    _state["library_root"], _state["cuda_home"] = library_root, cuda_home
+    cabi.check(cabi.load().gdn_init(library_root.encode(), cuda_home.encode()), "init")
+
+
+def fused_gdn_gating(A_log, dt_bias, a, b, is_var_len: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(beta, gate) = (sigmoid(b), -exp(A_log) * softplus(a + dt_bias)); python_api.cpp:161-168.
+
+    `A_log` may be the per-head vector (vh,) or, as in the reference, a tensor shaped like
+    `a` whose first vh entries are the per-head values.  Output dtype = input dtype."""
+    _require(a.is_cuda and b.is_cuda and A_log.is_cuda and dt_bias.is_cuda, "inputs must be CUDA tensors")
+    _require(a.dtype == b.dtype == A_log.dtype == dt_bias.dtype, "A_log, dt_bias, a, b must share a dtype")
+    vh = a.shape[-1]
+    _require(dt_bias.numel() >= vh and A_log.numel() >= vh, "A_log and dt_bias need one entry per head")
+    a_c, b_c = a.contiguous(), b.contiguous()
+    A_c, dt_c = A_log.contiguous(), dt_bias.contiguous()
+    beta = torch.empty_like(b_c)
+    gate = torch.empty_like(a_c)
+    n = a_c.numel() // vh
+    cabi.check(cabi.load().gdn_fused_gating(A_c.data_ptr(), dt_c.data_ptr(), a_c.data_ptr(), b_c.data_ptr(),
+                                             beta.data_ptr(), gate.data_ptr(), n, vh, _dt(a_c), _dt(gate),
+                                             _stream()), "fused_gdn_gating")
+    return beta, gate
+
+
+def chunk_local_cumsum_bf16(input, output, batch_size: int, seq_len: int, num_heads: int,
+                            head_first: bool = False, cu_seqlens=None, chunk_indices=None) -> None:
+    """Chunk-local inclusive cumsum, bf16 (or fp32) in, fp32 out; python_api.cpp:328-339.
+
+    As in the reference, `head_first=True` means the token-major layout (B,T,H)/(N,H) and
+    `False` the time-contiguous one (B*H,T)/(H,N)."""
+    _require(input.is_cuda and output.is_cuda, "tensors must be CUDA tensors")
+    _require(output.dtype == torch.float32, "output must be fp32")
+    _require(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
+    tc = 0 if chunk_indices is None else chunk_indices.numel() // 2
+    cabi.check(cabi.load().gdn_chunk_local_cumsum(
+        input.data_ptr(), output.data_ptr(), _dt(input), batch_size, seq_len, num_heads, 1 if head_first else 0,
+        _i32(cu_seqlens, "cu_seqlens"), _i32(chunk_indices, "chunk_indices"), tc, _stream()),
+        "chunk_local_cumsum")
+
+
+def _chunk_local_cumsum_f32(gate: torch.Tensor, batch, seq_len, vh, cu_seqlens, chunk_indices) -> torch.Tensor:
+    out = torch.empty(gate.shape, dtype=torch.float32, device=gate.device)
+    chunk_local_cumsum_bf16(gate.contiguous(), out, batch, seq_len, vh, True, cu_seqlens, chunk_indices)
+    return out
+
+
+def transpose_to_mn_major(input: torch.Tensor, alignment: int = 16) -> torch.Tensor:
+    """(..., mn, k) -> same logical shape with mn padded to `alignment` bytes and
+    stride(-2) == 1; python_api.cpp:362-368 / csrc/apis/layout.hpp:13-57.  Pad rows are zero."""
+    _require(input.is_cuda and input.dim() >= 2, "input must be a CUDA tensor of rank >= 2")
+    _require(input.dtype in (torch.float32, torch.bfloat16), "only fp32 and bf16 are supported")
+    es = input.element_size()
+    _require(alignment % es == 0, "alignment must be a multiple of the element size")
+    x = input.contiguous()
+    mn, k = x.shape[-2], x.shape[-1]
+    per = alignment // es
+    mn_al = (mn + per - 1) // per * per
+    groups = x.numel() // max(mn * k, 1)
+    store = torch.empty(*x.shape[:-2], k, mn_al, dtype=x.dtype, device=x.device)
+    cabi.check(cabi.load().gdn_transpose_mn_major(x.data_ptr(), store.data_ptr(), es, groups, mn, k, mn_al,
+                                                   _stream()), "transpose_to_mn_major")
+    return store.transpose(-1, -2)
+
+
+def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=None, cu_seqlens=None,
+                      num_accepted_tokens=None, inference_mode: int = 0, is_qk_norm: bool = False,
+                      scale: Optional[float] = None, *, inplace_state: bool = False):
+    """Token recurrence for decode / speculative verify / short prefill; python_api.cpp:107-122
+    and csrc/apis/gdn_forward.cpp:134-206.
+
+    Returns (output, new_state).  new_state is (B, vh, dv, dk), or one state per token
+    ((B,T,vh,dv,dk) / (N,vh,dv,dk)) when inference_mode == SpecVerify.  `gate` may be bf16
+    or fp32 (or None for no decay).  With `inplace_state=True` (an extension) the new state
+    overwrites `initial_state`, which is returned."""
+    _require(beta is not None, "beta is required")
+    for t, n in ((query, "query"), (key, "key"), (value, "value")):
+        _cuda_bf16(t, n)
+    varlen = cu_seqlens is not None
+    mode = int(inference_mode)
+    store_steps = mode == int(InferenceMode.SpecVerify)
+    d = query.shape[-1]
+    _require(key.shape[-1] == d, "query and key head dims differ")
+    dv_in = value.shape[-1]
+    d_al, dv_al = _aligned_dim(d), _aligned_dim(dv_in)
+    _require(d_al <= 256 and dv_al <= 256, "head dims above 256 are not supported")
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    q, k, v = _pad_last(query, d_al), _pad_last(key, d_al), _pad_last(value, dv_al)
+    s_in = initial_state
+    if s_in is not None:
+        _cuda_bf16(s_in, "initial_state")
+        if s_in.shape[-1] != d_al or s_in.shape[-2] != dv_al:
+            _require(not inplace_state, "in-place state needs head dims that are multiples of 64")
+            s_in = torch.nn.functional.pad(s_in, (0, d_al - s_in.shape[-1], 0, dv_al - s_in.shape[-2]))
+        s_in = s_in if s_in.stride(-1) == 1 and s_in.stride(-2) == d_al else s_in.contiguous()
+    kh, vh = q.shape[-2], v.shape[-2]
+    if varlen:
+        batch, seq_len, total = cu_seqlens.numel() - 1, 0, q.shape[0]
+    else:
+        batch, seq_len, total = q.shape[0], q.shape[1], q.shape[0] * q.shape[1]
+    out = torch.empty_like(v)
+    if store_steps:
+        lead = (total,) if varlen else (batch, seq_len)
+        s_out = torch.empty(*lead, vh, dv_al, d_al, dtype=torch.bfloat16, device=q.device)
+        so_desc = cabi.State(s_out.data_ptr(), vh * dv_al * d_al, dv_al * d_al)
+    elif inplace_state:
+        _require(s_in is not None, "inplace_state needs an initial_state")
+        s_out = s_in
+        so_desc = _state_desc(s_out)
+    else:
+        s_out = torch.empty(batch, vh, dv_al, d_al, dtype=torch.bfloat16, device=q.device)
+        so_desc = _state_desc(s_out)
+    args = cabi.RecurrentArgs(
+        _shape(batch, seq_len, total, kh, vh, d_al, dv_al, cu_seqlens),
+        _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen), _token_tensor(out, varlen),
+        _token_scalar(beta, varlen), _token_scalar(gate, varlen), _state_desc(s_in), so_desc,
+        _i32(num_accepted_tokens, "num_accepted_tokens"), float(scale), int(bool(is_qk_norm)), int(store_steps))
+    cabi.check(cabi.load().gdn_recurrent_forward(C.byref(args), _stream()), "recurrent_forward")
+    if dv_al != dv_in:
+        out = out[..., :dv_in]
+    if d_al != d or dv_al != dv_in:
+        s_out = s_out[..., :dv_in, :d]
+    return out, s_out

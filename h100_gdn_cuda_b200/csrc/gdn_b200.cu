@@ -1,0 +1,234 @@
+// C-ABI entry points of libgdn_b200.so: runtime, helper kernels and the recurrent
+// (decode / speculative-verify) path.  The chunked-prefill entry points live in
+// gdn_prefill.cu.  See include/gdn_b200.h for the contract of each function.
+#include "host_common.hpp"
+#include "kernels/helpers.cuh"
+#include "kernels/recurrent.cuh"
+
+namespace gdn {
+
+static __device__ int g_status_word;
+
+static std::mutex g_dev_mutex;
+static DeviceInfo g_devices[64];
+static std::string g_library_root, g_cuda_home;
+
+int get_device_info(DeviceInfo** out) {
+    int dev = 0;
+    GDN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(GDN_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_devices[dev];
+    if (!d.valid) {
+        GDN_CUDA(cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev));
+        GDN_CUDA(cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev));
+        GDN_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+        if (d.major != 10)
+            return fail(GDN_ERR_UNSUPPORTED,
+                        "device %d is sm_%d%d; this library only has sm_100a kernels", dev, d.major,
+                        d.minor);
+        void* p = nullptr;
+        GDN_CUDA(cudaGetSymbolAddress(&p, g_status_word));
+        d.status = static_cast<int*>(p);
+        d.valid = true;
+    }
+    *out = &d;
+    return GDN_OK;
+}
+
+const std::string& library_root() { return g_library_root; }
+const std::string& cuda_home() { return g_cuda_home; }
+
+}  // namespace gdn
+
+using namespace gdn;
+
+// ------------------------------------------------------------------ recurrent
+template <int DK>
+static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st) {
+    constexpr int smem = recurrent_smem_bytes<DK>();
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set[dev] = true;
+    }
+    const int per_sm = DK <= 128 ? 4 : 2;  // matches the kernel's launch bounds
+    const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
+    gdn_recurrent_kernel<DK><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+extern "C" {
+
+int gdn_init(const char* library_root, const char* cuda_home) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    g_library_root = library_root ? library_root : "";
+    g_cuda_home = cuda_home ? cuda_home : "";
+    return GDN_OK;
+}
+
+const char* gdn_last_error(void) { return last_error_ref().c_str(); }
+
+int gdn_version(void) { return 100; }
+
+int gdn_device_status(int device, int* status_out) {
+    GDN_REQUIRE(status_out != nullptr, "status_out is NULL");
+    int cur = 0;
+    GDN_CUDA(cudaGetDevice(&cur));
+    if (device != cur) GDN_CUDA(cudaSetDevice(device));
+    DeviceInfo* d = nullptr;
+    int rc = get_device_info(&d);
+    if (rc == GDN_OK) {
+        cudaError_t e = cudaDeviceSynchronize();
+        if (e == cudaSuccess) e = cudaMemcpy(status_out, d->status, sizeof(int), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemset(d->status, 0, sizeof(int));
+        if (e != cudaSuccess) rc = fail(GDN_ERR_CUDA, "reading status word: %s", cudaGetErrorString(e));
+    }
+    if (device != cur) cudaSetDevice(cur);
+    return rc;
+}
+
+// ------------------------------------------------------------------ helpers
+int gdn_fused_gating(const void* A_log, const void* dt_bias, const void* a, const void* b,
+                     void* beta, void* gate, int64_t num_tokens, int32_t num_v_heads,
+                     int32_t dtype, int32_t gate_dtype, gdn_stream_t stream) {
+    GDN_REQUIRE(A_log && dt_bias && a && b && beta && gate, "gdn_fused_gating: NULL pointer");
+    GDN_REQUIRE(num_tokens >= 0 && num_v_heads > 0, "gdn_fused_gating: bad sizes");
+    GDN_REQUIRE(dtype == GDN_BF16 || dtype == GDN_F32, "gdn_fused_gating: dtype must be bf16 or f32");
+    GDN_REQUIRE(gate_dtype == GDN_BF16 || gate_dtype == GDN_F32, "gdn_fused_gating: bad gate dtype");
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    const long long total = static_cast<long long>(num_tokens) * num_v_heads;
+    if (total == 0) return GDN_OK;
+    const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, d->sms * 16ll));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    using bf = __nv_bfloat16;
+    if (dtype == GDN_F32 && gate_dtype == GDN_F32)
+        gdn_gating_kernel<float, float><<<blocks, 256, 0, st>>>((const float*)A_log, (const float*)dt_bias, (const float*)a, (const float*)b, (float*)beta, (float*)gate, total, num_v_heads);
+    else if (dtype == GDN_BF16 && gate_dtype == GDN_BF16)
+        gdn_gating_kernel<bf, bf><<<blocks, 256, 0, st>>>((const bf*)A_log, (const bf*)dt_bias, (const bf*)a, (const bf*)b, (bf*)beta, (bf*)gate, total, num_v_heads);
+    else if (dtype == GDN_BF16 && gate_dtype == GDN_F32)
+        gdn_gating_kernel<bf, float><<<blocks, 256, 0, st>>>((const bf*)A_log, (const bf*)dt_bias, (const bf*)a, (const bf*)b, (bf*)beta, (float*)gate, total, num_v_heads);
+    else
+        return fail(GDN_ERR_UNSUPPORTED, "gdn_fused_gating: f32 inputs with bf16 gate is not built");
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+int gdn_chunk_local_cumsum(const void* input, float* output, int32_t in_dtype, int32_t batch,
+                           int64_t seq_len, int32_t num_heads, int32_t token_major,
+                           const int32_t* cu_seqlens, const int32_t* chunk_indices,
+                           int32_t total_chunks, gdn_stream_t stream) {
+    GDN_REQUIRE(input && output, "gdn_chunk_local_cumsum: NULL pointer");
+    GDN_REQUIRE(in_dtype == GDN_BF16 || in_dtype == GDN_F32, "gdn_chunk_local_cumsum: bad dtype");
+    GDN_REQUIRE(batch > 0 && seq_len >= 0 && num_heads > 0, "gdn_chunk_local_cumsum: bad sizes");
+    int chunks_per_seq = 0, nchunks = 0;
+    if (cu_seqlens) {
+        GDN_REQUIRE(chunk_indices != nullptr, "gdn_chunk_local_cumsum: packed mode needs chunk_indices");
+        GDN_REQUIRE(total_chunks >= 0, "gdn_chunk_local_cumsum: bad total_chunks");
+        nchunks = total_chunks;
+    } else {
+        chunks_per_seq = static_cast<int>((seq_len + 63) / 64);
+        nchunks = chunks_per_seq * batch;
+    }
+    if (nchunks == 0) return GDN_OK;
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long items = static_cast<long long>(nchunks) * num_heads;
+    using bf = __nv_bfloat16;
+    if (token_major) {
+        const unsigned blocks = static_cast<unsigned>((items + 127) / 128);
+        if (in_dtype == GDN_F32)
+            gdn_cumsum_token_major_kernel<float><<<blocks, 128, 0, st>>>((const float*)input, output, nchunks, chunks_per_seq, seq_len, num_heads, cu_seqlens, chunk_indices);
+        else
+            gdn_cumsum_token_major_kernel<bf><<<blocks, 128, 0, st>>>((const bf*)input, output, nchunks, chunks_per_seq, seq_len, num_heads, cu_seqlens, chunk_indices);
+    } else {
+        const unsigned blocks = static_cast<unsigned>((items + 3) / 4);
+        if (in_dtype == GDN_F32)
+            gdn_cumsum_time_major_kernel<float><<<blocks, 128, 0, st>>>((const float*)input, output, nchunks, chunks_per_seq, seq_len, num_heads, batch, cu_seqlens, chunk_indices);
+        else
+            gdn_cumsum_time_major_kernel<bf><<<blocks, 128, 0, st>>>((const bf*)input, output, nchunks, chunks_per_seq, seq_len, num_heads, batch, cu_seqlens, chunk_indices);
+    }
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+int gdn_transpose_mn_major(const void* input, void* output, int32_t elem_size, int64_t groups,
+                           int64_t mn, int64_t k, int64_t mn_aligned, gdn_stream_t stream) {
+    GDN_REQUIRE(input && output, "gdn_transpose_mn_major: NULL pointer");
+    GDN_REQUIRE(elem_size == 2 || elem_size == 4, "gdn_transpose_mn_major: element size must be 2 or 4");
+    GDN_REQUIRE(groups >= 0 && mn >= 0 && k >= 0 && mn_aligned >= mn, "gdn_transpose_mn_major: bad sizes");
+    GDN_REQUIRE(groups <= 65535 && (k + 31) / 32 <= 65535, "gdn_transpose_mn_major: too many groups or columns");
+    if (groups == 0 || k == 0 || mn_aligned == 0) return GDN_OK;
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    dim3 grid(static_cast<unsigned>((mn_aligned + 31) / 32), static_cast<unsigned>((k + 31) / 32),
+              static_cast<unsigned>(groups));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (elem_size == 4)
+        gdn_transpose_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)input, (uint32_t*)output, mn, k, mn_aligned);
+    else
+        gdn_transpose_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t*)input, (uint16_t*)output, mn, k, mn_aligned);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
+    GDN_REQUIRE(a != nullptr, "gdn_recurrent_forward: args is NULL");
+    if (int rc = check_shape(a->shape, false)) return rc;
+    const GdnShape& s = a->shape;
+    GDN_REQUIRE(s.head_dim_k % 64 == 0 && s.head_dim_k <= 256,
+                "gdn_recurrent_forward: dk must be 64, 128, 192 or 256 (got %d)", s.head_dim_k);
+    GDN_REQUIRE(s.head_dim_v % 32 == 0, "gdn_recurrent_forward: dv must be a multiple of 32 (got %d)", s.head_dim_v);
+    if (int rc = check_token_tensor(a->q, "q", s.head_dim_k)) return rc;
+    if (int rc = check_token_tensor(a->k, "k", s.head_dim_k)) return rc;
+    if (int rc = check_token_tensor(a->v, "v", s.head_dim_v)) return rc;
+    if (int rc = check_token_tensor(a->out, "out", s.head_dim_v)) return rc;
+    GDN_REQUIRE(a->beta.ptr != nullptr, "gdn_recurrent_forward: beta is NULL");
+    GDN_REQUIRE(a->beta.dtype == GDN_BF16 || a->beta.dtype == GDN_F32, "beta dtype must be bf16 or f32");
+    GDN_REQUIRE(!a->gate.ptr || a->gate.dtype == GDN_BF16 || a->gate.dtype == GDN_F32, "gate dtype must be bf16 or f32");
+    GDN_REQUIRE(a->state_out.ptr != nullptr, "gdn_recurrent_forward: state_out is NULL");
+    GDN_REQUIRE(aligned16(a->state_out.ptr) && a->state_out.stride_seq % 8 == 0 && a->state_out.stride_head % 8 == 0,
+                "state_out must be 16-byte aligned with strides that are multiples of 8");
+    if (a->state_in.ptr) {
+        GDN_REQUIRE(aligned16(a->state_in.ptr) && a->state_in.stride_seq % 8 == 0 && a->state_in.stride_head % 8 == 0,
+                    "state_in must be 16-byte aligned with strides that are multiples of 8");
+        GDN_REQUIRE(!(a->store_step_state && a->state_in.ptr == a->state_out.ptr),
+                    "state_out may not alias state_in when step states are stored");
+    }
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+
+    RecurrentParams p{};
+    p.q = (const __nv_bfloat16*)a->q.ptr; p.q_sb = a->q.stride_batch; p.q_st = a->q.stride_token; p.q_sh = a->q.stride_head;
+    p.k = (const __nv_bfloat16*)a->k.ptr; p.k_sb = a->k.stride_batch; p.k_st = a->k.stride_token; p.k_sh = a->k.stride_head;
+    p.v = (const __nv_bfloat16*)a->v.ptr; p.v_sb = a->v.stride_batch; p.v_st = a->v.stride_token; p.v_sh = a->v.stride_head;
+    p.out = (__nv_bfloat16*)a->out.ptr; p.o_sb = a->out.stride_batch; p.o_st = a->out.stride_token; p.o_sh = a->out.stride_head;
+    p.beta = a->beta.ptr; p.beta_f32 = a->beta.dtype == GDN_F32;
+    p.beta_sb = a->beta.stride_batch; p.beta_st = a->beta.stride_token; p.beta_sh = a->beta.stride_head;
+    p.gate = a->gate.ptr; p.gate_f32 = a->gate.dtype == GDN_F32;
+    p.gate_sb = a->gate.stride_batch; p.gate_st = a->gate.stride_token; p.gate_sh = a->gate.stride_head;
+    p.state_in = (const __nv_bfloat16*)a->state_in.ptr; p.si_ss = a->state_in.stride_seq; p.si_sh = a->state_in.stride_head;
+    p.state_out = (__nv_bfloat16*)a->state_out.ptr; p.so_ss = a->state_out.stride_seq; p.so_sh = a->state_out.stride_head;
+    p.cu_seqlens = s.cu_seqlens;
+    p.num_accepted = a->num_accepted_tokens;
+    p.batch = s.batch; p.seq_len = s.seq_len; p.kh = s.num_k_heads; p.vh = s.num_v_heads; p.dv = s.head_dim_v;
+    p.scale = a->scale;
+    p.is_qk_norm = a->is_qk_norm; p.store_step = a->store_step_state;
+    p.num_tiles = static_cast<long long>(s.batch) * s.num_v_heads * (s.head_dim_v / kRecTileRows);
+    p.status = d->status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (s.head_dim_k) {
+        case 64: return launch_recurrent<64>(p, d->sms, st);
+        case 128: return launch_recurrent<128>(p, d->sms, st);
+        case 192: return launch_recurrent<192>(p, d->sms, st);
+        case 256: return launch_recurrent<256>(p, d->sms, st);
+    }
+    return fail(GDN_ERR_UNSUPPORTED, "unsupported dk %d", s.head_dim_k);
+}
+
+}  // extern "C"

@@ -1,0 +1,218 @@
+/* gdn_b200.h - C ABI of libgdn_b200.so, a Gated DeltaNet kernel library for NVIDIA B200
+ * (sm_100a).
+ *
+ * Every entry point replaces one function of the `gdn_cuda` C++ API of
+ * kingsleykimm/h100_gdn_cuda (csrc/apis/gdn_forward.hpp:15-73); the citation beside each
+ * declaration names the reference function it stands in for.  The functions take plain
+ * device pointers, sizes and element strides, enqueue their work on the given stream,
+ * never synchronise, never allocate unless stated, never exit the process and never throw:
+ * they return GDN_OK or a negative error code, and gdn_last_error() returns a message for
+ * the calling thread's last failure.
+ *
+ * Conventions
+ *   - "token tensors" (q, k, v, u, w, o) are bf16 with the head dimension contiguous; they are
+ *     addressed as  base + batch*stride_batch + token*stride_token + head*stride_head  (in
+ *     elements).  In packed variable-length mode (`cu_seqlens != NULL`) there is no batch
+ *     axis and `token` is the global token index.
+ *   - "per-token scalars" (beta, gate) are addressed the same way with a head stride, so
+ *     both the token-major (B,T,H) layout and the time-contiguous "MN-major" (B,H,T_pad)
+ *     layout of the reference are expressed by strides.
+ *   - states are bf16, laid out (sequence, v_head, dv, dk) with dk contiguous and dv rows
+ *     packed (the reference's layout, csrc/apis/gdn_forward.cpp:102-112).
+ *   - the chunk size is 64 tokens.
+ *   - q and k have `num_k_heads` heads, v/u/w/o/beta/gate/state have `num_v_heads`;
+ *     v-head h uses k-head h / (num_v_heads / num_k_heads).
+ */
+#ifndef GDN_B200_H
+#define GDN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* gdn_stream_t; /* a cudaStream_t */
+
+enum {
+    GDN_OK = 0,
+    GDN_ERR_INVALID = -1,     /* bad shape, stride, alignment, dtype or NULL pointer          */
+    GDN_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for (or non-sm_100 GPU) */
+    GDN_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed                          */
+    GDN_ERR_WORKSPACE = -4,   /* workspace missing, misaligned or too small                   */
+    GDN_ERR_DEVICE = -5       /* a kernel reported a bounded wait that ran out                */
+};
+
+enum { GDN_BF16 = 0, GDN_F32 = 1 };
+enum { GDN_MODE_PREFILL = 0, GDN_MODE_DECODE = 1, GDN_MODE_SPEC_VERIFY = 2 };
+
+/* bf16 tensor with a contiguous last (head-dim) axis. */
+typedef struct {
+    void* ptr;
+    int64_t stride_batch;
+    int64_t stride_token;
+    int64_t stride_head;
+} GdnTokenTensor;
+
+/* one scalar per (token, v-head); dtype GDN_BF16 or GDN_F32; ptr == NULL means absent. */
+typedef struct {
+    void* ptr;
+    int32_t dtype;
+    int64_t stride_batch;
+    int64_t stride_token;
+    int64_t stride_head;
+} GdnTokenScalar;
+
+/* (sequence, v_head, dv, dk) bf16 state; the inner (dv, dk) block is contiguous. */
+typedef struct {
+    void* ptr;
+    int64_t stride_seq;
+    int64_t stride_head;
+} GdnState;
+
+/* Shape of a call.  Padded mode: `batch` sequences of `seq_len` tokens.  Packed mode
+ * (`cu_seqlens` given): `batch` sequences, `total_tokens` tokens, `seq_len` ignored. */
+typedef struct {
+    int32_t batch;
+    int32_t seq_len;
+    int64_t total_tokens;
+    int32_t num_k_heads;
+    int32_t num_v_heads;
+    int32_t head_dim_k; /* dk */
+    int32_t head_dim_v; /* dv */
+    const int32_t* cu_seqlens;    /* device, batch+1 entries, or NULL                    */
+    const int32_t* chunk_indices; /* device, 2*total_chunks entries [seq, chunk], or NULL */
+    const int32_t* cu_chunks;     /* device, batch+1 entries, or NULL                    */
+    int32_t total_chunks;         /* packed mode: number of 64-token chunks              */
+} GdnShape;
+
+/* ---------------------------------------------------------------- runtime
+ * Replaces gdn_cuda::init (csrc/apis/gdn_forward.cpp:14-16 -> Compiler::init_static_vars,
+ * csrc/jit/compiler.hpp:34-40): records where the kernel headers and the CUDA toolkit are
+ * for the run-time kernel compiler.  Either argument may be NULL (built-in kernels only). */
+int gdn_init(const char* library_root, const char* cuda_home);
+
+/* Message for the calling thread's most recent failure ("" if none). */
+const char* gdn_last_error(void);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int gdn_version(void);
+
+/* Reads and clears the device-side status word of `device` (synchronises that device's
+ * work first).  0 = no kernel reported a problem.  Debug / test aid; has no counterpart in
+ * the reference, whose device asserts trap (kernels/common/common.hpp:485-493). */
+int gdn_device_status(int device, int* status_out);
+
+/* ---------------------------------------------------------------- helpers
+ * Replaces kernels::gdn_gating (src/gdn_ops.cu:13-33; kernel gdn_helpers.cuh:41-122):
+ *   beta = sigmoid(b),  gate = -exp(A_log[h]) * softplus(a + dt_bias[h])   (softplus(x) = x for x > 20)
+ * a, b, beta, gate are contiguous (num_tokens, num_v_heads); A_log, dt_bias have num_v_heads
+ * entries.  `dtype` is the type of all four inputs and of beta; `gate_dtype` that of gate. */
+int gdn_fused_gating(const void* A_log, const void* dt_bias, const void* a, const void* b,
+                     void* beta, void* gate, int64_t num_tokens, int32_t num_v_heads,
+                     int32_t dtype, int32_t gate_dtype, gdn_stream_t stream);
+
+/* Replaces kernels::chunk_local_cumsum (src/gdn_ops.cu:38-57; kernels gdn_helpers.cuh:142-256):
+ * inclusive prefix sum of `input` restarted at every 64-token chunk of every sequence;
+ * fp32 output in the same layout.  `token_major` != 0: (batch, seq_len, heads) / (tokens, heads)
+ * (the reference's head_first=true); 0: time-contiguous (batch*heads, seq_len) / (heads, tokens).
+ * Packed mode needs cu_seqlens and chunk_indices (total_chunks pairs). */
+int gdn_chunk_local_cumsum(const void* input, float* output, int32_t in_dtype, int32_t batch,
+                           int64_t seq_len, int32_t num_heads, int32_t token_major,
+                           const int32_t* cu_seqlens, const int32_t* chunk_indices,
+                           int32_t total_chunks, gdn_stream_t stream);
+
+/* Replaces api::transpose_to_mn_major (csrc/apis/layout.hpp:13-57; kernels sm90_layout.cuh:10-87):
+ * `groups` row-major (mn, k) matrices -> (k, mn_aligned) each, pad columns written as zero.
+ * elem_size is 2 or 4 bytes. */
+int gdn_transpose_mn_major(const void* input, void* output, int32_t elem_size, int64_t groups,
+                           int64_t mn, int64_t k, int64_t mn_aligned, gdn_stream_t stream);
+
+/* ---------------------------------------------------------------- recurrent decode / spec-verify
+ * Replaces gdn_cuda::bf16_gdn_recurrent / recurrent_forward (csrc/apis/gdn_forward.cpp:134-206,
+ * 240-250; kernel sm90_bf16_gdn_recurrent.cuh:20-440).  Per token t of sequence s, v-head h:
+ *     S <- exp(g) S ;  S <- S + beta (v - S k) k^T ;  o = scale * S q
+ * with optional L2 normalisation of q and k (x * rsqrt(sum x^2 + 1e-6)).
+ *   state_in.ptr == NULL  : start from zero.
+ *   num_accepted_tokens   : optional device int32[batch]; caps the tokens processed per sequence
+ *                           (outputs past the cap are left untouched).
+ *   store_step_state != 0 : state_out holds one state per token, addressed
+ *                           token_index*stride_seq + head*stride_head (token_index =
+ *                           b*seq_len + t, or the packed token index); otherwise one per
+ *                           sequence.  state_out may alias state_in when not storing steps. */
+typedef struct {
+    GdnShape shape;
+    GdnTokenTensor q, k, v, out;
+    GdnTokenScalar beta, gate; /* gate.ptr may be NULL (no decay) */
+    GdnState state_in, state_out;
+    const int32_t* num_accepted_tokens;
+    float scale;
+    int32_t is_qk_norm;
+    int32_t store_step_state;
+} GdnRecurrentArgs;
+int gdn_recurrent_forward(const GdnRecurrentArgs* args, gdn_stream_t stream);
+
+/* ---------------------------------------------------------------- chunked prefill, stage by stage
+ * Replaces api::bf16_gdn_compute_u_w (csrc/apis/gdn.hpp:14-24; kernel
+ * sm90_bf16_gdn_compute_u_w.cuh:153-667).  Per 64-token chunk and v-head, with g the
+ * chunk-local cumulative gate (fp32; absent = no decay):
+ *     A = tril(diag(beta) K K^T .* exp(g_i - g_j), -1),  T = (I + A)^-1 diag(beta)
+ *     U = T V,   W = T (K .* exp(g))
+ * (W is the canonical form; the reference scales rows after the solve instead.) */
+typedef struct {
+    GdnShape shape;
+    GdnTokenTensor k, v, u, w;
+    GdnTokenScalar beta, gate_cumsum;
+} GdnComputeUWArgs;
+int gdn_compute_u_w(const GdnComputeUWArgs* args, gdn_stream_t stream);
+
+/* Replaces api::bf16_chunked_seq_state_update (csrc/apis/gdn.hpp:26-39; kernel
+ * sm90_bf16_chunked_seq_state_update2.cuh).  Sequential over the chunks of a sequence:
+ *     h[c] = S ;  U_new = U - W S^T ;  S <- exp(g_last) S + U_new^T (K .* exp(g_last - g))
+ * `u` is overwritten with U_new.  chunk_states is (batch, num_chunks, vh, dv, dk) in padded
+ * mode and (total_chunks, vh, dv, dk) in packed mode, contiguous.  initial_state.ptr and
+ * final_state.ptr may be NULL. */
+typedef struct {
+    GdnShape shape;
+    GdnTokenTensor k, u, w;
+    GdnTokenScalar gate_cumsum;
+    GdnState initial_state, final_state;
+    void* chunk_states;
+} GdnSeqStateArgs;
+int gdn_seq_state_update(const GdnSeqStateArgs* args, gdn_stream_t stream);
+
+/* Replaces api::bf16_gdn_chunked_compute_O (csrc/apis/gdn.hpp:41-55; kernel
+ * sm90_bf16_gdn_chunked_compute_O.cuh:23-530):
+ *     O = scale * ( exp(g) .* (Q h[c]^T) + tril(Q K^T .* exp(g_i - g_j)) U_new ) */
+typedef struct {
+    GdnShape shape;
+    GdnTokenTensor q, k, u_new, out;
+    GdnTokenScalar gate_cumsum;
+    const void* chunk_states;
+    float scale;
+} GdnComputeOArgs;
+int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
+
+/* ---------------------------------------------------------------- chunked prefill, whole layer
+ * Replaces gdn_cuda::chunked_forward (csrc/apis/gdn_forward.cpp:18-132): raw (pre-cumsum)
+ * fp32 or bf16 gate, token-major beta; writes `out` (like v) and final_state.  The per-chunk
+ * state tensor of the reference is never materialised.  `workspace` is caller-provided device
+ * memory of at least gdn_chunked_forward_workspace_bytes(&shape) bytes, 256-byte aligned; its
+ * contents need not be initialised and are garbage afterwards. */
+typedef struct {
+    GdnShape shape;
+    GdnTokenTensor q, k, v, out;
+    GdnTokenScalar beta, gate;
+    GdnState initial_state, final_state; /* either ptr may be NULL */
+    float scale;
+    void* workspace;
+    size_t workspace_bytes;
+} GdnChunkedArgs;
+size_t gdn_chunked_forward_workspace_bytes(const GdnShape* shape);
+int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GDN_B200_H */

@@ -1,0 +1,68 @@
+"""CPU checks of the C-ABI library: it loads without a GPU and exports every declared symbol."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from h100_gdn_cuda_b200 import build, _cabi
+    build.build()
+    return _cabi.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "gdn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gdn_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(lib):
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), "symbol %s declared in include/gdn_b200.h is not exported" % n
+
+
+def test_binding_table_covers_header():
+    from h100_gdn_cuda_b200 import _cabi
+    assert set(_declared_symbols()) == set(_cabi.SYMBOLS)
+
+
+def test_version_and_error_text(lib):
+    assert lib.gdn_version() >= 100
+    assert lib.gdn_init(b"/tmp", b"/usr/local/cuda") == 0
+    # argument validation happens before any CUDA call, so it is testable without a GPU
+    rc = lib.gdn_recurrent_forward(None, None)
+    assert rc == -1 and b"NULL" in lib.gdn_last_error()
+    rc = lib.gdn_transpose_mn_major(None, None, 2, 1, 1, 1, 1, None)
+    assert rc == -1
+
+
+def test_struct_sizes_match_c(lib):
+    # sizes computed by the C compiler for the structs in the header
+    import subprocess, tempfile, textwrap
+    from h100_gdn_cuda_b200 import _cabi
+    src = textwrap.dedent('''
+        #include <stdio.h>
+        #include "gdn_b200.h"
+        int main(void) {
+            printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(GdnTokenTensor), sizeof(GdnTokenScalar),
+                   sizeof(GdnState), sizeof(GdnShape), sizeof(GdnRecurrentArgs), sizeof(GdnComputeUWArgs),
+                   sizeof(GdnSeqStateArgs), sizeof(GdnComputeOArgs), sizeof(GdnChunkedArgs));
+            return 0;
+        }''')
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "s.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "s")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        sizes = [int(x) for x in subprocess.check_output([exe]).split()]
+    py = [ctypes.sizeof(t) for t in (_cabi.TokenTensor, _cabi.TokenScalar, _cabi.State, _cabi.Shape,
+                                     _cabi.RecurrentArgs, _cabi.ComputeUWArgs, _cabi.SeqStateArgs,
+                                     _cabi.ComputeOArgs, _cabi.ChunkedArgs)]
+    assert sizes == py
