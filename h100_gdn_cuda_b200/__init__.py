@@ -13,7 +13,11 @@ from .api import (  # noqa: F401
     InferenceMode,
     Prefill,
     SpecVerify,
+    bf16_chunked_seq_state_update,
+    bf16_gdn_chunked_compute_O,
+    bf16_gdn_compute_u_w,
     chunk_local_cumsum_bf16,
+    chunked_forward,
     fused_gdn_gating,
     init,
     recurrent_forward,

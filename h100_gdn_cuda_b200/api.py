@@ -233,3 +233,145 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
     if d_al != d or dv_al != dv_in:
         s_out = s_out[..., :dv_in, :d]
     return out, s_out
+
+
+# --------------------------------------------------------------------------
+# chunked prefill
+# --------------------------------------------------------------------------
+_PREFILL_D = 128  # head dimension the tensor-core kernels are built for
+
+
+def _prefill_dims(query, value, cu_seqlens):
+    varlen = cu_seqlens is not None
+    if varlen:
+        batch, seq_len, total = cu_seqlens.numel() - 1, 0, query.shape[0]
+    else:
+        batch, seq_len, total = query.shape[0], query.shape[1], query.shape[0] * query.shape[1]
+    return varlen, batch, seq_len, total
+
+
+def _check_head_dim(d: int):
+    _require(0 < d <= _PREFILL_D, "chunked kernels support head dims up to %d (got %d)" % (_PREFILL_D, d))
+
+
+def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None, initial_state=None,
+                    cu_seqlens=None, chunk_indices=None, cu_chunks=None, total_chunks: Optional[int] = None):
+    """Chunked (64-token) Gated DeltaNet prefill; python_api.cpp:47-60, csrc/apis/gdn_forward.cpp:18-132.
+
+    query/key (B,T,kh,d) or (N,kh,d); value (B,T,vh,d) or (N,vh,d); beta bf16 and gate fp32
+    (raw per-token log-decay, before any cumsum) shaped (B,T,vh) / (N,vh); initial_state
+    (B|S, vh, d, d) bf16 or None.  Packed mode needs int32 cu_seqlens, chunk_indices and
+    cu_chunks.  Returns (output shaped like value, final_state (B|S, vh, d, d)), both bf16.
+    The default scale is d ** -0.5 with d the caller's (unpadded) head dimension."""
+    for t, n in ((query, "query"), (key, "key"), (value, "value")):
+        _cuda_bf16(t, n)
+    _require(gate is None or gate.dtype in (torch.float32, torch.bfloat16), "gate must be fp32 (or bf16)")
+    varlen, batch, seq_len, total = _prefill_dims(query, value, cu_seqlens)
+    d = query.shape[-1]
+    _require(key.shape[-1] == d and value.shape[-1] == d, "chunked kernels need dk == dv")
+    _check_head_dim(d)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    D = _PREFILL_D
+    q, k, v = _pad_last(query, D), _pad_last(key, D), _pad_last(value, D)
+    s_in = _pad_state(initial_state, D)
+    if s_in is not None:
+        _cuda_bf16(s_in, "initial_state")
+        s_in = s_in if s_in.stride(-1) == 1 and s_in.stride(-2) == D else s_in.contiguous()
+    kh, vh = q.shape[-2], v.shape[-2]
+    if varlen:
+        _require(chunk_indices is not None and cu_chunks is not None,
+                 "packed mode needs cu_seqlens, chunk_indices and cu_chunks")
+        tc = chunk_indices.numel() // 2 if total_chunks is None else int(total_chunks)
+    else:
+        tc = 0
+    out = torch.empty_like(v)
+    final = torch.empty(batch, vh, D, D, dtype=torch.bfloat16, device=q.device)
+    shape = _shape(batch, seq_len, total, kh, vh, D, D, cu_seqlens, chunk_indices, cu_chunks, tc)
+    lib = cabi.load()
+    ws_bytes = lib.gdn_chunked_forward_workspace_bytes(C.byref(shape))
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    args = cabi.ChunkedArgs(shape, _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen),
+                            _token_tensor(out, varlen), _token_scalar(beta, varlen), _token_scalar(gate, varlen),
+                            _state_desc(s_in), _state_desc(final), float(scale), ws.data_ptr(), ws_bytes)
+    cabi.check(lib.gdn_chunked_forward(C.byref(args), _stream()), "chunked_forward")
+    if d != D:
+        out, final = out[..., :d], final[..., :d, :d]
+    return out, final
+
+
+def bf16_gdn_compute_u_w(k, v, u, w, beta, gate=None, compiled_dims: str = "t", cu_seqlens=None,
+                         chunk_indices=None) -> None:
+    """Low-level WY/UT transform; python_api.cpp:199-210.  Writes u and w in place.
+
+    beta and gate (chunk-local cumsum, fp32) may be MN-major views (stride(-2) == 1, as
+    transpose_to_mn_major returns) or plain token-major tensors; `compiled_dims` is accepted
+    and ignored (no dimension is baked into the kernels)."""
+    for t, n in ((k, "k"), (v, "v"), (u, "u"), (w, "w")):
+        _cuda_bf16(t, n)
+    varlen, batch, seq_len, total = _prefill_dims(k, v, cu_seqlens)
+    d = k.shape[-1]
+    _require(d == _PREFILL_D and v.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    beta, gate = _crop_tokens(beta, total if varlen else seq_len), _crop_tokens(gate, total if varlen else seq_len)
+    tc = 0 if chunk_indices is None else chunk_indices.numel() // 2
+    shape = _shape(batch, seq_len, total, k.shape[-2], v.shape[-2], d, d, cu_seqlens, chunk_indices, None, tc)
+    args = cabi.ComputeUWArgs(shape, _token_tensor(k, varlen), _token_tensor(v, varlen), _token_tensor(u, varlen),
+                              _token_tensor(w, varlen), _token_scalar(beta, varlen), _token_scalar(gate, varlen))
+    cabi.check(cabi.load().gdn_compute_u_w(C.byref(args), _stream()), "bf16_gdn_compute_u_w")
+
+
+def _crop_tokens(t: Optional[torch.Tensor], tokens: int) -> Optional[torch.Tensor]:
+    """MN-major tensors carry a padded token axis; cut the view back to the real length."""
+    if t is None:
+        return None
+    return t[..., :tokens, :] if t.shape[-2] != tokens else t
+
+
+def bf16_chunked_seq_state_update(k, u, w, initial_state, state, final_state, gate=None,
+                                  compiled_dims: str = "t", cu_seqlens=None, cu_chunks=None,
+                                  total_chunks: Optional[int] = None, chunk_size: int = 64) -> None:
+    """Low-level chunk-to-chunk state pass; python_api.cpp:243-258.  Writes `state` (the state
+    entering every chunk, (B,nc,vh,d,d) / (total_chunks,vh,d,d)), `final_state`, and
+    overwrites `u` with U_new."""
+    _require(chunk_size == CHUNK, "only chunk_size 64 is supported")
+    for t, n in ((k, "k"), (u, "u"), (w, "w"), (state, "state")):
+        _cuda_bf16(t, n)
+    varlen, batch, seq_len, total = _prefill_dims(k, u, cu_seqlens)
+    d = k.shape[-1]
+    _require(d == _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    _require(state.is_contiguous(), "state must be contiguous")
+    gate = _crop_tokens(gate, total if varlen else seq_len)
+    if varlen:
+        _require(cu_chunks is not None, "packed mode needs cu_chunks")
+        tc = state.shape[0] if total_chunks is None else int(total_chunks)
+    else:
+        tc = 0
+    shape = _shape(batch, seq_len, total, k.shape[-2], u.shape[-2], d, d, cu_seqlens, None, cu_chunks, tc)
+    args = cabi.SeqStateArgs(shape, _token_tensor(k, varlen), _token_tensor(u, varlen), _token_tensor(w, varlen),
+                             _token_scalar(gate, varlen), _state_desc(initial_state), _state_desc(final_state),
+                             state.data_ptr())
+    cabi.check(cabi.load().gdn_seq_state_update(C.byref(args), _stream()), "bf16_chunked_seq_state_update")
+
+
+def bf16_gdn_chunked_compute_O(q, state, k, u, o, gate=None, scale: Optional[float] = None,
+                               compiled_dims: str = "t", cu_seqlens=None, chunk_indices=None, cu_chunks=None,
+                               chunk_size: int = 64) -> None:
+    """Low-level output stage; python_api.cpp:287-302.  Writes `o`."""
+    _require(chunk_size == CHUNK, "only chunk_size 64 is supported")
+    for t, n in ((q, "q"), (k, "k"), (u, "u"), (o, "o"), (state, "state")):
+        _cuda_bf16(t, n)
+    varlen, batch, seq_len, total = _prefill_dims(q, u, cu_seqlens)
+    d = q.shape[-1]
+    _require(d == _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    _require(state.is_contiguous(), "state must be contiguous")
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    gate = _crop_tokens(gate, total if varlen else seq_len)
+    tc = 0
+    if varlen:
+        _require(chunk_indices is not None, "packed mode needs chunk_indices")
+        tc = chunk_indices.numel() // 2
+    shape = _shape(batch, seq_len, total, q.shape[-2], u.shape[-2], d, d, cu_seqlens, chunk_indices, cu_chunks, tc)
+    args = cabi.ComputeOArgs(shape, _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(u, varlen),
+                             _token_tensor(o, varlen), _token_scalar(gate, varlen), state.data_ptr(), float(scale))
+    cabi.check(cabi.load().gdn_compute_o(C.byref(args), _stream()), "bf16_gdn_chunked_compute_O")

@@ -220,6 +220,7 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.scale = a->scale;
     p.is_qk_norm = a->is_qk_norm; p.store_step = a->store_step_state;
     p.num_tiles = static_cast<long long>(s.batch) * s.num_v_heads * (s.head_dim_v / kRecTileRows);
+    GDN_REQUIRE(p.num_tiles < (1ll << 31), "gdn_recurrent_forward: too many state tiles");
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (s.head_dim_k) {

@@ -1,29 +1,249 @@
-// C-ABI entry points of the chunked-prefill path (see include/gdn_b200.h).
+// C-ABI entry points of the chunked-prefill path (see include/gdn_b200.h): tensor-map
+// construction, argument checks and launches of the tcgen05 kernels.
 #include "host_common.hpp"
+#include "kernels/prefill_seq.cuh"
+#include "kernels/prefill_uw.cuh"
+#include "tma_host.hpp"
 
 using namespace gdn;
+
+namespace {
+
+constexpr int kD = 128;  // head dimension the tensor-core kernels are built for
+
+int require_d128(const GdnShape& s, const char* who) {
+    if (s.head_dim_k != kD || s.head_dim_v != kD)
+        return fail(GDN_ERR_UNSUPPORTED,
+                    "%s: the chunked kernels are built for dk = dv = 128 (got %d, %d); pad the head "
+                    "dimension with zeros (the Python and C++ wrappers do)",
+                    who, s.head_dim_k, s.head_dim_v);
+    return GDN_OK;
+}
+
+// 4-D map over a token tensor: (dim, head, token, batch), box 64 x 1 x 64 x 1, 128-byte swizzle.
+int make_token_map(CUtensorMap* out, const GdnTokenTensor& t, const GdnShape& s, int heads, const char* name) {
+    const bool packed = s.cu_seqlens != nullptr;
+    const uint64_t tokens = packed ? static_cast<uint64_t>(s.total_tokens) : static_cast<uint64_t>(s.seq_len);
+    const uint64_t batch = packed ? 1 : static_cast<uint64_t>(s.batch);
+    uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(heads), tokens, batch};
+    uint64_t sb = static_cast<uint64_t>(t.stride_batch) * 2;
+    if (packed || sb == 0) sb = std::max<uint64_t>(16, tokens * static_cast<uint64_t>(t.stride_token) * 2);
+    uint64_t strides[3] = {static_cast<uint64_t>(t.stride_head) * 2, static_cast<uint64_t>(t.stride_token) * 2, sb};
+    if (heads == 1 && strides[0] == 0) strides[0] = kD * 2;
+    uint32_t box[4] = {64, 1, 64, 1};
+    if (tokens == 0) return fail(GDN_ERR_INVALID, "%s: no tokens", name);
+    if (!make_tmap_bf16(out, t.ptr, 4, dims, strides, box, true))
+        return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of %s (strides %llu/%llu/%llu bytes)", name,
+                    (unsigned long long)strides[0], (unsigned long long)strides[1], (unsigned long long)strides[2]);
+    return GDN_OK;
+}
+
+ScalarView scalar_view(const GdnTokenScalar& t) {
+    ScalarView v;
+    v.ptr = t.ptr;
+    v.is_f32 = t.dtype == GDN_F32;
+    v.sb = t.stride_batch;
+    v.st = t.stride_token;
+    v.sh = t.stride_head;
+    return v;
+}
+TokenView token_view(const GdnTokenTensor& t) {
+    TokenView v;
+    v.ptr = static_cast<__nv_bfloat16*>(t.ptr);
+    v.sb = t.stride_batch;
+    v.st = t.stride_token;
+    v.sh = t.stride_head;
+    return v;
+}
+ChunkMap chunk_map(const GdnShape& s) {
+    ChunkMap m;
+    m.cu_seqlens = s.cu_seqlens;
+    m.chunk_indices = s.chunk_indices;
+    m.cu_chunks = s.cu_chunks;
+    m.seq_len = s.seq_len;
+    m.chunks_per_seq = (s.seq_len + kChunk - 1) / kChunk;
+    return m;
+}
+int num_chunks(const GdnShape& s) {
+    return s.cu_seqlens ? s.total_chunks : s.batch * ((s.seq_len + kChunk - 1) / kChunk);
+}
+int check_scalar(const GdnTokenScalar& t, const char* name, bool required) {
+    if (!t.ptr) {
+        GDN_REQUIRE(!required, "%s is NULL", name);
+        return GDN_OK;
+    }
+    GDN_REQUIRE(t.dtype == GDN_BF16 || t.dtype == GDN_F32, "%s dtype must be bf16 or f32", name);
+    return GDN_OK;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+    GDN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    return GDN_OK;
+}
+
+int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& v, const GdnTokenTensor& u,
+              const GdnTokenTensor& w, const GdnTokenScalar& beta, const GdnTokenScalar& gate, bool gate_is_raw,
+              DeviceInfo* d, cudaStream_t st) {
+    const int nc = num_chunks(s);
+    if (nc == 0) return GDN_OK;
+    GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
+    CUtensorMap tmK, tmV;
+    if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
+    if (int rc = make_token_map(&tmV, v, s, s.num_v_heads, "v")) return rc;
+    UWParams p{};
+    p.map = chunk_map(s);
+    p.beta = scalar_view(beta);
+    p.gate = scalar_view(gate);
+    p.gate_is_raw = gate_is_raw;
+    p.u = token_view(u);
+    p.w = token_view(w);
+    p.kh = s.num_k_heads;
+    p.vh = s.num_v_heads;
+    p.status = d->status;
+    constexpr int smem = UWSmem<kD>::kBytes;
+    if (int rc = set_smem(gdn_uw_kernel<kD>, smem)) return rc;
+    gdn_uw_kernel<kD><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, p);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+template <bool O, bool H, bool UN>
+int launch_seq_t(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmW, const CUtensorMap& tmU,
+                 const SeqParams& p, dim3 grid, cudaStream_t st) {
+    constexpr int smem = SeqSmem::kBytes;
+    if (int rc = set_smem(gdn_seq_kernel<O, H, UN>, smem)) return rc;
+    gdn_seq_kernel<O, H, UN><<<grid, 256, smem, st>>>(tmQ, tmK, tmW, tmU, p);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
 int gdn_compute_u_w(const GdnComputeUWArgs* a, gdn_stream_t stream) {
-    (void)a; (void)stream;
-    return fail(GDN_ERR_UNSUPPORTED, "gdn_compute_u_w: not built yet");
+    GDN_REQUIRE(a != nullptr, "gdn_compute_u_w: args is NULL");
+    if (int rc = check_shape(a->shape, true)) return rc;
+    if (int rc = require_d128(a->shape, "gdn_compute_u_w")) return rc;
+    if (int rc = check_token_tensor(a->k, "k", kD)) return rc;
+    if (int rc = check_token_tensor(a->v, "v", kD)) return rc;
+    if (int rc = check_token_tensor(a->u, "u", kD)) return rc;
+    if (int rc = check_token_tensor(a->w, "w", kD)) return rc;
+    if (int rc = check_scalar(a->beta, "beta", true)) return rc;
+    if (int rc = check_scalar(a->gate_cumsum, "gate", false)) return rc;
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    return launch_uw(a->shape, a->k, a->v, a->u, a->w, a->beta, a->gate_cumsum, false, d,
+                     static_cast<cudaStream_t>(stream));
 }
+
 int gdn_seq_state_update(const GdnSeqStateArgs* a, gdn_stream_t stream) {
-    (void)a; (void)stream;
-    return fail(GDN_ERR_UNSUPPORTED, "gdn_seq_state_update: not built yet");
+    GDN_REQUIRE(a != nullptr, "gdn_seq_state_update: args is NULL");
+    const GdnShape& s = a->shape;
+    if (int rc = check_shape(s, false)) return rc;
+    if (int rc = require_d128(s, "gdn_seq_state_update")) return rc;
+    if (int rc = check_token_tensor(a->k, "k", kD)) return rc;
+    if (int rc = check_token_tensor(a->u, "u", kD)) return rc;
+    if (int rc = check_token_tensor(a->w, "w", kD)) return rc;
+    if (int rc = check_scalar(a->gate_cumsum, "gate", false)) return rc;
+    GDN_REQUIRE(a->chunk_states != nullptr, "gdn_seq_state_update: chunk_states is NULL");
+    GDN_REQUIRE(aligned16(a->chunk_states), "chunk_states must be 16-byte aligned");
+    GDN_REQUIRE(!s.cu_seqlens || s.cu_chunks, "gdn_seq_state_update: packed mode needs cu_chunks");
+    GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    CUtensorMap tmK, tmW, tmU;
+    if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
+    if (int rc = make_token_map(&tmW, a->w, s, s.num_v_heads, "w")) return rc;
+    if (int rc = make_token_map(&tmU, a->u, s, s.num_v_heads, "u")) return rc;
+    SeqParams p{};
+    p.map = chunk_map(s);
+    p.gate = scalar_view(a->gate_cumsum);
+    p.gate_is_raw = 0;
+    p.u_out = token_view(a->u);
+    p.state_in = static_cast<const __nv_bfloat16*>(a->initial_state.ptr);
+    p.si_ss = a->initial_state.stride_seq;
+    p.si_sh = a->initial_state.stride_head;
+    p.state_out = static_cast<__nv_bfloat16*>(a->final_state.ptr);
+    p.so_ss = a->final_state.stride_seq;
+    p.so_sh = a->final_state.stride_head;
+    p.chunk_states = static_cast<__nv_bfloat16*>(a->chunk_states);
+    p.kh = s.num_k_heads;
+    p.vh = s.num_v_heads;
+    p.scale = 1.f;
+    p.status = d->status;
+    return launch_seq_t<false, true, true>(tmK, tmK, tmW, tmU, p, dim3(s.batch, s.num_v_heads),
+                                           static_cast<cudaStream_t>(stream));
 }
+
 int gdn_compute_o(const GdnComputeOArgs* a, gdn_stream_t stream) {
     (void)a; (void)stream;
     return fail(GDN_ERR_UNSUPPORTED, "gdn_compute_o: not built yet");
 }
-size_t gdn_chunked_forward_workspace_bytes(const GdnShape* shape) {
-    (void)shape;
-    return 0;
+
+size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
+    if (!s) return 0;
+    const size_t tokens = s->cu_seqlens ? static_cast<size_t>(s->total_tokens)
+                                        : static_cast<size_t>(s->batch) * static_cast<size_t>(s->seq_len);
+    // U and W, (tokens, vh, 128) bf16 each
+    return 2 * tokens * static_cast<size_t>(s->num_v_heads) * kD * 2 + 256;
 }
+
 int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
-    (void)a; (void)stream;
-    return fail(GDN_ERR_UNSUPPORTED, "gdn_chunked_forward: not built yet");
+    GDN_REQUIRE(a != nullptr, "gdn_chunked_forward: args is NULL");
+    const GdnShape& s = a->shape;
+    if (int rc = check_shape(s, true)) return rc;
+    if (int rc = require_d128(s, "gdn_chunked_forward")) return rc;
+    if (int rc = check_token_tensor(a->q, "q", kD)) return rc;
+    if (int rc = check_token_tensor(a->k, "k", kD)) return rc;
+    if (int rc = check_token_tensor(a->v, "v", kD)) return rc;
+    if (int rc = check_token_tensor(a->out, "out", kD)) return rc;
+    if (int rc = check_scalar(a->beta, "beta", true)) return rc;
+    if (int rc = check_scalar(a->gate, "gate", false)) return rc;
+    GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
+    const size_t need = gdn_chunked_forward_workspace_bytes(&s);
+    if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+        return fail(GDN_ERR_WORKSPACE, "gdn_chunked_forward: workspace of %zu bytes (256-byte aligned) required, got %zu",
+                    need, a->workspace_bytes);
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const bool packed = s.cu_seqlens != nullptr;
+    const long long tokens_per_batch = packed ? s.total_tokens : s.seq_len;
+    const long long tokens = packed ? s.total_tokens : static_cast<long long>(s.batch) * s.seq_len;
+    GdnTokenTensor u, w;
+    u.ptr = a->workspace;
+    u.stride_head = kD;
+    u.stride_token = static_cast<int64_t>(s.num_v_heads) * kD;
+    u.stride_batch = packed ? 0 : tokens_per_batch * u.stride_token;
+    w = u;
+    w.ptr = static_cast<__nv_bfloat16*>(a->workspace) + tokens * s.num_v_heads * kD;
+
+    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st)) return rc;
+
+    CUtensorMap tmQ, tmK, tmW, tmU;
+    if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
+    if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
+    if (int rc = make_token_map(&tmW, w, s, s.num_v_heads, "w")) return rc;
+    if (int rc = make_token_map(&tmU, u, s, s.num_v_heads, "u")) return rc;
+    SeqParams p{};
+    p.map = chunk_map(s);
+    p.gate = scalar_view(a->gate);
+    p.gate_is_raw = 1;
+    p.out = token_view(a->out);
+    p.state_in = static_cast<const __nv_bfloat16*>(a->initial_state.ptr);
+    p.si_ss = a->initial_state.stride_seq;
+    p.si_sh = a->initial_state.stride_head;
+    p.state_out = static_cast<__nv_bfloat16*>(a->final_state.ptr);
+    p.so_ss = a->final_state.stride_seq;
+    p.so_sh = a->final_state.stride_head;
+    p.kh = s.num_k_heads;
+    p.vh = s.num_v_heads;
+    p.scale = a->scale;
+    p.status = d->status;
+    return launch_seq_t<true, false, false>(tmQ, tmK, tmW, tmU, p, dim3(s.batch, s.num_v_heads), st);
 }
 
 }  // extern "C"

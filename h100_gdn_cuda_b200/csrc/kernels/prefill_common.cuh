@@ -1,0 +1,89 @@
+// Pieces shared by the chunked-prefill kernels: chunk lookup, gate/beta loading with the
+// chunk-local cumulative sum, and the coalesced row-predicated store of a staged tile.
+#pragma once
+#include "sm100_ptx.cuh"
+
+namespace gdn {
+
+constexpr int kChunk = 64;
+
+// per-token scalar tensor (beta or gate) as the kernels see it
+struct ScalarView {
+    const void* ptr;
+    int is_f32;
+    long long sb, st, sh;
+    __device__ __forceinline__ float load(long long b, long long t, int h) const {
+        const long long o = b * sb + t * st + static_cast<long long>(h) * sh;
+        return is_f32 ? __ldg(reinterpret_cast<const float*>(ptr) + o)
+                      : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ptr)[o]);
+    }
+};
+
+struct TokenView {
+    __nv_bfloat16* ptr;
+    long long sb, st, sh;
+};
+
+// Where the chunks of the problem are.
+struct ChunkMap {
+    const int* cu_seqlens;     // packed mode or NULL
+    const int* chunk_indices;  // packed mode: [seq, chunk] pairs
+    const int* cu_chunks;      // packed mode: first global chunk of each sequence
+    int seq_len;               // padded mode
+    int chunks_per_seq;        // padded mode
+};
+
+struct ChunkPos {
+    int seq;          // sequence index
+    int batch;        // batch coordinate for addressing (0 in packed mode)
+    long long tok0;   // first token of the chunk (index along the token axis of `batch`)
+    int n;            // valid tokens in the chunk (1..64)
+};
+
+// chunk `c` (in chunk_indices order / batch-major order) -> position
+__device__ __forceinline__ ChunkPos locate_chunk(const ChunkMap& m, int c) {
+    ChunkPos r;
+    if (m.cu_seqlens) {
+        r.seq = m.chunk_indices[2 * c];
+        const int ci = m.chunk_indices[2 * c + 1];
+        const int bos = m.cu_seqlens[r.seq], eos = m.cu_seqlens[r.seq + 1];
+        r.batch = 0;
+        r.tok0 = static_cast<long long>(bos) + static_cast<long long>(ci) * kChunk;
+        const long long rem = eos - r.tok0;
+        r.n = rem < kChunk ? static_cast<int>(rem) : kChunk;
+    } else {
+        r.seq = c / m.chunks_per_seq;
+        const int ci = c % m.chunks_per_seq;
+        r.batch = r.seq;
+        r.tok0 = static_cast<long long>(ci) * kChunk;
+        const int rem = m.seq_len - ci * kChunk;
+        r.n = rem < kChunk ? rem : kChunk;
+    }
+    return r;
+}
+
+// Offset of 16-byte chunk `chunk` of row `row` in a staging tile of D bf16 per row whose
+// chunks are XOR-swizzled by the row so that 16 rows written at once hit distinct banks.
+template <int D>
+__device__ __forceinline__ uint32_t stage_off(int row, int chunk) {
+    constexpr int CPR = D / 8;
+    return static_cast<uint32_t>(row) * (D * 2) + static_cast<uint32_t>((chunk ^ (row & (CPR - 1))) * 16);
+}
+
+// Copy rows [0, n) of a staged 64 x D bf16 tile to global memory, 16 bytes per thread,
+// consecutive threads on consecutive 16-byte pieces of a row.
+template <int D, int THREADS>
+__device__ __forceinline__ void store_staged_tile(const uint8_t* stage, const TokenView& dst, int batch,
+                                                  long long tok0, int head, int n, int tid) {
+    constexpr int CPR = D / 8;
+    __nv_bfloat16* base = dst.ptr + batch * dst.sb + tok0 * dst.st + static_cast<long long>(head) * dst.sh;
+    for (int idx = tid; idx < kChunk * CPR; idx += THREADS) {
+        const int row = idx / CPR, chunk = idx % CPR;
+        if (row < n) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + stage_off<D>(row, chunk));
+            *reinterpret_cast<uint4*>(base + row * dst.st + chunk * 8) = v;
+        }
+    }
+}
+
+}  // namespace gdn

@@ -114,6 +114,15 @@ GDN_DEVICE void tma_load_3d(void* dst, const void* tmap, uint64_t* bar, int c0, 
         "r"(c1), "r"(c2)
         : "memory");
 }
+GDN_DEVICE void tma_load_4d(void* dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
+                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0),
+        "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(

@@ -1,0 +1,216 @@
+"""GPU parity of the chunked-prefill path (tcgen05 kernels) against the CPU oracle.
+
+Tolerances (bf16 tensors out, fp32 oracle on the same bf16-rounded inputs): relative
+Frobenius error <= 1e-2 and max-abs error <= 5e-2 * max|ref| for O, final state, U, W,
+U_new and per-chunk states.  The end-to-end checks compare with the *token recurrence*
+(the layer semantics), not with a chunked re-statement.
+"""
+import pytest
+import torch
+
+from oracle import gdn_oracle as O
+from h100_gdn_cuda_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO, MAX_ABS = 1e-2, 5e-2
+
+
+def close(x, ref, what, rel=REL_FRO, mx=MAX_ABS):
+    x = x.float().cpu()
+    assert torch.isfinite(x).all(), "%s has non-finite values" % what
+    rf, ma = O.rel_fro(x, ref), O.max_abs_over_max(x, ref)
+    assert rf <= rel and ma <= mx, "%s: rel_fro %.3e max_abs/max %.3e" % (what, rf, ma)
+    return rf, ma
+
+
+@pytest.fixture(scope="module")
+def gdn():
+    import h100_gdn_cuda_b200 as g
+    from h100_gdn_cuda_b200 import build
+    build.build()
+    return g
+
+
+def dev(d):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in d.items()}
+
+
+def f32(p, *names):
+    return [None if p[n] is None else p[n].float() for n in names]
+
+
+def check_status(gdn):
+    import ctypes
+    from h100_gdn_cuda_b200 import _cabi
+    st = ctypes.c_int(0)
+    assert _cabi.load().gdn_device_status(torch.cuda.current_device(), ctypes.byref(st)) == 0
+    assert st.value == 0, "a kernel reported a bounded wait that ran out (status %d)" % st.value
+
+
+# ---------------------------------------------------------------- per-stage
+@pytest.mark.parametrize("B,T,kh,vh,mild", [(1, 64, 1, 1, False), (2, 130, 2, 4, True), (1, 255, 1, 2, False)])
+def test_compute_u_w_padded(gdn, B, T, kh, vh, mild):
+    p = synthetic.prefill_inputs(B, T, kh, vh, 128, seed=T, with_state=False, mild_gate=mild)
+    gc = O.chunk_local_cumsum_ref(p["g"])
+    u_ref, w_ref = O.compute_u_w_ref(*f32(p, "k", "v", "beta"), gc)
+    pd = dev(p)
+    u = torch.full_like(pd["v"], float("nan"))
+    w = torch.full_like(pd["v"], float("nan"))
+    # MN-major beta / gate as the reference's wrappers require
+    beta_mn = gdn.transpose_to_mn_major(pd["beta"])
+    gate_mn = gdn.transpose_to_mn_major(gc.cuda())
+    gdn.bf16_gdn_compute_u_w(pd["k"], pd["v"], u, w, beta_mn, gate_mn)
+    check_status(gdn)
+    close(u, u_ref, "U")
+    close(w, w_ref, "W")
+    # token-major scalars give the same bits
+    u2, w2 = torch.empty_like(u), torch.empty_like(w)
+    gdn.bf16_gdn_compute_u_w(pd["k"], pd["v"], u2, w2, pd["beta"], gc.cuda())
+    assert torch.equal(u2, u) and torch.equal(w2, w)
+
+
+def test_compute_u_w_varlen_ragged(gdn):
+    lens = [1, 63, 64, 65, 130, 2]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=5, with_state=False, mild_gate=True)
+    gc = O.chunk_local_cumsum_ref(p["g"], p["cu_seqlens"])
+    u_ref, w_ref = O.compute_u_w_ref(*f32(p, "k", "v", "beta"), gc, p["cu_seqlens"])
+    pd = dev(p)
+    u = torch.full_like(pd["v"], float("nan"))
+    w = torch.full_like(pd["v"], float("nan"))
+    gdn.bf16_gdn_compute_u_w(pd["k"], pd["v"], u, w, pd["beta"], gc.cuda(), cu_seqlens=pd["cu_seqlens"],
+                             chunk_indices=pd["chunk_indices"])
+    check_status(gdn)
+    close(u, u_ref, "U")
+    close(w, w_ref, "W")
+
+
+@pytest.mark.parametrize("varlen", [False, True])
+def test_seq_state_update(gdn, varlen):
+    if varlen:
+        lens = [65, 1, 200, 64]
+        p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=8, mild_gate=True)
+        cu = p["cu_seqlens"]
+    else:
+        p = synthetic.prefill_inputs(2, 200, 2, 4, 128, seed=8, mild_gate=True)
+        cu = None
+    gc = O.chunk_local_cumsum_ref(p["g"], cu)
+    u_ref, w_ref = O.compute_u_w_ref(*f32(p, "k", "v", "beta"), gc, cu)
+    u_bf, w_bf = u_ref.bfloat16(), w_ref.bfloat16()
+    h_ref, un_ref, s_ref = O.seq_state_update_ref(p["k"].float(), u_bf.float(), w_bf.float(), gc, p["state"].float(), cu)
+    pd = dev(p)
+    u, w = u_bf.cuda(), w_bf.cuda()
+    state = torch.full(h_ref.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    final = torch.empty_like(pd["state"])
+    kw = dict(cu_seqlens=pd["cu_seqlens"], cu_chunks=pd["cu_chunks"], total_chunks=p["total_chunks"]) if varlen else {}
+    gdn.bf16_chunked_seq_state_update(pd["k"], u, w, pd["state"], state, final, gc.cuda(), **kw)
+    check_status(gdn)
+    close(state, h_ref, "chunk states")
+    close(u, un_ref, "U_new")
+    close(final, s_ref, "final state")
+
+
+# ---------------------------------------------------------------- end to end
+PADDED = [
+    # (B, T, kh, vh, d)   shapes from the reference's test lists plus BASELINE-like ones
+    (1, 63, 1, 1, 64), (2, 500, 3, 3, 60), (2, 1000, 3, 3, 64), (3, 1024, 4, 4, 100), (4, 1024, 4, 4, 128),
+    (2, 1500, 4, 4, 128), (1, 130, 2, 4, 128), (1, 97, 1, 2, 128), (2, 65, 2, 2, 128), (1, 255, 2, 8, 128),
+    (1, 256, 4, 4, 64), (2, 512, 16, 32, 128),
+]
+
+
+@pytest.mark.parametrize("B,T,kh,vh,d", PADDED)
+@pytest.mark.parametrize("mild", [False, True])
+def test_chunked_forward_padded(gdn, B, T, kh, vh, d, mild):
+    p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=T + d, mild_gate=mild)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float())
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"])
+    check_status(gdn)
+    assert o.shape == p["v"].shape and s.shape == p["state"].shape
+    close(o, o_ref, "O")
+    close(s, s_ref, "final state")
+
+
+def test_chunked_forward_no_state_custom_scale(gdn):
+    p = synthetic.prefill_inputs(2, 300, 2, 4, 128, seed=77, with_state=False, mild_gate=True)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], None, scale=0.5)
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], 0.5)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final state")
+
+
+RAGGED = [
+    [64, 64], [128, 64, 192], [1], [2, 1, 63, 65], [130, 97, 65, 255], [1, 64, 1, 65, 1],
+    [63, 63, 63], [300, 5, 1000, 64, 17], [700, 1, 1, 129],
+]
+
+
+@pytest.mark.parametrize("lens", RAGGED)
+def test_chunked_forward_varlen(gdn, lens):
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=sum(lens), mild_gate=(len(lens) % 2 == 0))
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"])
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final state")
+
+
+def test_varlen_equals_padded_per_sequence(gdn):
+    lens = [200, 77]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=4, mild_gate=True)
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    off = 0
+    for i, n in enumerate(lens):
+        sl = slice(off, off + n)
+        oi, si = gdn.chunked_forward(pd["q"][None, sl], pd["k"][None, sl], pd["v"][None, sl], pd["beta"][None, sl],
+                                     pd["g"][None, sl], None, pd["state"][i:i + 1])
+        assert torch.equal(oi[0], o[sl]) and torch.equal(si[0], s[i])
+        off += n
+
+
+def test_prefill_state_handoff(gdn):
+    # prefill(T1) -> state -> prefill(T2) == prefill(T1+T2); then hand the state to decode
+    p = synthetic.prefill_inputs(1, 384, 2, 4, 128, seed=12, mild_gate=True)
+    pd = dev(p)
+    a = [pd[k] for k in ("q", "k", "v", "beta", "g")]
+    o, s = gdn.chunked_forward(*a, None, pd["state"])
+    o1, s1 = gdn.chunked_forward(*(x[:, :128] for x in a), None, pd["state"])
+    o2, s2 = gdn.chunked_forward(*(x[:, 128:] for x in a), None, s1)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float())
+    close(torch.cat([o1, o2], 1), o_ref, "O (two-part)")
+    close(s2, s_ref, "state (two-part)")
+    # decode continues from the prefill state
+    d = synthetic.decode_inputs(1, 1, 2, 4, 128, seed=3)
+    beta, g = O.gating_ref(d["A_log"], d["dt_bias"], d["a"], d["b"])
+    od, sd = gdn.recurrent_forward(d["q"].cuda(), d["k"].cuda(), d["v"].cuda(), s, beta.bfloat16().cuda(), g.cuda(),
+                                   is_qk_norm=True, inference_mode=1)
+    od_ref, sd_ref = O.recurrent_ref(d["q"].float(), d["k"].float(), d["v"].float(), beta.bfloat16().float(), g,
+                                     s.float().cpu(), is_qk_norm=True)
+    close(od, od_ref, "decode O after prefill")
+    close(sd, sd_ref, "decode state after prefill")
+
+
+def test_chunked_head_sliced_views(gdn):
+    # value-head sharding: non-contiguous head slices must give the same bits as the full call
+    p = synthetic.prefill_inputs(1, 200, 4, 8, 128, seed=31, mild_gate=True)
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"])
+    oh, sh = gdn.chunked_forward(pd["q"][:, :, 2:4], pd["k"][:, :, 2:4], pd["v"][:, :, 4:8], pd["beta"][:, :, 4:8],
+                                 pd["g"][:, :, 4:8], None, pd["state"][:, 4:8])
+    assert torch.equal(oh, o[:, :, 4:8]) and torch.equal(sh, s[:, 4:8])
+
+
+def test_chunked_errors(gdn):
+    p = dev(synthetic.prefill_inputs(1, 64, 1, 1, 128, seed=1))
+    with pytest.raises(RuntimeError):
+        gdn.chunked_forward(p["q"].float(), p["k"], p["v"], p["beta"], p["g"])
+    big = torch.zeros(1, 64, 1, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        gdn.chunked_forward(big, big, big, p["beta"], p["g"])
