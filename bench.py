@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the Gated DeltaNet hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass of chunked prefill (`chunked_forward`) over one batch of the padded
+prefill configuration: B=4, T=4096, kh=16, vh=32, dk=dv=128, bf16 q/k/v/beta, fp32 gate, bf16
+initial state (synthetic, seeded).  With N > 1 (launched under torchrun, one rank per GPU)
+every rank processes its own batch of that size - sequences are independent, so the path
+shards by sequence with no collective - and `value` is the total over ranks (weak scaling).
+
+The printed JSON line carries:
+  value      prefill tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e        the same through the public API from pinned HOST buffers: host->device copies of
+             q, k, v, beta, gate and the state and the device->host copy of O and the final
+             state are inside the timed region
+  roofline   for the dominant kernel (the state/output kernel), timed live with CUDA events
+  decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, fused gating) and its
+             HBM roofline fraction
+  cpu_baseline  the fp32 CPU token recurrence (the oracle) on a bounded sample, rank 0, N=1
+
+`--impl reference` times only that CPU recurrence (the reference library's own sm_90a kernels
+cannot run on a B200 and it has no CPU path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(B=4, T=4096, kh=16, vh=32, d=128)
+DECODE = dict(B=256, T=1, kh=16, vh=32, d=128)
+CHUNK = 64
+
+
+def flops_per_unit(d: int, c: int = CHUNK) -> float:
+    """All contractions of one (64-token chunk, v-head): 2C(5Cd + 3dd) + (2/3)C^3."""
+    return 2.0 * c * (5 * c * d + 3 * d * d) + (2.0 / 3.0) * c ** 3
+
+
+def seq_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
+    """Contractions done by the state/output kernel: QK^T, P U_new (2Ccd each) and
+    W S^T, Q S^T, U_new^T K (2Cdd each)."""
+    return 2.0 * c * (2 * c * d + 3 * d * d)
+
+
+def uw_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
+    return 2.0 * c * (3 * c * d) + (2.0 / 3.0) * c ** 3
+
+
+def decode_bytes_per_token(kh, vh, d) -> float:
+    return vh * (2 * d * d * 2) + 2 * (2 * kh * d + 2 * vh * d) + vh * 4
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=mx, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def cpu_recurrence_tokens_per_s(sample_tokens: int, repeats: int = 1):
+    """fp32 CPU token recurrence (the oracle) on one sequence of `sample_tokens` tokens of the
+    prefill configuration; returns (tokens/s, threads, description)."""
+    from oracle import gdn_oracle as O
+    from h100_gdn_cuda_b200 import synthetic
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    p = synthetic.prefill_inputs(1, sample_tokens, CFG["kh"], CFG["vh"], CFG["d"], seed=0)
+    args = [p[k].float() for k in ("q", "k", "v", "beta")] + [p["g"], p["state"].float()]
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        O.recurrent_ref(*args)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_tokens / best, threads, "B=1 x T=%d of the prefill config (kh=16, vh=32, d=128), fp32 torch" % sample_tokens
+
+
+def run_reference(args):
+    """The reference arm: the CPU recurrence, the only implementation of the path that can run
+    on this box (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 1024
+    from oracle import gdn_oracle as O
+    from h100_gdn_cuda_b200 import synthetic
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    p = synthetic.prefill_inputs(1, sample, CFG["kh"], CFG["vh"], CFG["d"], seed=0)
+    a = [p[k].float() for k in ("q", "k", "v", "beta")] + [p["g"], p["state"].float()]
+    for _ in range(args.warmup):
+        O.recurrent_ref(*a)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.recurrent_ref(*a)
+    dt = (time.perf_counter() - t0) / args.steps
+    tps = sample / dt
+    line = {
+        "impl": "reference", "metric": "prefill_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128", "l2": "not applicable (CPU)"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": "each step = B=1 x T=%d of the prefill config, fp32 torch token recurrence" % sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import h100_gdn_cuda_b200 as gdn
+    from h100_gdn_cuda_b200 import build, synthetic
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    gdn.init(ROOT, os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    peaks = load_peaks()
+    dev = torch.device("cuda", local)
+
+    B, T, kh, vh, d = (CFG[k] for k in ("B", "T", "kh", "vh", "d"))
+    p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=rank)
+    host = {k: p[k].pin_memory() for k in ("q", "k", "v", "beta", "g", "state")}
+    devt = {k: v.to(dev) for k, v in host.items()}
+    tokens = B * T
+    units = B * ((T + CHUNK - 1) // CHUNK) * vh
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ws = torch.empty(2 * tokens * vh * d * 2 + 256, dtype=torch.uint8, device=dev)
+    stage_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for e in stage_ev:
+        e.record()
+
+    def step_resident(events=None):
+        return gdn.chunked_forward(devt["q"], devt["k"], devt["v"], devt["beta"], devt["g"], None, devt["state"],
+                                   _workspace=ws, _stage_events=events)
+
+    # ---------------- device-resident timing (inputs 0.4 GB per step: larger than the 126 MB L2)
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    uw_ms, seq_ms = 0.0, 0.0
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms_res = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    # per-kernel durations: same steps again with events between the two kernels
+    for _ in range(args.steps):
+        step_resident(stage_ev)
+        torch.cuda.synchronize()
+        uw_ms += stage_ev[0].elapsed_time(stage_ev[1])
+        seq_ms += stage_ev[1].elapsed_time(stage_ev[2])
+    uw_ms /= args.steps
+    seq_ms /= args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---------------- end to end from host buffers
+    out_host = torch.empty(B, T, vh, d, dtype=torch.bfloat16).pin_memory()
+    st_host = torch.empty(B, vh, d, d, dtype=torch.bfloat16).pin_memory()
+    stage = {k: torch.empty_like(v) for k, v in devt.items()}
+
+    def step_e2e():
+        for k in ("q", "k", "v", "beta", "g", "state"):
+            stage[k].copy_(host[k], non_blocking=True)
+        o, s = gdn.chunked_forward(stage["q"], stage["k"], stage["v"], stage["beta"], stage["g"], None,
+                                   stage["state"], _workspace=ws)
+        out_host.copy_(o, non_blocking=True)
+        st_host.copy_(s, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    h2d = sum(host[k].numel() * host[k].element_size() for k in host)
+    d2h = out_host.numel() * 2 + st_host.numel() * 2
+
+    # ---------------- decode (B=256, T=1): state 268 MB per step, larger than L2
+    dB = DECODE["B"]
+    dp = synthetic.decode_inputs(dB, 1, kh, vh, d, seed=100 + rank)
+    dd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in dp.items()}
+    states = [dd["state"].clone() for _ in range(2)]
+
+    def step_decode(i):
+        beta, gate = gdn.fused_gdn_gating(dd["A_log"], dd["dt_bias"], dd["a"], dd["b"])
+        return gdn.recurrent_forward(dd["q"], dd["k"], dd["v"], states[i & 1], beta, gate, inference_mode=1,
+                                     is_qk_norm=True)
+
+    for i in range(5):
+        step_decode(i)
+    barrier()
+    dsteps = max(args.steps, 20)
+    e0.record()
+    for i in range(dsteps):
+        step_decode(i)
+    e1.record()
+    barrier()
+    ms_dec = max_over_ranks(e0.elapsed_time(e1) / dsteps)
+    # the recurrent kernel alone (gating excluded) for its roofline
+    beta, gate = gdn.fused_gdn_gating(dd["A_log"], dd["dt_bias"], dd["a"], dd["b"])
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(dsteps):
+        gdn.recurrent_forward(dd["q"], dd["k"], dd["v"], states[i & 1], beta, gate, inference_mode=1, is_qk_norm=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_dec_kernel = e0.elapsed_time(e1) / dsteps
+    dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        tps, cores, what = cpu_recurrence_tokens_per_s(4096)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": what}
+
+    seq_flops = units * seq_kernel_flops_per_unit(d)
+    achieved = seq_flops / (seq_ms * 1e-3) / 1e12
+    total_flops = units * flops_per_unit(d)
+    line = {
+        "metric": "prefill_tokens_per_s", "value": world * tokens / (ms_res * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128 chunk=64 per GPU",
+                   "sharding": "by sequence, no collective", "l2": "inputs (0.41 GB per step) larger than L2"},
+        "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"kernel": "gdn_seq_kernel (state propagation + output)", "bound": "tensor",
+                     "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
+                     "ms_per_launch": seq_ms, "flops_per_launch": seq_flops},
+        "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_seq_kernel_ms": seq_ms,
+                    "uw_tflops": units * uw_kernel_flops_per_unit(d) / (uw_ms * 1e-3) / 1e12,
+                    "whole_step_tflops": total_flops / (ms_res * 1e-3) / 1e12,
+                    "whole_step_frac_of_tensor_peak": total_flops / (ms_res * 1e-3) / 1e12 / peaks["tflops"]},
+        "decode": {"metric": "decode_tokens_per_s", "value": world * dB / (ms_dec * 1e-3), "unit": "tokens/s",
+                   "config": "B=256 T=1 kh=16 vh=32 d=128, qk-norm, fused gating, per GPU", "ms_per_step": ms_dec,
+                   "roofline": {"kernel": "gdn_recurrent_kernel", "bound": "hbm",
+                                "achieved": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                                "unit": "GB/s", "frac": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                "frac_of_nominal_8TBs": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / 8000.0,
+                                "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes}},
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

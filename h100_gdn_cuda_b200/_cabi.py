@@ -63,7 +63,8 @@ class ChunkedArgs(C.Structure):
     _fields_ = [("shape", Shape), ("q", TokenTensor), ("k", TokenTensor), ("v", TokenTensor),
                 ("out", TokenTensor), ("beta", TokenScalar), ("gate", TokenScalar),
                 ("initial_state", State), ("final_state", State), ("scale", C.c_float),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("stage_events", C.POINTER(C.c_void_p))]
 
 
 # name -> (restype, argtypes); every symbol include/gdn_b200.h declares

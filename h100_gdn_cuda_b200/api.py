@@ -255,7 +255,8 @@ def _check_head_dim(d: int):
 
 
 def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None, initial_state=None,
-                    cu_seqlens=None, chunk_indices=None, cu_chunks=None, total_chunks: Optional[int] = None):
+                    cu_seqlens=None, chunk_indices=None, cu_chunks=None, total_chunks: Optional[int] = None,
+                    *, _stage_events=None, _workspace=None):
     """Chunked (64-token) Gated DeltaNet prefill; python_api.cpp:47-60, csrc/apis/gdn_forward.cpp:18-132.
 
     query/key (B,T,kh,d) or (N,kh,d); value (B,T,vh,d) or (N,vh,d); beta bf16 and gate fp32
@@ -290,10 +291,15 @@ def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None
     shape = _shape(batch, seq_len, total, kh, vh, D, D, cu_seqlens, chunk_indices, cu_chunks, tc)
     lib = cabi.load()
     ws_bytes = lib.gdn_chunked_forward_workspace_bytes(C.byref(shape))
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    ws = _workspace if _workspace is not None and _workspace.numel() >= ws_bytes else \
+        torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    ev = None
+    if _stage_events is not None:  # three torch.cuda.Event(enable_timing=True), already recorded once
+        ev = (C.c_void_p * 3)(*[e.cuda_event for e in _stage_events])
     args = cabi.ChunkedArgs(shape, _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen),
                             _token_tensor(out, varlen), _token_scalar(beta, varlen), _token_scalar(gate, varlen),
-                            _state_desc(s_in), _state_desc(final), float(scale), ws.data_ptr(), ws_bytes)
+                            _state_desc(s_in), _state_desc(final), float(scale), ws.data_ptr(), ws_bytes,
+                            ev)
     cabi.check(lib.gdn_chunked_forward(C.byref(args), _stream()), "chunked_forward")
     if d != D:
         out, final = out[..., :d], final[..., :d, :d]

@@ -221,7 +221,10 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     w = u;
     w.ptr = static_cast<__nv_bfloat16*>(a->workspace) + tokens * s.num_v_heads * kD;
 
+    void* const* ev = a->stage_events;
+    if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[0]), st));
     if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st)) return rc;
+    if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
     CUtensorMap tmQ, tmK, tmW, tmU;
     if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
@@ -243,7 +246,9 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     p.vh = s.num_v_heads;
     p.scale = a->scale;
     p.status = d->status;
-    return launch_seq_t<true, false, false>(tmQ, tmK, tmW, tmU, p, dim3(s.batch, s.num_v_heads), st);
+    if (int rc = launch_seq_t<true, false, false>(tmQ, tmK, tmW, tmU, p, dim3(s.batch, s.num_v_heads), st)) return rc;
+    if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
+    return GDN_OK;
 }
 
 }  // extern "C"

@@ -208,6 +208,9 @@ typedef struct {
     float scale;
     void* workspace;
     size_t workspace_bytes;
+    /* Optional profiling aid: NULL, or three cudaEvent_t recorded on `stream` before the first
+     * kernel, between the WY/UT kernel and the state/output kernel, and after the last. */
+    void* const* stage_events;
 } GdnChunkedArgs;
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* shape);
 int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
