@@ -172,6 +172,38 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_only(args, gdn, synthetic, dev, peaks):
+    """Small single-path runs for profiler captures (few launches, a few hundred MB)."""
+    kh, vh, d = CFG["kh"], CFG["vh"], CFG["d"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.only == "prefill":
+        B, T = args.batch or 2, CFG["T"]
+        p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=0)
+        t = {k: p[k].to(dev) for k in ("q", "k", "v", "beta", "g", "state")}
+        run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"])
+        work, unit = B * T, "tokens/s"
+    else:
+        B = args.batch or 128
+        p = synthetic.decode_inputs(B, 1, kh, vh, d, seed=0)
+        t = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
+        beta, gate = gdn.fused_gdn_gating(t["A_log"], t["dt_bias"], t["a"], t["b"])
+        states = [t["state"], t["state"].clone()]
+        run = lambda i: gdn.recurrent_forward(t["q"], t["k"], t["v"], states[i & 1], beta, gate, inference_mode=1,
+                                              is_qk_norm=True)
+        work, unit = B, "tokens/s"
+    for i in range(args.warmup):
+        run(i)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(args.steps):
+        run(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"only": args.only, "batch": B, "ms_per_step": ms, "value": work / (ms * 1e-3), "unit": unit,
+                      "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -179,8 +211,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["prefill", "decode"],
+                    help="profiling aid: run only this path, resident inputs, reduced JSON line")
+    ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.only is None:
+        args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
 
@@ -205,6 +241,8 @@ def main():
     dev = torch.device("cuda", local)
 
     B, T, kh, vh, d = (CFG[k] for k in ("B", "T", "kh", "vh", "d"))
+    if args.only is not None:
+        return run_only(args, gdn, synthetic, dev, peaks)
     p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=rank)
     host = {k: p[k].pin_memory() for k in ("q", "k", "v", "beta", "g", "state")}
     devt = {k: v.to(dev) for k, v in host.items()}
