@@ -84,6 +84,7 @@ SYMBOLS = {
     "gdn_compute_o": (C.c_int, [C.POINTER(ComputeOArgs), C.c_void_p]),
     "gdn_chunked_forward_workspace_bytes": (C.c_size_t, [C.POINTER(Shape)]),
     "gdn_chunked_forward": (C.c_int, [C.POINTER(ChunkedArgs), C.c_void_p]),
+    "gdn_chunked_forward_static_scratch": (C.c_int, [C.POINTER(ChunkedArgs), C.c_void_p]),
 }
 
 _lib = None

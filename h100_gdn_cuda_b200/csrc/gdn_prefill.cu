@@ -251,4 +251,43 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     return GDN_OK;
 }
 
+// ------------------------------------------------------------------ prefill on built-in scratch
+// Scratch for callers that cannot allocate device memory (see include/gdn_b200.h).  The array
+// lives in the library image; in host code its name is only a handle for the runtime, so the
+// device address is looked up once per device and that address is what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[GDN_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[64] = {};
+static std::mutex g_static_scratch_mutex;
+
+int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* a, gdn_stream_t stream) {
+    GDN_REQUIRE(a != nullptr, "gdn_chunked_forward_static_scratch: args is NULL");
+    if (int rc = check_shape(a->shape, true)) return rc;
+    const size_t need = gdn_chunked_forward_workspace_bytes(&a->shape);
+    if (need > GDN_STATIC_SCRATCH_BYTES)
+        return fail(GDN_ERR_WORKSPACE,
+                    "gdn_chunked_forward_static_scratch: this problem needs %zu bytes of scratch but the built-in "
+                    "array holds %u (tokens * num_v_heads must not exceed %u); use gdn_chunked_forward with a "
+                    "caller-provided workspace",
+                    need, GDN_STATIC_SCRATCH_BYTES, (GDN_STATIC_SCRATCH_BYTES - 256u) / 512u);
+    int dev = 0;
+    GDN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(GDN_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (!g_static_scratch_addr[dev]) {
+            // first call on this device (it is the current one): resolve the device address
+            void* p = nullptr;
+            GDN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+            if (!p) return fail(GDN_ERR_CUDA, "built-in scratch array has no device address");
+            g_static_scratch_addr[dev] = p;
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+    GdnChunkedArgs b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = GDN_STATIC_SCRATCH_BYTES;
+    return gdn_chunked_forward(&b, stream);
+}
+
 }  // extern "C"
