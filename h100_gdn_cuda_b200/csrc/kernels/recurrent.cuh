@@ -5,15 +5,18 @@
 // canonical update order  S <- exp(g) S ;  S <- S + beta (v - S k) k^T ;  o = scale S q.
 //
 // The kernel is bound by HBM traffic: per (sequence, v-head) it must read and write the
-// dv x dk bf16 state once.  Work unit = a tile of 32 state rows (32 x DK bf16, 8 KB at
-// DK = 128).  A persistent CTA of 128 threads walks tiles round-robin; tiles are fetched
-// ahead into a ring of shared-memory buffers by bulk asynchronous copies (one elected
-// thread issues them, completion is signalled on an mbarrier), so several tiles per CTA
-// are in flight while the current one is processed.  Each thread keeps 4 rows x DK/16
-// columns of the tile in fp32 registers; the two products S.k and S.q are row sums reduced
-// over 16 lanes with shuffles, both taken from the same pass over the old state:
+// dv x dk bf16 state once.  A persistent CTA of 128 threads takes (sequence, v-head) units
+// round-robin and walks each unit's tiles of 32 state rows (32 x DK bf16, 8 KB at DK = 128).
+// Tiles are fetched ahead into a ring of shared-memory buffers by bulk asynchronous copies
+// (one elected thread issues them together with the first token's k, q and v slice,
+// completion is signalled on an mbarrier), so several tiles per CTA are in flight while the
+// current one is processed.  Each thread keeps 4 rows x DK/16 columns of the tile as packed
+// fp32 pairs and works on them with two-wide fp32 FMAs; the two products S.k and S.q come
+// from the same pass over the old state:
 //     r = v - e^g (S k),   S' = e^g S + beta r k^T,   o = scale (e^g (S q) + beta r (k.q)).
-// New states leave through coalesced 8-byte stores straight from registers.
+// The eight row sums are reduced over 16 lanes with a transposing butterfly (8 shuffles
+// instead of 32).  For single-token decode q/k normalisation and k.q are computed once per
+// unit, not per tile.  New states leave through coalesced 8-byte stores from registers.
 #pragma once
 #include "sm100_ptx.cuh"
 
@@ -49,7 +52,7 @@ constexpr int kRecTileRows = 32;
 constexpr int kRecStages = 4;
 constexpr int kRecThreads = 128;
 
-// One ring stage: the 32 x DK state tile, then k and q of the sequence's first token
+// One ring stage: the 32 x DK state tile, then k and q of the unit's first token
 // (DK bf16 each) and the 32 entries of v that belong to the tile's rows.
 template <int DK>
 struct RecStage {
@@ -65,11 +68,42 @@ constexpr int recurrent_smem_bytes() {
     return kRecStages * RecStage<DK>::kBytes + 128;
 }
 
+namespace rec {
+using f2 = unsigned long long;  // two packed fp32 values
+__device__ __forceinline__ f2 pk(float lo, float hi) {
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpk(f2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f2 bf2_to_f2(uint32_t w) {  // bf16 pair -> fp32 pair
+    return pk(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+__device__ __forceinline__ float hsum(f2 v) {
+    float a, b;
+    unpk(v, a, b);
+    return a + b;
+}
+}  // namespace rec
+
 template <int DK>
 __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurrent_kernel(const RecurrentParams p) {
     using namespace ptx;
+    using namespace rec;
     using Stage = RecStage<DK>;
-    constexpr int NP = DK / 64;  // 64-column pieces; each lane owns 4 columns of every piece
+    constexpr int NQ = DK / 32;  // packed pairs per row per lane (lane owns 4 columns of every 64)
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kRecStages * Stage::kBytes);
     __shared__ int abort_flag;
@@ -80,7 +114,7 @@ __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurren
     const int rblocks = p.dv / kRecTileRows;
     const bool has_in = p.state_in != nullptr;
     const int rep = p.vh / p.kh;
-    const int num_tiles = static_cast<int>(p.num_tiles);
+    const int num_units = static_cast<int>(p.num_tiles / rblocks);
     const int stride = static_cast<int>(gridDim.x);
 
     if (tid == 0) {
@@ -90,16 +124,14 @@ __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurren
     }
     __syncthreads();
 
-    struct Tile {
-        int seq, head, rb, khead, ntok;
+    struct Unit {
+        int seq, head, khead, ntok;
         long long tok0, bidx;
     };
-    auto decode = [&](int tile) {
-        Tile t;
-        t.rb = tile % rblocks;
-        const int sh = tile / rblocks;
-        t.head = sh % p.vh;
-        t.seq = sh / p.vh;
+    auto decode = [&](int unit) {
+        Unit t;
+        t.head = unit % p.vh;
+        t.seq = unit / p.vh;
         t.khead = t.head / rep;
         if (p.cu_seqlens) {
             t.tok0 = p.cu_seqlens[t.seq];
@@ -113,25 +145,24 @@ __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurren
         if (p.num_accepted) t.ntok = min(t.ntok, p.num_accepted[t.seq]);
         return t;
     };
-    // Producer (one thread): everything the tile needs for its first token, on one barrier.
-    auto issue = [&](int tile, int stage) {
-        const Tile t = decode(tile);
+    // Producer (one thread): everything tile `rb` of `unit` needs for its first token.
+    auto issue = [&](const Unit& t, int rb, int stage) {
         uint8_t* dst = smem + stage * Stage::kBytes;
-        uint32_t bytes = (has_in ? Stage::kTileBytes : 0) + (t.ntok > 0 ? 4 * DK + kRecTileRows * 2 : 0);
+        const uint32_t bytes = (has_in ? Stage::kTileBytes : 0) + (t.ntok > 0 ? 4 * DK + kRecTileRows * 2 : 0);
         mbar_arrive_expect_tx(&full[stage], bytes);
         if (has_in) {
             const __nv_bfloat16* src = p.state_in + t.seq * p.si_ss + t.head * p.si_sh +
-                                       static_cast<long long>(t.rb) * kRecTileRows * DK;
+                                       static_cast<long long>(rb) * kRecTileRows * DK;
             bulk_load(dst, src, Stage::kTileBytes, &full[stage]);
         }
         if (t.ntok > 0) {
             bulk_load(dst + Stage::kOffK, p.k + t.bidx * p.k_sb + t.tok0 * p.k_st + t.khead * p.k_sh, DK * 2, &full[stage]);
             bulk_load(dst + Stage::kOffQ, p.q + t.bidx * p.q_sb + t.tok0 * p.q_st + t.khead * p.q_sh, DK * 2, &full[stage]);
-            bulk_load(dst + Stage::kOffV, p.v + t.bidx * p.v_sb + t.tok0 * p.v_st + t.head * p.v_sh + t.rb * kRecTileRows,
+            bulk_load(dst + Stage::kOffV, p.v + t.bidx * p.v_sb + t.tok0 * p.v_st + t.head * p.v_sh + rb * kRecTileRows,
                       kRecTileRows * 2, &full[stage]);
         }
     };
-    auto load_scalars = [&](const Tile& t, int tk, float& bt, float& gt) {
+    auto load_scalars = [&](const Unit& t, int tk, float& bt, float& gt) {
         const long long tok = t.tok0 + tk;
         const long long bo = t.bidx * p.beta_sb + tok * p.beta_st + t.head * p.beta_sh;
         bt = p.beta_f32 ? __ldg(reinterpret_cast<const float*>(p.beta) + bo)
@@ -145,201 +176,257 @@ __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurren
         }
     };
 
-    // prologue: fill the ring
+    // The producer walks (unit, rb) pairs kRecStages-1 iterations ahead of the consumers.
+    int prod_unit = blockIdx.x, prod_rb = 0, prod_it = 0;
+    Unit prod_u{};
+    if (tid == 0 && prod_unit < num_units) prod_u = decode(prod_unit);
+    auto produce_one = [&]() {
+        if (prod_unit >= num_units) return;
+        issue(prod_u, prod_rb, prod_it % kRecStages);
+        ++prod_it;
+        if (++prod_rb == rblocks) {
+            prod_rb = 0;
+            prod_unit += stride;
+            if (prod_unit < num_units) prod_u = decode(prod_unit);
+        }
+    };
     if (tid == 0) {
-        int t = blockIdx.x;
-        for (int s = 0; s < kRecStages - 1 && t < num_tiles; ++s, t += stride) issue(t, s);
+        for (int s = 0; s < kRecStages - 1; ++s) produce_one();
     }
-    float beta_first = 0.f, g_first = 0.f;  // scalars of the first token of the *current* tile
-    if (static_cast<int>(blockIdx.x) < num_tiles) {
-        const Tile t0 = decode(blockIdx.x);
+
+    float beta_first = 0.f, g_first = 0.f;  // scalars of the first token of the current unit
+    if (static_cast<int>(blockIdx.x) < num_units) {
+        const Unit t0 = decode(blockIdx.x);
         if (t0.ntok > 0) load_scalars(t0, 0, beta_first, g_first);
     }
 
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += stride, ++it) {
-        const int stage = it % kRecStages;
-        const uint32_t parity = static_cast<uint32_t>((it / kRecStages) & 1);
-        if (tid == 0) {
-            // the stage consumed in the previous iteration is free (block-wide barrier below)
-            const int nt = tile + (kRecStages - 1) * stride;
-            if (nt < num_tiles) issue(nt, (it + kRecStages - 1) % kRecStages);
-        }
-        const Tile T = decode(tile);
-        // scalars of the next tile's first token: requested now, used next iteration
+    for (int unit = blockIdx.x; unit < num_units; unit += stride) {
+        const Unit T = decode(unit);
         float beta_next = 0.f, g_next = 0.f;
-        if (tile + stride < num_tiles) {
-            const Tile tn = decode(tile + stride);
+        if (unit + stride < num_units) {
+            const Unit tn = decode(unit + stride);
             if (tn.ntok > 0) load_scalars(tn, 0, beta_next, g_next);
         }
+        // per-unit values of the first token (kept across the unit's tiles when ntok == 1)
+        f2 k2[NQ], q2[NQ];
+        float kq = 0.f;
 
-        // ---- staged data -> registers
-        float S[4][NP * 4];
-        uint2 kw[NP], qw[NP];
-        float vr[4];
-        mbar_wait(&full[stage], parity, &abort_flag);
-        const uint8_t* st = smem + stage * Stage::kBytes;
-        if (has_in) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int row = warp * 8 + 2 * j + half;
-#pragma unroll
-                for (int pc = 0; pc < NP; ++pc) {
-                    const uint2 w = *reinterpret_cast<const uint2*>(st + (row * DK + pc * 64 + l16 * 4) * 2);
-                    S[j][pc * 4 + 0] = bf16_lo(w.x);
-                    S[j][pc * 4 + 1] = bf16_hi(w.x);
-                    S[j][pc * 4 + 2] = bf16_lo(w.y);
-                    S[j][pc * 4 + 3] = bf16_hi(w.y);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int c = 0; c < NP * 4; ++c) S[j][c] = 0.f;
-        }
-        if (T.ntok > 0) {
-#pragma unroll
-            for (int pc = 0; pc < NP; ++pc) {
-                kw[pc] = *reinterpret_cast<const uint2*>(st + Stage::kOffK + (pc * 64 + l16 * 4) * 2);
-                qw[pc] = *reinterpret_cast<const uint2*>(st + Stage::kOffQ + (pc * 64 + l16 * 4) * 2);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                vr[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st + Stage::kOffV)[warp * 8 + 2 * j + half]);
-        }
-        __syncthreads();  // every thread has read this stage: it may be refilled
+        for (int rb = 0; rb < rblocks; ++rb, ++it) {
+            const int stage = it % kRecStages;
+            const uint32_t parity = static_cast<uint32_t>((it / kRecStages) & 1);
+            if (tid == 0) produce_one();  // refills the stage consumed in the previous iteration
 
-        // ---- token loop (inputs of token t+1 are fetched from global while token t is computed)
-        float beta_t = beta_first, g_t = g_first;
-        auto load_token = [&](int t, uint2* kk, uint2* qq, float* vv, float& bt, float& gt) {
-            const long long tok = T.tok0 + t;
-            const __nv_bfloat16* kp = p.k + T.bidx * p.k_sb + tok * p.k_st + T.khead * p.k_sh;
-            const __nv_bfloat16* qp = p.q + T.bidx * p.q_sb + tok * p.q_st + T.khead * p.q_sh;
-#pragma unroll
-            for (int pc = 0; pc < NP; ++pc) {
-                kk[pc] = __ldg(reinterpret_cast<const uint2*>(kp + pc * 64 + l16 * 4));
-                qq[pc] = __ldg(reinterpret_cast<const uint2*>(qp + pc * 64 + l16 * 4));
-            }
-            const __nv_bfloat16* vp = p.v + T.bidx * p.v_sb + tok * p.v_st + T.head * p.v_sh + T.rb * kRecTileRows;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) vv[j] = __bfloat162float(vp[warp * 8 + 2 * j + half]);
-            load_scalars(T, t, bt, gt);
-        };
-
-        for (int t = 0; t < T.ntok; ++t) {
-            float kc[NP * 4], qc[NP * 4];
-#pragma unroll
-            for (int pc = 0; pc < NP; ++pc) {
-                kc[pc * 4 + 0] = bf16_lo(kw[pc].x); kc[pc * 4 + 1] = bf16_hi(kw[pc].x);
-                kc[pc * 4 + 2] = bf16_lo(kw[pc].y); kc[pc * 4 + 3] = bf16_hi(kw[pc].y);
-                qc[pc * 4 + 0] = bf16_lo(qw[pc].x); qc[pc * 4 + 1] = bf16_hi(qw[pc].x);
-                qc[pc * 4 + 2] = bf16_lo(qw[pc].y); qc[pc * 4 + 3] = bf16_hi(qw[pc].y);
-            }
-            uint2 kn[NP], qn[NP];
-            float vn[4], beta_n = 0.f, g_n = 0.f;
-            if (t + 1 < T.ntok) load_token(t + 1, kn, qn, vn, beta_n, g_n);
-
-            float kq = 0.f;
-            if (p.is_qk_norm) {
-                float sk = 0.f, sq = 0.f;
-#pragma unroll
-                for (int c = 0; c < NP * 4; ++c) {
-                    sk = fmaf(kc[c], kc[c], sk);
-                    sq = fmaf(qc[c], qc[c], sq);
-                }
-#pragma unroll
-                for (int m = 1; m < 16; m <<= 1) {
-                    sk += __shfl_xor_sync(0xffffffffu, sk, m);
-                    sq += __shfl_xor_sync(0xffffffffu, sq, m);
-                }
-                const float inv_k = rsqrtf(sk + 1e-6f);
-                const float inv_q = rsqrtf(sq + 1e-6f);
-#pragma unroll
-                for (int c = 0; c < NP * 4; ++c) {
-                    kc[c] *= inv_k;
-                    qc[c] *= inv_q;
-                }
-            }
-            float dk_[4], dq_[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                dk_[j] = 0.f;
-                dq_[j] = 0.f;
-            }
-#pragma unroll
-            for (int c = 0; c < NP * 4; ++c) {
-                kq = fmaf(kc[c], qc[c], kq);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    dk_[j] = fmaf(S[j][c], kc[c], dk_[j]);
-                    dq_[j] = fmaf(S[j][c], qc[c], dq_[j]);
-                }
-            }
-#pragma unroll
-            for (int m = 1; m < 16; m <<= 1) {
-                kq += __shfl_xor_sync(0xffffffffu, kq, m);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    dk_[j] += __shfl_xor_sync(0xffffffffu, dk_[j], m);
-                    dq_[j] += __shfl_xor_sync(0xffffffffu, dq_[j], m);
-                }
-            }
-            const float eg = __expf(g_t);
-            float o_mine = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float r = vr[j] - eg * dk_[j];
-                const float br = beta_t * r;
-                const float o = p.scale * fmaf(eg, dq_[j], br * kq);
-                if (l16 == j) o_mine = o;
-#pragma unroll
-                for (int c = 0; c < NP * 4; ++c) S[j][c] = fmaf(eg, S[j][c], br * kc[c]);
-            }
-            const long long tok = T.tok0 + t;
-            if (l16 < 4) {
-                __nv_bfloat16* op = p.out + T.bidx * p.o_sb + tok * p.o_st + T.head * p.o_sh + T.rb * kRecTileRows;
-                op[warp * 8 + 2 * l16 + half] = __float2bfloat16(o_mine);
-            }
-            if (p.store_step) {
-                const long long sidx = p.cu_seqlens ? tok : (static_cast<long long>(T.seq) * p.seq_len + t);
-                __nv_bfloat16* sp = p.state_out + sidx * p.so_ss + T.head * p.so_sh +
-                                    static_cast<long long>(T.rb) * kRecTileRows * DK;
+            // ---- staged data -> registers
+            f2 S[4][NQ];
+            float vr[4];
+            mbar_wait(&full[stage], parity, &abort_flag);
+            const uint8_t* st = smem + stage * Stage::kBytes;
+            if (has_in) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int row = warp * 8 + 2 * j + half;
 #pragma unroll
-                    for (int pc = 0; pc < NP; ++pc) {
-                        uint2 w;
-                        w.x = pack_bf16(S[j][pc * 4 + 0], S[j][pc * 4 + 1]);
-                        w.y = pack_bf16(S[j][pc * 4 + 2], S[j][pc * 4 + 3]);
-                        *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                    for (int pc = 0; pc < NQ / 2; ++pc) {
+                        const uint2 w = *reinterpret_cast<const uint2*>(st + (row * DK + pc * 64 + l16 * 4) * 2);
+                        S[j][2 * pc] = bf2_to_f2(w.x);
+                        S[j][2 * pc + 1] = bf2_to_f2(w.y);
                     }
                 }
-            }
+            } else {
 #pragma unroll
-            for (int pc = 0; pc < NP; ++pc) {
-                kw[pc] = kn[pc];
-                qw[pc] = qn[pc];
-            }
+                for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) vr[j] = vn[j];
-            beta_t = beta_n;
-            g_t = g_n;
-        }
+                    for (int c = 0; c < NQ; ++c) S[j][c] = 0ull;
+            }
+            const bool fresh_qk = (rb == 0) || (T.ntok > 1);
+            uint2 kw[NQ / 2], qw[NQ / 2];
+            if (T.ntok > 0) {
+                if (fresh_qk) {
+#pragma unroll
+                    for (int pc = 0; pc < NQ / 2; ++pc) {
+                        kw[pc] = *reinterpret_cast<const uint2*>(st + Stage::kOffK + (pc * 64 + l16 * 4) * 2);
+                        qw[pc] = *reinterpret_cast<const uint2*>(st + Stage::kOffQ + (pc * 64 + l16 * 4) * 2);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    vr[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st + Stage::kOffV)[warp * 8 + 2 * j + half]);
+            }
+            __syncthreads();  // every thread has read this stage: it may be refilled
 
-        if (!p.store_step) {
-            __nv_bfloat16* sp = p.state_out + static_cast<long long>(T.seq) * p.so_ss + T.head * p.so_sh +
-                                static_cast<long long>(T.rb) * kRecTileRows * DK;
+            // ---- token loop (inputs of token t+1 are fetched from global while token t is computed)
+            float beta_t = beta_first, g_t = g_first;
+            auto load_token = [&](int t, uint2* kk, uint2* qq, float* vv, float& bt, float& gt) {
+                const long long tok = T.tok0 + t;
+                const __nv_bfloat16* kp = p.k + T.bidx * p.k_sb + tok * p.k_st + T.khead * p.k_sh;
+                const __nv_bfloat16* qp = p.q + T.bidx * p.q_sb + tok * p.q_st + T.khead * p.q_sh;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int row = warp * 8 + 2 * j + half;
+                for (int pc = 0; pc < NQ / 2; ++pc) {
+                    kk[pc] = __ldg(reinterpret_cast<const uint2*>(kp + pc * 64 + l16 * 4));
+                    qq[pc] = __ldg(reinterpret_cast<const uint2*>(qp + pc * 64 + l16 * 4));
+                }
+                const __nv_bfloat16* vp = p.v + T.bidx * p.v_sb + tok * p.v_st + T.head * p.v_sh + rb * kRecTileRows;
 #pragma unroll
-                for (int pc = 0; pc < NP; ++pc) {
-                    uint2 w;
-                    w.x = pack_bf16(S[j][pc * 4 + 0], S[j][pc * 4 + 1]);
-                    w.y = pack_bf16(S[j][pc * 4 + 2], S[j][pc * 4 + 3]);
-                    *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                for (int j = 0; j < 4; ++j) vv[j] = __bfloat162float(vp[warp * 8 + 2 * j + half]);
+                load_scalars(T, t, bt, gt);
+            };
+
+            for (int t = 0; t < T.ntok; ++t) {
+                uint2 kn[NQ / 2], qn[NQ / 2];
+                float vn[4], beta_n = 0.f, g_n = 0.f;
+                if (t + 1 < T.ntok) load_token(t + 1, kn, qn, vn, beta_n, g_n);
+
+                if (t > 0 || fresh_qk) {
+                    // unpack, optional L2 normalisation, k.q
+#pragma unroll
+                    for (int pc = 0; pc < NQ / 2; ++pc) {
+                        k2[2 * pc] = bf2_to_f2(kw[pc].x);
+                        k2[2 * pc + 1] = bf2_to_f2(kw[pc].y);
+                        q2[2 * pc] = bf2_to_f2(qw[pc].x);
+                        q2[2 * pc + 1] = bf2_to_f2(qw[pc].y);
+                    }
+                    f2 akk = 0ull, aqq = 0ull, akq = 0ull;
+#pragma unroll
+                    for (int c = 0; c < NQ; ++c) {
+                        akk = fma2(k2[c], k2[c], akk);
+                        aqq = fma2(q2[c], q2[c], aqq);
+                        akq = fma2(k2[c], q2[c], akq);
+                    }
+                    float skk = hsum(akk), sqq = hsum(aqq), skq = hsum(akq);
+#pragma unroll
+                    for (int m = 1; m < 16; m <<= 1) {
+                        skk += __shfl_xor_sync(0xffffffffu, skk, m);
+                        sqq += __shfl_xor_sync(0xffffffffu, sqq, m);
+                        skq += __shfl_xor_sync(0xffffffffu, skq, m);
+                    }
+                    kq = skq;
+                    if (p.is_qk_norm) {
+                        const float inv_k = rsqrtf(skk + 1e-6f), inv_q = rsqrtf(sqq + 1e-6f);
+                        const f2 ik2 = pk(inv_k, inv_k), iq2 = pk(inv_q, inv_q);
+#pragma unroll
+                        for (int c = 0; c < NQ; ++c) {
+                            k2[c] = mul2(k2[c], ik2);
+                            q2[c] = mul2(q2[c], iq2);
+                        }
+                        kq = skq * inv_k * inv_q;
+                    }
+                }
+                // ---- S.k and S.q for the thread's 4 rows
+                f2 ak[4], aq[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ak[j] = 0ull;
+                    aq[j] = 0ull;
+                }
+#pragma unroll
+                for (int c = 0; c < NQ; ++c) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        ak[j] = fma2(S[j][c], k2[c], ak[j]);
+                        aq[j] = fma2(S[j][c], q2[c], aq[j]);
+                    }
+                }
+                // transposing butterfly over the 16 lanes of a row: 8 values -> lane l16 holds
+                // the full sum of value (l16 >> 1): S.k of row j on lanes 2j, 2j+1; S.q on 8+2j, 8+2j+1
+                float v8[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v8[j] = hsum(ak[j]);
+                    v8[4 + j] = hsum(aq[j]);
+                }
+                float v4[4], v2[2], v1;
+                {
+                    const bool up = (l16 & 8) != 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float send = up ? v8[i] : v8[4 + i];
+                        const float keep = up ? v8[4 + i] : v8[i];
+                        v4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                }
+                {
+                    const bool up = (l16 & 4) != 0;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float send = up ? v4[i] : v4[2 + i];
+                        const float keep = up ? v4[2 + i] : v4[i];
+                        v2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                }
+                {
+                    const bool up = (l16 & 2) != 0;
+                    const float send = up ? v2[0] : v2[1];
+                    const float keep = up ? v2[1] : v2[0];
+                    v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+                }
+                v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+
+                const float eg = __expf(g_t);
+                const f2 eg2 = pk(eg, eg);
+                const int base = lane & 16;
+                float o_mine = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float dkj = __shfl_sync(0xffffffffu, v1, base + 2 * j);
+                    const float r = vr[j] - eg * dkj;
+                    const float br = beta_t * r;
+                    if (l16 == 8 + 2 * j) o_mine = p.scale * fmaf(eg, v1, br * kq);
+                    const f2 br2 = pk(br, br);
+#pragma unroll
+                    for (int c = 0; c < NQ; ++c) S[j][c] = fma2(eg2, S[j][c], mul2(br2, k2[c]));
+                }
+                const long long tok = T.tok0 + t;
+                if (l16 >= 8 && (l16 & 1) == 0) {
+                    __nv_bfloat16* op = p.out + T.bidx * p.o_sb + tok * p.o_st + T.head * p.o_sh + rb * kRecTileRows;
+                    op[warp * 8 + (l16 - 8) + half] = __float2bfloat16(o_mine);
+                }
+                if (p.store_step) {
+                    const long long sidx = p.cu_seqlens ? tok : (static_cast<long long>(T.seq) * p.seq_len + t);
+                    __nv_bfloat16* sp = p.state_out + sidx * p.so_ss + T.head * p.so_sh +
+                                        static_cast<long long>(rb) * kRecTileRows * DK;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int row = warp * 8 + 2 * j + half;
+#pragma unroll
+                        for (int pc = 0; pc < NQ / 2; ++pc) {
+                            float a0, a1, a2, a3;
+                            unpk(S[j][2 * pc], a0, a1);
+                            unpk(S[j][2 * pc + 1], a2, a3);
+                            uint2 w;
+                            w.x = pack_bf16(a0, a1);
+                            w.y = pack_bf16(a2, a3);
+                            *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int pc = 0; pc < NQ / 2; ++pc) {
+                    kw[pc] = kn[pc];
+                    qw[pc] = qn[pc];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) vr[j] = vn[j];
+                beta_t = beta_n;
+                g_t = g_n;
+            }
+
+            if (!p.store_step) {
+                __nv_bfloat16* sp = p.state_out + static_cast<long long>(T.seq) * p.so_ss + T.head * p.so_sh +
+                                    static_cast<long long>(rb) * kRecTileRows * DK;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int row = warp * 8 + 2 * j + half;
+#pragma unroll
+                    for (int pc = 0; pc < NQ / 2; ++pc) {
+                        float a0, a1, a2, a3;
+                        unpk(S[j][2 * pc], a0, a1);
+                        unpk(S[j][2 * pc + 1], a2, a3);
+                        uint2 w;
+                        w.x = pack_bf16(a0, a1);
+                        w.y = pack_bf16(a2, a3);
+                        *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                    }
                 }
             }
         }
