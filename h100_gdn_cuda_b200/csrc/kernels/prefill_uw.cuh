@@ -5,14 +5,21 @@
 // sm90_bf16_compute_u_w (gdn_cuda/include/gdn_cuda/kernels/sm90_bf16_gdn_compute_u_w.cuh:153-667),
 // using the canonical W (gate folded in before the solve).
 //
-// One CTA of 128 threads per unit; tcgen05 tensor cores do the three contractions:
-//   K K^T      : M=64 N=64 K=D, both operands the same K-major shared-memory tile (TMA, 128B swizzle)
-//   U = T V    : M=64 N=D  K=64, A = T (bf16, written by the CTA), B = the V tile read MN-major
-//   W = T' K   : M=64 N=D  K=64, A = T' = X diag(beta e^g), B = the K tile read MN-major
-// so neither K nor V is ever rescaled or copied.  The unit-lower-triangular inverse is done
-// in fp32 on CUDA cores: 16x16 diagonal blocks by forward substitution (one column per
-// thread), then three levels of 16x16 block products.
-// Accumulators live in tensor memory (2*D columns); the raw K K^T block shares columns with U.
+// One CTA of 128 threads per unit, three CTAs per SM.  tcgen05 tensor cores do the three
+// big contractions with the TMA-loaded tiles used as they are:
+//   K K^T      : two M=64 N=32 K=D MMAs (columns 0-31 and 32-63 of the result) whose
+//                accumulators are interleaved in the same tensor-memory columns (lanes +0 and
+//                +16 of every 32-lane quarter), so one 32-lane load hands every thread of a
+//                warp half a row;
+//   U = T V    : M=64 N=D K=64, A = T (bf16, written by the CTA), B = the V tile read MN-major;
+//   W = T' K   : M=64 N=D K=64, A = T' = X diag(beta e^g), B = the K tile read MN-major;
+//                U and W are interleaved the same way (U in lanes +0, W in lanes +16).
+// The unit-lower-triangular inverse runs in fp32 accuracy: the 16x16 diagonal blocks by
+// forward substitution (one column per thread), then two levels of recursive doubling
+// (16 -> 32 -> 64) whose block products use warp-level tensor-core MMAs on TF32 operands
+// split into a high and a low part (three MMAs per product, error ~2^-21).
+// Tensor memory: D columns.  Shared memory: K and V tiles (later the U/W staging), A (later
+// T and T'), X, and a small scratch: about 73 KB.
 #pragma once
 #include <cuda.h>
 
@@ -32,41 +39,88 @@ struct UWParams {
 
 template <int D>
 struct UWSmem {
-    static constexpr int kTile = kChunk * D * 2;          // K or V tile
+    static constexpr int kTile = kChunk * D * 2;  // K or V tile; later the U / W staging tile
+    static constexpr int kLdA = 68;               // fp32 row strides chosen for conflict-free
+    static constexpr int kLdX = 68;               //   MMA fragment loads
+    static constexpr int kLdT = 40;
     static constexpr int kOffK = 0;
     static constexpr int kOffV = kOffK + kTile;
-    static constexpr int kOffT = kOffV + kTile;           // T  (64x64 bf16, K-major SW128)
-    static constexpr int kOffT2 = kOffT + 8192;           // T' (same layout)
-    static constexpr int kOffA = kOffT2 + 8192;           // A, fp32 [64][65]; later U staging
-    static constexpr int kOffX = kOffA + 64 * 65 * 4 + 64; // X, fp32 [64][65]; later W staging
-    static constexpr int kOffTmp = kOffX + 64 * 65 * 4 + 64;
-    static constexpr int kOffVec = kOffTmp + 3 * 256 * 4;  // beta[64], g[64], e^g[64]
-    static constexpr int kBytes = kOffVec + 3 * 64 * 4 + 1024;  // + alignment slack
-    static_assert(64 * 65 * 4 + 64 >= kTile || D > 128, "staging must fit");
+    static constexpr int kOffA = kOffV + kTile;          // A fp32 [64][68]; later T and T' (8 KB each)
+    static constexpr int kOffX = kOffA + 64 * kLdA * 4;  // X fp32 [64][68]
+    static constexpr int kOffTmp = kOffX + 64 * kLdX * 4;  // fp32 [32][40]
+    static constexpr int kOffVec = kOffTmp + 32 * kLdT * 4;  // beta[64], g[64], e^g[64]
+    static constexpr int kOffBar = kOffVec + 3 * 64 * 4;     // 2 mbarriers, tmem slot, abort flag
+    static constexpr int kBytes = kOffBar + 64 + 1024;       // + alignment slack
+    static_assert(64 * kLdA * 4 >= 2 * 8192, "T and T' must fit over A");
+    static_assert(kOffA % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
+namespace uw {
+// fp32 -> (hi, lo) TF32 parts
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float r = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+__device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// d(16x8) += A(16x8 at [r0][k0] of `am`) * B(8x8 at [k0b][n0] of `bm`), fp32-accurate
+__device__ __forceinline__ void mma_block(float* d, const float* am, int lda, int r0, int k0, const float* bm,
+                                          int ldb, int k0b, int n0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    float af[4], bf[2];
+    af[0] = am[(r0 + g) * lda + k0 + t];
+    af[1] = am[(r0 + g + 8) * lda + k0 + t];
+    af[2] = am[(r0 + g) * lda + k0 + t + 4];
+    af[3] = am[(r0 + g + 8) * lda + k0 + t + 4];
+    bf[0] = bm[(k0b + t) * ldb + n0 + g];
+    bf[1] = bm[(k0b + t + 4) * ldb + n0 + g];
+    uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) split_tf32(af[i], ah[i], al[i]);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) split_tf32(bf[i], bh[i], bl[i]);
+    mma_tf32(d, al, bh);
+    mma_tf32(d, ah, bl);
+    mma_tf32(d, ah, bh);
+}
+// store -d (16x8) at [r0][n0]
+__device__ __forceinline__ void store_block(const float* d, float sign, float* m, int ld, int r0, int n0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    *reinterpret_cast<float2*>(&m[(r0 + g) * ld + n0 + 2 * t]) = make_float2(sign * d[0], sign * d[1]);
+    *reinterpret_cast<float2*>(&m[(r0 + g + 8) * ld + n0 + 2 * t]) = make_float2(sign * d[2], sign * d[3]);
+}
+}  // namespace uw
+
 template <int D>
-__global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
-                                                     const __grid_constant__ CUtensorMap tmV,
-                                                     const UWParams p) {
+__global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                        const __grid_constant__ CUtensorMap tmV,
+                                                        const UWParams p) {
     using namespace ptx;
+    using namespace uw;
     using L = UWSmem<D>;
     constexpr int NA = D / 64;  // 64-column swizzle atoms per tile
+    constexpr int LDA = L::kLdA, LDX = L::kLdX, LDT = L::kLdT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem + L::kOffK;
     uint8_t* sV = smem + L::kOffV;
-    uint8_t* sT = smem + L::kOffT;
-    uint8_t* sT2 = smem + L::kOffT2;
-    float(*sA)[65] = reinterpret_cast<float(*)[65]>(smem + L::kOffA);
-    float(*sX)[65] = reinterpret_cast<float(*)[65]>(smem + L::kOffX);
+    uint8_t* sT = smem + L::kOffA;
+    uint8_t* sT2 = sT + 8192;
+    float* sA = reinterpret_cast<float*>(smem + L::kOffA);
+    float* sX = reinterpret_cast<float*>(smem + L::kOffX);
     float* sTmp = reinterpret_cast<float*>(smem + L::kOffTmp);
     float* sBeta = reinterpret_cast<float*>(smem + L::kOffVec);
     float* sG = sBeta + 64;
     float* sEg = sG + 64;
-    __shared__ uint64_t bar_load, bar_mma;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_flag;
+    uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+    uint64_t* bar_mma = bar_load + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_load + 2);
+    int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int head = blockIdx.y;
@@ -75,26 +129,26 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
     const int n = cp.n;
 
     if (tid == 0) {
-        abort_flag = 0;
-        mbar_init(&bar_load, 1);
-        mbar_init(&bar_mma, 1);
+        *abort_flag = 0;
+        mbar_init(bar_load, 1);
+        mbar_init(bar_mma, 1);
         mbar_fence_init();
     }
-    if (warp == 0) tmem_alloc(&tmem_slot, 2 * D);
+    if (warp == 0) tmem_alloc(tmem_slot, D);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem = tmem_slot;
-    const uint32_t tU = tmem, tW = tmem + D;
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tLo = tmem, tHi = tmem + (16u << 16);  // the two interleaved M=64 accumulators
 
     if (tid == 0) {
-        mbar_arrive_expect_tx(&bar_load, 2 * L::kTile);
+        mbar_arrive_expect_tx(bar_load, 2 * L::kTile);
         for (int a = 0; a < NA; ++a) {
-            tma_load_4d(sK + a * 8192, &tmK, &bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
-            tma_load_4d(sV + a * 8192, &tmV, &bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+            tma_load_4d(sK + a * 8192, &tmK, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
+            tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
         }
     }
-    // beta and gate of the chunk's tokens (rows past the end: beta = 0, g = g of the last row)
+    // beta and the chunk-local cumulative gate (rows past the end: beta = 0, g = g of the last row)
     if (tid < 64) {
         float b = 0.f, g = 0.f;
         if (tid < n) {
@@ -102,66 +156,79 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
             if (p.gate.ptr) g = p.gate.load(cp.batch, cp.tok0 + tid, head);
         }
         sBeta[tid] = b;
-        sEg[tid] = g;  // raw values; replaced by exp(g) below
-    }
-    __syncthreads();
-    if (tid < 64) {
-        float g = 0.f;
-        if (p.gate.ptr) {
-            const int last = tid < n ? tid : n - 1;
-            if (p.gate_is_raw) {
-                for (int m = 0; m <= last; ++m) g += sEg[m];
-            } else {
-                g = sEg[last];
+        if (p.gate_is_raw) {
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const float y = __shfl_up_sync(0xffffffffu, g, m);
+                if (lane >= m) g += y;
             }
         }
         sG[tid] = g;
     }
+    // X starts as zero (blocks above the diagonal are read by the block products)
+    for (int idx = tid; idx < 64 * LDX / 4; idx += 128) reinterpret_cast<float4*>(sX)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
-    if (tid < 64) sEg[tid] = __expf(sG[tid]);
+    if (tid < 64) {
+        float g = sG[tid];
+        if (p.gate_is_raw) {
+            if (tid >= 32) g += sG[31];
+        } else if (tid >= n) {
+            g = sG[n - 1];
+        }
+        sEg[tid] = g;  // final g, parked here until every thread has read the partial sums
+    }
+    __syncthreads();
+    if (tid < 64) {
+        const float g = sEg[tid];
+        sG[tid] = g;
+        sEg[tid] = __expf(g);
+    }
     __syncthreads();
 
-    // ---- A_raw = K K^T
-    mbar_wait(&bar_load, 0, &abort_flag);
+    // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
+    mbar_wait(bar_load, 0, abort_flag);
     if (tid == 0) {
         tc_fence_after_sync();
-        constexpr uint32_t idesc = make_idesc_bf16(64, 64, false, false);
+        constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t d = make_smem_desc_sw128(smem_u32(sK) + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024);
-            mma_ss(tU, d, d, idesc, ks > 0);
+            const uint32_t off = (ks / 4) * 8192 + (ks % 4) * 32;
+            const uint64_t a = make_smem_desc_sw128(smem_u32(sK) + off, 0, 1024);
+            const uint64_t b0 = a;
+            const uint64_t b1 = make_smem_desc_sw128(smem_u32(sK) + off + 32 * 128, 0, 1024);
+            mma_ss(tLo, a, b0, idesc, ks > 0);
+            mma_ss(tHi, a, b1, idesc, ks > 0);
         }
-        mma_commit(&bar_mma);
+        mma_commit(bar_mma);
     }
     __syncwarp();
-    mbar_wait(&bar_mma, 0, &abort_flag);
+    mbar_wait(bar_mma, 0, abort_flag);
     tc_fence_after_sync();
     {
-        // M=64 accumulator: row 16*warp + l sits in lane 32*warp + l for l < 16
+        // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63
         const int i = 16 * warp + (lane & 15);
+        const int cbase = (lane >> 4) * 32;
         const float bi = sBeta[i], gi = sG[i];
+        uint32_t r[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(tU + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
-            tmem_wait_ld();
-            if (lane < 16) {
+        for (int j = 0; j < 32; j += 4) {
+            float a[4];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int col = c0 + j;
-                    float a = 0.f;
-                    if (col < i && i < n) a = bi * __uint_as_float(r[j]) * __expf(gi - sG[col]);
-                    sA[i][col] = a;
-                }
+            for (int e = 0; e < 4; ++e) {
+                const int col = cbase + j + e;
+                a[e] = (col < i && i < n) ? bi * __uint_as_float(r[j + e]) * __expf(gi - sG[col]) : 0.f;
             }
+            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
         }
     }
     tc_fence_before_sync();
     __syncthreads();
 
     // ---- X = (I + A)^-1 : diagonal 16x16 blocks, one column per thread
-    if (tid < 64) {
-        const int b = tid >> 4, j = tid & 15;
+    if (lane < 16) {
+        const int b = warp, j = lane;
         float x[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = (i == j) ? 1.f : 0.f;
@@ -169,54 +236,67 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
         for (int i = 1; i < 16; ++i) {
             float acc = 0.f;
 #pragma unroll
-            for (int m = 0; m < i; ++m) acc = fmaf(sA[16 * b + i][16 * b + m], x[m], acc);
+            for (int m = 0; m < i; ++m) acc = fmaf(sA[(16 * b + i) * LDA + 16 * b + m], x[m], acc);
             if (i > j) x[i] = -acc;
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) sX[16 * b + i][16 * b + j] = x[i];
+        for (int i = 0; i < 16; ++i) sX[(16 * b + i) * LDX + 16 * b + j] = x[i];
     }
     __syncthreads();
-    // off-diagonal blocks, level by level: X_ij = -X_ii * sum_{m=j}^{i-1} A_im X_mj
-#pragma unroll 1
-    for (int lvl = 1; lvl <= 3; ++lvl) {
-        const int nblk = 4 - lvl;
-        for (int idx = tid; idx < nblk * 256; idx += 128) {
-            const int bi = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
-            const int i = bi + lvl, j = bi;
-            const float* arow = &sA[16 * i + rr][0];
-            float acc = 0.f;
-            for (int kk = 16 * j; kk < 16 * i; ++kk) acc = fmaf(arow[kk], sX[kk][16 * j + cc], acc);
-            sTmp[idx] = acc;
-        }
+    // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half)
+    {
+        const int pr = warp >> 1, n0 = 8 * (warp & 1);
+        const int i0 = 16 * (2 * pr + 1), j0 = 16 * (2 * pr);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) mma_block(d, sA, LDA, i0, j0 + 8 * ks, sX, LDX, j0 + 8 * ks, j0 + n0, lane);
+        store_block(d, 1.f, sTmp, LDT, 16 * pr, n0, lane);
         __syncthreads();
-        for (int idx = tid; idx < nblk * 256; idx += 128) {
-            const int bi = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
-            const int i = bi + lvl, j = bi;
-            float acc = 0.f;
-            for (int m = 0; m <= rr; ++m) acc = fmaf(sX[16 * i + rr][16 * i + m], sTmp[(bi << 8) + (m << 4) + cc], acc);
-            sX[16 * i + rr][16 * j + cc] = -acc;
-        }
-        __syncthreads();
+        float e[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) mma_block(e, sX, LDX, i0, i0 + 8 * ks, sTmp, LDT, 16 * pr + 8 * ks, n0, lane);
+        __syncthreads();  // everyone is done with this level's scratch
+        store_block(e, -1.f, sX, LDX, i0, j0 + n0, lane);
     }
+    __syncthreads();
+    // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result
+    {
+        const int rb = warp >> 1, cb = warp & 1;
+        float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+                mma_block(d[nt], sA, LDA, 32 + 16 * rb, 8 * ks, sX, LDX, 8 * ks, 16 * cb + 8 * nt, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) store_block(d[nt], 1.f, sTmp, LDT, 16 * rb, 16 * cb + 8 * nt, lane);
+        __syncthreads();
+        float e[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+                mma_block(e[nt], sX, LDX, 32 + 16 * rb, 32 + 8 * ks, sTmp, LDT, 8 * ks, 16 * cb + 8 * nt, lane);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) store_block(e[nt], -1.f, sX, LDX, 32 + 16 * rb, 16 * cb + 8 * nt, lane);
+    }
+    __syncthreads();
 
-    // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles
+    // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles (over A)
     {
         const int i = tid >> 1, c0 = (tid & 1) * 32;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
+            const float4 xa = *reinterpret_cast<const float4*>(&sX[i * LDX + c0 + ch * 8]);
+            const float4 xb = *reinterpret_cast<const float4*>(&sX[i * LDX + c0 + ch * 8 + 4]);
+            const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
             uint32_t t1[4], t2[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v0[2], v1[2];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int j = c0 + ch * 8 + e * 2 + q;
-                    const float x = ((j >> 4) <= (i >> 4)) ? sX[i][j] : 0.f;  // blocks above the diagonal are zero
-                    v0[q] = x * sBeta[j];
-                    v1[q] = v0[q] * sEg[j];
-                }
-                t1[e] = pack_bf16(v0[0], v0[1]);
-                t2[e] = pack_bf16(v1[0], v1[1]);
+                const int j = c0 + ch * 8 + e * 2;
+                const float v0 = xs[2 * e] * sBeta[j], v1 = xs[2 * e + 1] * sBeta[j + 1];
+                t1[e] = pack_bf16(v0, v1);
+                t2[e] = pack_bf16(v0 * sEg[j], v1 * sEg[j + 1]);
             }
             const uint32_t off = sw128_offset(i, c0 + ch * 8);
             *reinterpret_cast<uint4*>(sT + off) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
@@ -226,7 +306,7 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
     fence_proxy_async_smem();
     __syncthreads();
 
-    // ---- U = T V, W = T' K
+    // ---- U = T V (lanes +0), W = T' K (lanes +16)
     if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
@@ -234,47 +314,39 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
         for (int ks = 0; ks < 4; ++ks) {
             const uint64_t a1 = make_smem_desc_sw128(smem_u32(sT) + ks * 32, 0, 1024);
             const uint64_t b1 = make_smem_desc_sw128(smem_u32(sV) + ks * 2048, 8192, 1024);
-            mma_ss(tU, a1, b1, idesc, ks > 0);
+            mma_ss(tLo, a1, b1, idesc, ks > 0);
         }
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
             const uint64_t a2 = make_smem_desc_sw128(smem_u32(sT2) + ks * 32, 0, 1024);
             const uint64_t b2 = make_smem_desc_sw128(smem_u32(sK) + ks * 2048, 8192, 1024);
-            mma_ss(tW, a2, b2, idesc, ks > 0);
+            mma_ss(tHi, a2, b2, idesc, ks > 0);
         }
-        mma_commit(&bar_mma);
+        mma_commit(bar_mma);
     }
     __syncwarp();
-    mbar_wait(&bar_mma, 1, &abort_flag);
+    mbar_wait(bar_mma, 1, abort_flag);
     tc_fence_after_sync();
 
-    // ---- accumulators -> bf16 -> staged tiles -> coalesced stores
-    uint8_t* stU = smem + L::kOffA;
-    uint8_t* stW = smem + L::kOffX;
+    // ---- accumulators -> bf16 -> staged tiles (over the K and V tiles) -> coalesced stores
+    uint8_t* stU = sK;
+    uint8_t* stW = sV;
     {
         const int i = 16 * warp + (lane & 15);
+        uint8_t* stg = (lane < 16) ? stU : stW;
 #pragma unroll
-        for (int which = 0; which < 2; ++which) {
-            const uint32_t tacc = which ? tW : tU;
-            uint8_t* stg = which ? stW : stU;
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
+            tmem_wait_ld();
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 16) {
-                uint32_t r[16];
-                tmem_ld16(tacc + (static_cast<uint32_t>(warp * 32) << 16) + c0, r);
-                tmem_wait_ld();
-                if (lane < 16) {
-                    uint4 lo, hi;
-                    lo.x = pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1]));
-                    lo.y = pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3]));
-                    lo.z = pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5]));
-                    lo.w = pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7]));
-                    hi.x = pack_bf16(__uint_as_float(r[8]), __uint_as_float(r[9]));
-                    hi.y = pack_bf16(__uint_as_float(r[10]), __uint_as_float(r[11]));
-                    hi.z = pack_bf16(__uint_as_float(r[12]), __uint_as_float(r[13]));
-                    hi.w = pack_bf16(__uint_as_float(r[14]), __uint_as_float(r[15]));
-                    *reinterpret_cast<uint4*>(stg + stage_off<D>(i, c0 / 8)) = lo;
-                    *reinterpret_cast<uint4*>(stg + stage_off<D>(i, c0 / 8 + 1)) = hi;
-                }
+            for (int q = 0; q < 4; ++q) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                v.y = pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                v.z = pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                v.w = pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                *reinterpret_cast<uint4*>(stg + stage_off<D>(i, c0 / 8 + q)) = v;
             }
         }
     }
@@ -282,8 +354,8 @@ __global__ void __launch_bounds__(128) gdn_uw_kernel(const __grid_constant__ CUt
     __syncthreads();
     store_staged_tile<D, 128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
     store_staged_tile<D, 128>(stW, p.w, cp.batch, cp.tok0, head, n, tid);
-    if (warp == 0) tmem_dealloc(tmem, 2 * D);
-    if (tid == 0 && abort_flag && p.status) atomicExch(p.status, 2);
+    if (warp == 0) tmem_dealloc(tmem, D);
+    if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
 }
 
 }  // namespace gdn
