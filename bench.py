@@ -261,7 +261,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    ws = torch.empty(2 * tokens * vh * d * 2 + 256, dtype=torch.uint8, device=dev)
+    from h100_gdn_cuda_b200 import api as gdn_api
+    ws = torch.empty(gdn_api.chunked_forward_workspace_bytes(B, T, vh), dtype=torch.uint8, device=dev)
     stage_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     for e in stage_ev:
         e.record()

@@ -254,6 +254,14 @@ def _check_head_dim(d: int):
     _require(0 < d <= _PREFILL_D, "chunked kernels support head dims up to %d (got %d)" % (_PREFILL_D, d))
 
 
+def chunked_forward_workspace_bytes(batch: int, seq_len: int, num_v_heads: int, total_tokens: int = 0,
+                                    total_chunks: int = 0, packed: bool = False) -> int:
+    """Bytes of scratch `chunked_forward` needs for a problem of this size (head dim 128)."""
+    shape = cabi.Shape(batch, seq_len, total_tokens if packed else batch * seq_len, 1, num_v_heads, _PREFILL_D,
+                       _PREFILL_D, 1 if packed else None, None, None, total_chunks)
+    return int(cabi.load().gdn_chunked_forward_workspace_bytes(C.byref(shape)))
+
+
 def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None, initial_state=None,
                     cu_seqlens=None, chunk_indices=None, cu_chunks=None, total_chunks: Optional[int] = None,
                     *, _stage_events=None, _workspace=None):

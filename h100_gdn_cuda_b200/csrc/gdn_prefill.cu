@@ -1,6 +1,7 @@
 // C-ABI entry points of the chunked-prefill path (see include/gdn_b200.h): tensor-map
 // construction, argument checks and launches of the tcgen05 kernels.
 #include "host_common.hpp"
+#include "kernels/prefill_fused.cuh"
 #include "kernels/prefill_seq.cuh"
 #include "kernels/prefill_uw.cuh"
 #include "tma_host.hpp"
@@ -84,13 +85,18 @@ int set_smem(K kernel, int bytes) {
 
 int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& v, const GdnTokenTensor& u,
               const GdnTokenTensor& w, const GdnTokenScalar& beta, const GdnTokenScalar& gate, bool gate_is_raw,
-              DeviceInfo* d, cudaStream_t st) {
+              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* p_out = nullptr) {
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
-    CUtensorMap tmK, tmV;
+    CUtensorMap tmK, tmV, tmQ;
     if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
     if (int rc = make_token_map(&tmV, v, s, s.num_v_heads, "v")) return rc;
+    if (q) {
+        if (int rc = make_token_map(&tmQ, *q, s, s.num_k_heads, "q")) return rc;
+    } else {
+        tmQ = tmK;
+    }
     UWParams p{};
     p.map = chunk_map(s);
     p.beta = scalar_view(beta);
@@ -101,9 +107,15 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
     p.kh = s.num_k_heads;
     p.vh = s.num_v_heads;
     p.status = d->status;
+    p.p_out = static_cast<__nv_bfloat16*>(p_out);
     constexpr int smem = UWSmem<kD>::kBytes;
-    if (int rc = set_smem(gdn_uw_kernel<kD>, smem)) return rc;
-    gdn_uw_kernel<kD><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, p);
+    if (q) {
+        if (int rc = set_smem(gdn_uw_kernel<kD, true>, smem)) return rc;
+        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, p);
+    } else {
+        if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
+        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, p);
+    }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
@@ -186,8 +198,11 @@ size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
     const size_t tokens = s->cu_seqlens ? static_cast<size_t>(s->total_tokens)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>(s->seq_len);
-    // U and W, (tokens, vh, 128) bf16 each
-    return 2 * tokens * static_cast<size_t>(s->num_v_heads) * kD * 2 + 256;
+    const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
+                                        : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
+    // U and W, (tokens, vh, 128) bf16 each, then P, (chunks, vh, 64, 64) bf16
+    return 2 * tokens * static_cast<size_t>(s->num_v_heads) * kD * 2 +
+           chunks * static_cast<size_t>(s->num_v_heads) * 8192 + 256;
 }
 
 int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
@@ -223,33 +238,56 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
 
     void* const* ev = a->stage_events;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[0]), st));
-    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st)) return rc;
+    GDN_REQUIRE(!packed || s.cu_chunks, "gdn_chunked_forward: packed mode needs cu_chunks");
+    __nv_bfloat16* pbuf = static_cast<__nv_bfloat16*>(a->workspace) + 2 * tokens * s.num_v_heads * kD;
+    const long long units = static_cast<long long>(num_chunks(s)) * s.num_v_heads;
+    GDN_REQUIRE(units * 64 < (1ll << 31), "gdn_chunked_forward: too many (chunk, head) units");
+    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st, &a->q, pbuf)) return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
-    CUtensorMap tmQ, tmK, tmW, tmU;
-    if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
-    if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
-    if (int rc = make_token_map(&tmW, w, s, s.num_v_heads, "w")) return rc;
-    if (int rc = make_token_map(&tmU, u, s, s.num_v_heads, "u")) return rc;
-    SeqParams p{};
-    p.map = chunk_map(s);
-    p.gate = scalar_view(a->gate);
-    p.gate_is_raw = 1;
-    p.out = token_view(a->out);
-    p.state_in = static_cast<const __nv_bfloat16*>(a->initial_state.ptr);
-    p.si_ss = a->initial_state.stride_seq;
-    p.si_sh = a->initial_state.stride_head;
-    p.state_out = static_cast<__nv_bfloat16*>(a->final_state.ptr);
-    p.so_ss = a->final_state.stride_seq;
-    p.so_sh = a->final_state.stride_head;
-    p.kh = s.num_k_heads;
-    p.vh = s.num_v_heads;
-    p.scale = a->scale;
-    p.status = d->status;
-    if (int rc = launch_seq_t<true, false, false>(tmQ, tmK, tmW, tmU, p, dim3(s.batch, s.num_v_heads), st)) return rc;
+    if (num_chunks(s) > 0) {
+        CUtensorMap tmQ, tmK, tmW, tmU, tmP;
+        if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
+        if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
+        if (int rc = make_token_map(&tmW, w, s, s.num_v_heads, "w")) return rc;
+        if (int rc = make_token_map(&tmU, u, s, s.num_v_heads, "u")) return rc;
+        {
+            uint64_t dims[2] = {64, static_cast<uint64_t>(units) * 64};
+            uint64_t strides[1] = {128};
+            uint32_t box[2] = {64, 64};
+            if (!make_tmap_bf16(&tmP, pbuf, 2, dims, strides, box, true))
+                return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of the P scratch");
+        }
+        FusedParams p{};
+        p.map = chunk_map(s);
+        p.gate = scalar_view(a->gate);
+        p.out = token_view(a->out);
+        p.state_in = static_cast<const __nv_bfloat16*>(a->initial_state.ptr);
+        p.si_ss = a->initial_state.stride_seq;
+        p.si_sh = a->initial_state.stride_head;
+        p.state_out = static_cast<__nv_bfloat16*>(a->final_state.ptr);
+        p.so_ss = a->final_state.stride_seq;
+        p.so_sh = a->final_state.stride_head;
+        p.kh = s.num_k_heads;
+        p.vh = s.num_v_heads;
+        p.scale = a->scale;
+        p.status = d->status;
+        constexpr int smem = FusedSmem::kBytes;
+        if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
+        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmW, tmU, tmP, p);
+        GDN_CUDA(cudaGetLastError());
+    }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
     return GDN_OK;
 }
+
+#ifdef GDN_PHASE_TIMING
+int gdn_debug_phase_stamps(long long* out64) {
+    GDN_CUDA(cudaDeviceSynchronize());
+    GDN_CUDA(cudaMemcpyFromSymbol(out64, g_phase_stamps, sizeof(long long) * 64));
+    return GDN_OK;
+}
+#endif
 
 // ------------------------------------------------------------------ prefill on built-in scratch
 // Scratch for callers that cannot allocate device memory (see include/gdn_b200.h).  The array
@@ -266,9 +304,9 @@ int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* a, gdn_stream_t str
     if (need > GDN_STATIC_SCRATCH_BYTES)
         return fail(GDN_ERR_WORKSPACE,
                     "gdn_chunked_forward_static_scratch: this problem needs %zu bytes of scratch but the built-in "
-                    "array holds %u (tokens * num_v_heads must not exceed %u); use gdn_chunked_forward with a "
+                    "array holds %u (about 640 bytes per token and v-head); use gdn_chunked_forward with a "
                     "caller-provided workspace",
-                    need, GDN_STATIC_SCRATCH_BYTES, (GDN_STATIC_SCRATCH_BYTES - 256u) / 512u);
+                    need, GDN_STATIC_SCRATCH_BYTES);
     int dev = 0;
     GDN_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(GDN_ERR_UNSUPPORTED, "device index %d out of range", dev);

@@ -7,6 +7,20 @@ namespace gdn {
 
 constexpr int kChunk = 64;
 
+// Optional phase timing for kernel development: compiled in only with -DGDN_PHASE_TIMING.
+// CTA (0,0) writes clock64() stamps to a global buffer.
+#ifdef GDN_PHASE_TIMING
+__device__ long long g_phase_stamps[64];
+#define GDN_STAMP(i)                                                                  \
+    do {                                                                              \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_stamps[i] = clock64(); \
+    } while (0)
+#else
+#define GDN_STAMP(i) \
+    do {             \
+    } while (0)
+#endif
+
 // per-token scalar tensor (beta or gate) as the kernels see it
 struct ScalarView {
     const void* ptr;

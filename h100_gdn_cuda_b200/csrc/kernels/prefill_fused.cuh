@@ -1,0 +1,391 @@
+// State propagation + output of chunked Gated DeltaNet prefill, warp-specialised.
+// One CTA of 448 threads walks the chunks of one (sequence, v-head):
+//     U_new = U - W S^T
+//     O     = scale * ( e^{g} .* (Q S^T) + P U_new ),   P = tril(Q K^T .* e^{g_i - g_j}) (precomputed)
+//     S    <- e^{g_L} S + U_new^T (K .* e^{g_L - g})
+// This is the path gdn_chunked_forward uses; it stands in for the reference's
+// sm90_bf16_chunked_seq_state_update and sm90_bf16_gdn_chunked_compute_O
+// (kernels/sm90_bf16_chunked_seq_state_update2.cuh, sm90_bf16_gdn_chunked_compute_O.cuh:23-530)
+// and never writes per-chunk states.
+//
+// The only serial dependence between chunks runs through the state:
+//     S_bf(c) -> [MMA] D1 = U^T I - S_bf W^T -> [pass] Un_a, Un_b -> [MMA] dS = Un_b K -> [pass] S, S_bf(c+1)
+// Roles keep everything else off that chain:
+//   warps 0-7   state warps: own the fp32 state in registers (row = TMEM lane, 64 columns each),
+//               run the two passes of the chain
+//   warps 8-11  output warps: O epilogue (scale, transpose through shared memory, coalesced stores)
+//   warp 12     producer: chunk-local gate cumsum + TMA loads of Q, K, W, U, P two chunks ahead
+//   warp 13     one thread issues every tcgen05.mma and commits completion onto mbarriers
+// All operands are transposed so that the 128 state rows are the MMA M dimension; S_bf, Un_a,
+// Un_b are bf16 A operands in tensor memory; Q, K, W, U, P tiles are used as TMA delivered them.
+#pragma once
+#include <cuda.h>
+
+#include "prefill_common.cuh"
+
+namespace gdn {
+
+struct FusedParams {
+    ChunkMap map;
+    ScalarView gate;  // raw per-token log-decay; ptr == NULL: no decay
+    TokenView out;
+    const __nv_bfloat16* state_in;
+    long long si_ss, si_sh;
+    __nv_bfloat16* state_out;  // final state or NULL
+    long long so_ss, so_sh;
+    int kh, vh;
+    float scale;
+    int* status;
+};
+
+struct FusedSmem {
+    static constexpr int D = 128;
+    static constexpr int kTile = kChunk * D * 2;  // 16 KB
+    static constexpr int kOffQ = 0, kOffK = kTile, kOffW = 2 * kTile, kOffU = 3 * kTile, kOffP = 4 * kTile;
+    static constexpr int kStage = 4 * kTile + 8192;  // Q, K, W, U, P
+    static constexpr int kOffI = 2 * kStage;         // identity 64x64 bf16 K-major
+    static constexpr int kOffO = kOffI + 8192;       // two output staging tiles
+    static constexpr int kOffGate = kOffO + 2 * kTile;  // 3 x { e^g[64], e^{gL-g}[64], e^{gL} }
+    static constexpr int kGateStride = (2 * 64 + 4) * 4;
+    static constexpr int kOffBar = kOffGate + 3 * kGateStride;
+    static constexpr int kBytes = kOffBar + 128 + 1024;
+};
+
+namespace fused {
+constexpr int kThreads = 448;
+constexpr uint32_t kTmSbf = 0;    // bf16 state, 64 columns
+constexpr uint32_t kTmUnA = 64;   // bf16 U_new^T, 32 columns
+constexpr uint32_t kTmUnB = 96;   // bf16 U_new^T .* decay, 32 columns
+constexpr uint32_t kTmD1 = 128;   // fp32 U_new^T, 64 columns
+constexpr uint32_t kTmO1a = 192;  // fp32 S Q^T, even chunks
+constexpr uint32_t kTmDS = 256;   // fp32 state increment, 128 columns
+constexpr uint32_t kTmO1b = 384;  // fp32 S Q^T, odd chunks
+constexpr uint32_t kTmO2 = 448;   // fp32 U_new^T P^T
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+}  // namespace fused
+
+__global__ void __launch_bounds__(fused::kThreads, 1)
+    gdn_fused_seq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmU,
+                         const __grid_constant__ CUtensorMap tmP, const FusedParams p) {
+    using namespace ptx;
+    using namespace fused;
+    using L = FusedSmem;
+    constexpr int D = 128;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sI = smem + L::kOffI;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+    uint64_t* bar_full = bars;        // [2]
+    uint64_t* bar_empty = bars + 2;   // [2]
+    uint64_t* bar_sbf = bars + 4;
+    uint64_t* bar_d1 = bars + 5;
+    uint64_t* bar_un = bars + 6;
+    uint64_t* bar_ds = bars + 7;
+    uint64_t* bar_o = bars + 8;
+    uint64_t* bar_ofree = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int khead = head / (p.vh / p.kh);
+
+    int batch, gchunk0;
+    long long seq_tok0, seq_tokens;
+    if (p.map.cu_seqlens) {
+        const int bos = p.map.cu_seqlens[seq], eos = p.map.cu_seqlens[seq + 1];
+        seq_tok0 = bos;
+        seq_tokens = eos - bos;
+        batch = 0;
+        gchunk0 = p.map.cu_chunks[seq];
+    } else {
+        seq_tok0 = 0;
+        seq_tokens = p.map.seq_len;
+        batch = seq;
+        gchunk0 = seq * p.map.chunks_per_seq;
+    }
+    const int nchunks = static_cast<int>((seq_tokens + kChunk - 1) / kChunk);
+    auto chunk_n = [&](int c) {
+        const long long rem = seq_tokens - static_cast<long long>(c) * kChunk;
+        return rem < kChunk ? static_cast<int>(rem) : kChunk;
+    };
+    auto gate_buf = [&](int c) { return reinterpret_cast<float*>(smem + L::kOffGate + (c % 3) * L::kGateStride); };
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        mbar_init(&bar_empty[0], 1);
+        mbar_init(&bar_empty[1], 1);
+        mbar_init(bar_sbf, 8);
+        mbar_init(bar_d1, 1);
+        mbar_init(bar_un, 8);
+        mbar_init(bar_ds, 1);
+        mbar_init(bar_o, 1);
+        mbar_init(bar_ofree, 4);
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(tmem_slot, 512);
+    // identity tile (bf16 1.0 = 0x3F80), K-major swizzled
+    for (int idx = tid; idx < 64 * 8; idx += kThreads) {
+        const int r = idx >> 3, ch = idx & 7;
+        uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
+        if ((r >> 3) == ch) {
+            const uint32_t v = (r & 1) ? 0x3F800000u : 0x00003F80u;
+            const int wi = (r & 7) >> 1;
+            w0 = wi == 0 ? v : 0;
+            w1 = wi == 1 ? v : 0;
+            w2 = wi == 2 ? v : 0;
+            w3 = wi == 3 ? v : 0;
+        }
+        *reinterpret_cast<uint4*>(sI + sw128_offset(r, ch * 8)) = make_uint4(w0, w1, w2, w3);
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // =============================================================== state warps
+        const int lq = warp & 3, hf = warp >> 2;
+        const int row = 32 * lq + lane;
+        const uint32_t tm_lane = static_cast<uint32_t>(32 * lq) << 16;
+        float S[64];
+        if (p.state_in) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.state_in + seq * p.si_ss + head * p.si_sh +
+                                                              static_cast<long long>(row) * D + 64 * hf);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint4 v = __ldg(src + q);
+                S[q * 8 + 0] = bf16_lo(v.x); S[q * 8 + 1] = bf16_hi(v.x);
+                S[q * 8 + 2] = bf16_lo(v.y); S[q * 8 + 3] = bf16_hi(v.y);
+                S[q * 8 + 4] = bf16_lo(v.z); S[q * 8 + 5] = bf16_hi(v.z);
+                S[q * 8 + 6] = bf16_lo(v.w); S[q * 8 + 7] = bf16_hi(v.w);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 64; ++q) S[q] = 0.f;
+        }
+        auto publish_state = [&]() {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t w[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) w[e] = pack_bf16(S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]);
+                tmem_st16(tmem + kTmSbf + tm_lane + 32 * hf + 16 * q, w);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sbf);
+        };
+        publish_state();
+
+        for (int c = 0; c < nchunks; ++c) {
+            const uint32_t par = static_cast<uint32_t>(c & 1);
+            const int n = chunk_n(c);
+            const float* gb = gate_buf(c);
+            mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);  // gate values visible
+            // ---- U_new^T -> two bf16 operand copies (rows past the end zeroed)
+            mbar_wait(bar_d1, par, abort_flag);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+                uint32_t r[16];
+                tmem_ld16(tmem + kTmD1 + tm_lane + 32 * hf + 16 * h2, r);
+                tmem_wait_ld();
+                uint32_t wa[8], wb[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int i0 = 32 * hf + 16 * h2 + 2 * e;
+                    const float u0 = i0 < n ? __uint_as_float(r[2 * e]) : 0.f;
+                    const float u1 = i0 + 1 < n ? __uint_as_float(r[2 * e + 1]) : 0.f;
+                    wa[e] = pack_bf16(u0, u1);
+                    wb[e] = pack_bf16(u0 * gb[64 + i0], u1 * gb[64 + i0 + 1]);
+                }
+                tmem_st8(tmem + kTmUnA + tm_lane + 16 * hf + 8 * h2, wa);
+                tmem_st8(tmem + kTmUnB + tm_lane + 16 * hf + 8 * h2, wb);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_un);
+            // ---- S <- e^{g_L} S + dS
+            const float eg_last = gb[128];
+            mbar_wait(bar_ds, par, abort_flag);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t r[32];
+                tmem_ld32(tmem + kTmDS + tm_lane + 64 * hf + 32 * q, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) S[q * 32 + e] = fmaf(S[q * 32 + e], eg_last, __uint_as_float(r[e]));
+            }
+            publish_state();
+        }
+        if (p.state_out) {
+            uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
+                                                 static_cast<long long>(row) * D + 64 * hf);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                uint4 v;
+                v.x = pack_bf16(S[q * 8 + 0], S[q * 8 + 1]);
+                v.y = pack_bf16(S[q * 8 + 2], S[q * 8 + 3]);
+                v.z = pack_bf16(S[q * 8 + 4], S[q * 8 + 5]);
+                v.w = pack_bf16(S[q * 8 + 6], S[q * 8 + 7]);
+                d4[q] = v;
+            }
+        }
+    } else if (warp < 12) {
+        // =============================================================== output warps
+        const int lq = warp & 3;
+        const int row = 32 * lq + lane;
+        const int otid = tid - 256;
+        const uint32_t tm_lane = static_cast<uint32_t>(32 * lq) << 16;
+        for (int c = 0; c < nchunks; ++c) {
+            const uint32_t par = static_cast<uint32_t>(c & 1);
+            const int n = chunk_n(c);
+            const float* gb = gate_buf(c);
+            uint8_t* sO = smem + L::kOffO + (c & 1) * L::kTile;
+            const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a) + tm_lane;
+            const uint32_t tO2 = tmem + kTmO2 + tm_lane;
+            mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
+            mbar_wait(bar_o, par, abort_flag);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                uint32_t r1[16], r2[16];
+                tmem_ld16(tO1 + 16 * b, r1);
+                tmem_ld16(tO2 + 16 * b, r2);
+                tmem_wait_ld();
+                if (b == 3) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_ofree);  // accumulators consumed
+                }
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int i = 16 * b + e;
+                    const float o = p.scale * fmaf(gb[i], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
+                    *reinterpret_cast<__nv_bfloat16*>(sO + stage_off<D>(i, row >> 3) + (row & 7) * 2) = __float2bfloat16(o);
+                }
+            }
+            named_bar_sync(1, 128);
+            store_staged_tile<D, 128>(sO, p.out, batch, seq_tok0 + static_cast<long long>(c) * kChunk, head, n, otid);
+            // the staging tile used now is rewritten two chunks later, after the next named barrier
+        }
+    } else if (warp == 12) {
+        // =============================================================== producer
+        for (int c = 0; c < nchunks; ++c) {
+            const int s = c & 1;
+            mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
+            // chunk-local cumulative gate: lane l holds tokens l and l + 32
+            float* gb = gate_buf(c);
+            const int n = chunk_n(c);
+            float g0 = 0.f, g1 = 0.f;
+            if (p.gate.ptr) {
+                const long long t0 = static_cast<long long>(c) * kChunk + lane;
+                if (t0 < seq_tokens) g0 = p.gate.load(batch, seq_tok0 + t0, head);
+                if (t0 + 32 < seq_tokens) g1 = p.gate.load(batch, seq_tok0 + t0 + 32, head);
+            }
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const float y0 = __shfl_up_sync(0xffffffffu, g0, m);
+                const float y1 = __shfl_up_sync(0xffffffffu, g1, m);
+                if (lane >= m) {
+                    g0 += y0;
+                    g1 += y1;
+                }
+            }
+            g1 += __shfl_sync(0xffffffffu, g0, 31);
+            // tokens past the end carry the last valid value (their raw gate was taken as 0)
+            const float g_last = __shfl_sync(0xffffffffu, (n - 1 < 32) ? g0 : g1, (n - 1) & 31);
+            gb[lane] = __expf(g0);
+            gb[lane + 32] = __expf(g1);
+            gb[64 + lane] = __expf(g_last - g0);
+            gb[64 + lane + 32] = __expf(g_last - g1);
+            if (lane == 0) gb[128] = __expf(g_last);
+            __syncwarp();
+            if (lane == 0) {
+                uint8_t* st = smem + s * L::kStage;
+                const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
+                const int prow = ((gchunk0 + c) * p.vh + head) * 64;
+                mbar_arrive_expect_tx(&bar_full[s], L::kStage);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    tma_load_4d(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
+                    tma_load_4d(st + L::kOffW + a * 8192, &tmW, &bar_full[s], a * 64, head, tok, batch);
+                    tma_load_4d(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
+                    tma_load_4d(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
+                }
+                tma_load_2d(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
+            }
+        }
+    } else {
+        // =============================================================== MMA issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t id_ui = make_idesc_bf16(128, 64, true, false);
+            constexpr uint32_t id_sw = make_idesc_bf16(128, 64, false, false, true);
+            constexpr uint32_t id_sq = make_idesc_bf16(128, 64, false, false);
+            constexpr uint32_t id_ds = make_idesc_bf16(128, 128, false, true);
+            for (int c = 0; c < nchunks; ++c) {
+                const int s = c & 1;
+                const uint32_t par = static_cast<uint32_t>(c & 1);
+                const uint32_t st = smem_u32(smem + s * L::kStage);
+                mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
+                tc_fence_after_sync();
+                // D1 = U^T I  (does not need the state)
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ss(tmem + kTmD1, make_smem_desc_sw128(st + L::kOffU + ks * 2048, 8192, 1024),
+                           make_smem_desc_sw128(smem_u32(sI) + ks * 32, 0, 1024), id_ui, ks > 0);
+                mbar_wait(bar_sbf, par, abort_flag);
+                tc_fence_after_sync();
+                // D1 -= S_bf W^T
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ts(tmem + kTmD1, tmem + kTmSbf + ks * 8,
+                           make_smem_desc_sw128(st + L::kOffW + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sw, 1);
+                mma_commit(bar_d1);
+                // O1 = S_bf Q^T
+                const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)
+                    mma_ts(tO1, tmem + kTmSbf + ks * 8,
+                           make_smem_desc_sw128(st + L::kOffQ + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sq, ks > 0);
+                mbar_wait(bar_un, par, abort_flag);
+                tc_fence_after_sync();
+                // dS = Un_b K
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ts(tmem + kTmDS, tmem + kTmUnB + ks * 8,
+                           make_smem_desc_sw128(st + L::kOffK + ks * 2048, 8192, 1024), id_ds, ks > 0);
+                mma_commit(bar_ds);
+                // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
+                if (c > 0) {
+                    mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
+                    tc_fence_after_sync();
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_ts(tmem + kTmO2, tmem + kTmUnA + ks * 8,
+                           make_smem_desc_sw128(st + L::kOffP + ks * 32, 0, 1024), id_sq, ks > 0);
+                mma_commit(bar_o);
+                mma_commit(&bar_empty[s]);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+    if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 4);
+}
+
+}  // namespace gdn

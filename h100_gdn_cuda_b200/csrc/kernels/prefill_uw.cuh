@@ -33,6 +33,7 @@ struct UWParams {
     ScalarView gate;      // ptr == NULL: no decay
     int gate_is_raw;      // 1: per-token log-decay (cumsum taken here); 0: already chunk-local cumsum
     TokenView u, w;
+    __nv_bfloat16* p_out;  // kWithP: (chunk, v-head, 64, 64) bf16, chunk in global chunk order
     int kh, vh;
     int* status;
 };
@@ -96,9 +97,13 @@ __device__ __forceinline__ void store_block(const float* d, float sign, float* m
 }
 }  // namespace uw
 
-template <int D>
+// With kWithP the kernel also produces the intra-chunk attention block the output stage needs,
+//     P = tril(Q K^T .* exp(g_i - g_j))   (bf16, 64x64 per unit),
+// from a Q tile that is loaded into the buffer the V tile later occupies.
+template <int D, bool kWithP>
 __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
                                                         const __grid_constant__ CUtensorMap tmV,
+                                                        const __grid_constant__ CUtensorMap tmQ,
                                                         const UWParams p) {
     using namespace ptx;
     using namespace uw;
@@ -141,11 +146,15 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     const uint32_t tmem = *tmem_slot;
     const uint32_t tLo = tmem, tHi = tmem + (16u << 16);  // the two interleaved M=64 accumulators
 
+    GDN_STAMP(0);
     if (tid == 0) {
         mbar_arrive_expect_tx(bar_load, 2 * L::kTile);
         for (int a = 0; a < NA; ++a) {
             tma_load_4d(sK + a * 8192, &tmK, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
-            tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+            if (kWithP)
+                tma_load_4d(sV + a * 8192, &tmQ, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
+            else
+                tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
         }
     }
     // beta and the chunk-local cumulative gate (rows past the end: beta = 0, g = g of the last row)
@@ -185,8 +194,10 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
+    GDN_STAMP(1);
     // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
     mbar_wait(bar_load, 0, abort_flag);
+    GDN_STAMP(2);
     if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
@@ -198,12 +209,18 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
             const uint64_t b1 = make_smem_desc_sw128(smem_u32(sK) + off + 32 * 128, 0, 1024);
             mma_ss(tLo, a, b0, idesc, ks > 0);
             mma_ss(tHi, a, b1, idesc, ks > 0);
+            if (kWithP) {  // Q K^T the same way, into columns 32-63
+                const uint64_t q = make_smem_desc_sw128(smem_u32(sV) + off, 0, 1024);
+                mma_ss(tLo + 32, q, b0, idesc, ks > 0);
+                mma_ss(tHi + 32, q, b1, idesc, ks > 0);
+            }
         }
         mma_commit(bar_mma);
     }
     __syncwarp();
     mbar_wait(bar_mma, 0, abort_flag);
     tc_fence_after_sync();
+    GDN_STAMP(3);
     {
         // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63
         const int i = 16 * warp + (lane & 15);
@@ -223,9 +240,47 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
             *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
         }
     }
+    uint32_t bar_load_parity = 0;
+    if (kWithP) {
+        // P rows into a plain [64][64] bf16 staging tile over the (dead) Q tile, then to global
+        const int i = 16 * warp + (lane & 15);
+        const int cbase = (lane >> 4) * 32;
+        const float gi = sG[i];
+        uint32_t r[32];
+        tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int col = cbase + j + 2 * e + q;
+                    v[q] = (col <= i && i < n) ? __uint_as_float(r[j + 2 * e + q]) * __expf(gi - sG[col]) : 0.f;
+                }
+                w[e] = pack_bf16(v[0], v[1]);
+            }
+            *reinterpret_cast<uint4*>(sV + stage_off<64>(i, (cbase + j) / 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
     tc_fence_before_sync();
     __syncthreads();
+    if (kWithP) {
+        uint4* dst = reinterpret_cast<uint4*>(p.p_out + (static_cast<long long>(blockIdx.x) * p.vh + head) * 4096);
+        for (int idx = tid; idx < 512; idx += 128) dst[idx] = *reinterpret_cast<const uint4*>(sV + stage_off<64>(idx >> 3, idx & 7));
+        fence_proxy_async_smem();
+        __syncthreads();  // staging read out: the buffer may now receive the V tile
+        if (tid == 0) {
+            mbar_arrive_expect_tx(bar_load, L::kTile);
+            for (int a = 0; a < NA; ++a)
+                tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+        }
+        bar_load_parity = 1;
+    }
 
+    GDN_STAMP(4);
     // ---- X = (I + A)^-1 : diagonal 16x16 blocks, one column per thread
     if (lane < 16) {
         const int b = warp, j = lane;
@@ -243,6 +298,7 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
         for (int i = 0; i < 16; ++i) sX[(16 * b + i) * LDX + 16 * b + j] = x[i];
     }
     __syncthreads();
+    GDN_STAMP(5);
     // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half)
     {
         const int pr = warp >> 1, n0 = 8 * (warp & 1);
@@ -259,6 +315,7 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
         store_block(e, -1.f, sX, LDX, i0, j0 + n0, lane);
     }
     __syncthreads();
+    GDN_STAMP(6);
     // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result
     {
         const int rb = warp >> 1, cb = warp & 1;
@@ -282,6 +339,7 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
+    GDN_STAMP(7);
     // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles (over A)
     {
         const int i = tid >> 1, c0 = (tid & 1) * 32;
@@ -306,7 +364,9 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     fence_proxy_async_smem();
     __syncthreads();
 
+    GDN_STAMP(8);
     // ---- U = T V (lanes +0), W = T' K (lanes +16)
+    if (kWithP) mbar_wait(bar_load, bar_load_parity, abort_flag);
     if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
@@ -328,6 +388,7 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     mbar_wait(bar_mma, 1, abort_flag);
     tc_fence_after_sync();
 
+    GDN_STAMP(9);
     // ---- accumulators -> bf16 -> staged tiles (over the K and V tiles) -> coalesced stores
     uint8_t* stU = sK;
     uint8_t* stW = sV;
@@ -352,8 +413,10 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     }
     tc_fence_before_sync();
     __syncthreads();
+    GDN_STAMP(10);
     store_staged_tile<D, 128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
     store_staged_tile<D, 128>(stW, p.w, cp.batch, cp.tok0, head, n, tid);
+    GDN_STAMP(11);
     if (warp == 0) tmem_dealloc(tmem, D);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
 }

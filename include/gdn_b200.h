@@ -222,14 +222,16 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  * prefill: a serving engine that has handed all HBM to its own pool, a plugin running
  * inside someone else's memory plan, or code on a path where cudaMalloc is forbidden
  * because it synchronises the device.  For them this entry point runs the same two kernels
- * as gdn_chunked_forward but keeps the U/W scratch in a fixed array that is part of the
+ * as gdn_chunked_forward but keeps their scratch in a fixed array that is part of the
  * library image (GDN_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the
  * library, held until the process exits).  `workspace` and `workspace_bytes` in `args` are
  * ignored; inputs and outputs are passed as usual.
  *
- *   - Limit: tokens * num_v_heads * 512 bytes of U/W scratch must fit, i.e.
- *     tokens * num_v_heads <= 131072 (for example 4096 tokens of 32 v-heads; the array is
- *     64 MiB plus the 256 bytes of slack gdn_chunked_forward_workspace_bytes adds).  Larger problems are refused with GDN_ERR_WORKSPACE and a message.
+ *   - Limit: gdn_chunked_forward_workspace_bytes(&args->shape) must not exceed
+ *     GDN_STATIC_SCRATCH_BYTES (80 MiB + 256 bytes).  The scratch holds U and W (512 bytes per
+ *     token and v-head) and the intra-chunk attention blocks (8 KiB per 64-token chunk and
+ *     v-head), so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
+ *     tokens of 32 v-heads.  Larger problems are refused with GDN_ERR_WORKSPACE and a message.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address; make that first
  *     call outside any stream capture.
@@ -237,7 +239,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  *     left there.  Nothing in it has to start at zero (every element that is read has been
  *     written earlier in the same call), but two calls whose kernels overlap on the GPU -
  *     different streams, or different host threads - race on it: serialise them. */
-#define GDN_STATIC_SCRATCH_BYTES ((64u << 20) + 256u)
+#define GDN_STATIC_SCRATCH_BYTES ((80u << 20) + 256u)
 int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* args, gdn_stream_t stream);
 
 #ifdef __cplusplus
