@@ -48,13 +48,14 @@ def flops_per_unit(d: int, c: int = CHUNK) -> float:
 
 
 def seq_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
-    """Contractions done by the state/output kernel: QK^T, P U_new (2Ccd each) and
+    """Contractions done by the state/output kernel: P U_new (2CCd) and
     W S^T, Q S^T, U_new^T K (2Cdd each)."""
-    return 2.0 * c * (2 * c * d + 3 * d * d)
+    return 2.0 * c * (c * d + 3 * d * d)
 
 
 def uw_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
-    return 2.0 * c * (3 * c * d) + (2.0 / 3.0) * c ** 3
+    """K K^T, Q K^T, T V, T' K (2CCd each) and the triangular inverse."""
+    return 2.0 * c * (4 * c * d) + (2.0 / 3.0) * c ** 3
 
 
 def decode_bytes_per_token(kh, vh, d) -> float:
@@ -376,11 +377,11 @@ def main():
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
         "gpu_launches": 2 * args.steps,
-        "roofline": {"kernel": "gdn_seq_kernel (state propagation + output)", "bound": "tensor",
+        "roofline": {"kernel": "gdn_fused_seq_kernel (state propagation + output)", "bound": "tensor",
                      "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
                      "ms_per_launch": seq_ms, "flops_per_launch": seq_flops},
-        "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_seq_kernel_ms": seq_ms,
+        "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_fused_seq_kernel_ms": seq_ms,
                     "uw_tflops": units * uw_kernel_flops_per_unit(d) / (uw_ms * 1e-3) / 1e12,
                     "whole_step_tflops": total_flops / (ms_res * 1e-3) / 1e12,
                     "whole_step_frac_of_tensor_peak": total_flops / (ms_res * 1e-3) / 1e12 / peaks["tflops"]},

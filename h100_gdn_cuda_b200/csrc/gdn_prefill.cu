@@ -85,13 +85,17 @@ int set_smem(K kernel, int bytes) {
 
 int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& v, const GdnTokenTensor& u,
               const GdnTokenTensor& w, const GdnTokenScalar& beta, const GdnTokenScalar& gate, bool gate_is_raw,
-              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* p_out = nullptr) {
+              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* p_out = nullptr,
+              const CUtensorMap* tm_p = nullptr, float p_scale = 1.f) {
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
-    CUtensorMap tmK, tmV, tmQ;
+    CUtensorMap tmK, tmV, tmQ, tmUo, tmWo;
     if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
     if (int rc = make_token_map(&tmV, v, s, s.num_v_heads, "v")) return rc;
+    if (int rc = make_token_map(&tmUo, u, s, s.num_v_heads, "u")) return rc;
+    if (int rc = make_token_map(&tmWo, w, s, s.num_v_heads, "w")) return rc;
+    const CUtensorMap tmPo = tm_p ? *tm_p : tmK;
     if (q) {
         if (int rc = make_token_map(&tmQ, *q, s, s.num_k_heads, "q")) return rc;
     } else {
@@ -108,13 +112,14 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
     p.vh = s.num_v_heads;
     p.status = d->status;
     p.p_out = static_cast<__nv_bfloat16*>(p_out);
+    p.p_scale = p_scale;
     constexpr int smem = UWSmem<kD>::kBytes;
     if (q) {
         if (int rc = set_smem(gdn_uw_kernel<kD, true>, smem)) return rc;
-        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, p);
+        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, tmPo, p);
     } else {
         if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
-        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, p);
+        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, tmPo, p);
     }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
@@ -242,22 +247,31 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     __nv_bfloat16* pbuf = static_cast<__nv_bfloat16*>(a->workspace) + 2 * tokens * s.num_v_heads * kD;
     const long long units = static_cast<long long>(num_chunks(s)) * s.num_v_heads;
     GDN_REQUIRE(units * 64 < (1ll << 31), "gdn_chunked_forward: too many (chunk, head) units");
-    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st, &a->q, pbuf)) return rc;
+    if (num_chunks(s) == 0) {
+        if (ev) {
+            GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
+            GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
+        }
+        return GDN_OK;
+    }
+    CUtensorMap tmP;
+    {
+        uint64_t dims[2] = {64, static_cast<uint64_t>(units) * 64};
+        uint64_t strides[1] = {128};
+        uint32_t box[2] = {64, 64};
+        if (!make_tmap_bf16(&tmP, pbuf, 2, dims, strides, box, true))
+            return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of the P scratch");
+    }
+    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st, &a->q, pbuf, &tmP, a->scale)) return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
-    if (num_chunks(s) > 0) {
-        CUtensorMap tmQ, tmK, tmW, tmU, tmP;
+    {
+        CUtensorMap tmQ, tmK, tmW, tmU, tmO;
         if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
         if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
         if (int rc = make_token_map(&tmW, w, s, s.num_v_heads, "w")) return rc;
         if (int rc = make_token_map(&tmU, u, s, s.num_v_heads, "u")) return rc;
-        {
-            uint64_t dims[2] = {64, static_cast<uint64_t>(units) * 64};
-            uint64_t strides[1] = {128};
-            uint32_t box[2] = {64, 64};
-            if (!make_tmap_bf16(&tmP, pbuf, 2, dims, strides, box, true))
-                return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of the P scratch");
-        }
+        if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "out")) return rc;
         FusedParams p{};
         p.map = chunk_map(s);
         p.gate = scalar_view(a->gate);
@@ -274,7 +288,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         p.status = d->status;
         constexpr int smem = FusedSmem::kBytes;
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
-        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmW, tmU, tmP, p);
+        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmW, tmU, tmP, tmO, p);
         GDN_CUDA(cudaGetLastError());
     }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));

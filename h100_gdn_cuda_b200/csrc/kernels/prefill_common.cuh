@@ -15,9 +15,16 @@ __device__ long long g_phase_stamps[64];
     do {                                                                              \
         if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_stamps[i] = clock64(); \
     } while (0)
+#define GDN_STAMP_ANY(i)                                                   \
+    do {                                                                  \
+        if (blockIdx.x == 0 && blockIdx.y == 0) g_phase_stamps[i] = clock64(); \
+    } while (0)
 #else
 #define GDN_STAMP(i) \
     do {             \
+    } while (0)
+#define GDN_STAMP_ANY(i) \
+    do {                 \
     } while (0)
 #endif
 
@@ -96,6 +103,28 @@ __device__ __forceinline__ void store_staged_tile(const uint8_t* stage, const To
         if (row < n) {
             const uint4 v = *reinterpret_cast<const uint4*>(stage + stage_off<D>(row, chunk));
             *reinterpret_cast<uint4*>(base + row * dst.st + chunk * 8) = v;
+        }
+    }
+}
+
+// Byte offset of 16-byte piece `c16` (0..15) of row `row` in a 64 x 128 bf16 tile kept as two
+// 64 x 64 atoms in the layout TMA uses with the 128-byte swizzle (what a tiled TMA store or
+// load with box 64 x 64 expects in shared memory).
+__device__ __forceinline__ uint32_t tile_off(int row, int c16) {
+    return static_cast<uint32_t>((c16 >> 3) * 8192 + row * 128 + (((c16 & 7) ^ (row & 7)) << 4));
+}
+
+// Row-predicated copy of rows [0, n) of such a tile to global memory (used where a TMA store
+// would write past the end of a packed sequence).
+template <int THREADS>
+__device__ __forceinline__ void store_tile_rows(const uint8_t* tile, const TokenView& dst, int batch, long long tok0,
+                                                int head, int n, int tid) {
+    __nv_bfloat16* base = dst.ptr + batch * dst.sb + tok0 * dst.st + static_cast<long long>(head) * dst.sh;
+    for (int idx = tid; idx < kChunk * 16; idx += THREADS) {
+        const int row = idx >> 4, c16 = idx & 15;
+        if (row < n) {
+            const uint4 v = *reinterpret_cast<const uint4*>(tile + tile_off(row, c16));
+            *reinterpret_cast<uint4*>(base + row * dst.st + c16 * 8) = v;
         }
     }
 }

@@ -70,7 +70,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 __global__ void __launch_bounds__(fused::kThreads, 1)
     gdn_fused_seq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmU,
-                         const __grid_constant__ CUtensorMap tmP, const FusedParams p) {
+                         const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmO,
+                         const FusedParams p) {
     using namespace ptx;
     using namespace fused;
     using L = FusedSmem;
@@ -194,6 +195,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             // ---- U_new^T -> two bf16 operand copies (rows past the end zeroed)
             mbar_wait(bar_d1, par, abort_flag);
             tc_fence_after_sync();
+            if (c == 4 && tid == 0) GDN_STAMP_ANY(40);
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
                 uint32_t r[16];
@@ -215,10 +217,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_un);
+            if (c == 4 && tid == 0) GDN_STAMP_ANY(41);
             // ---- S <- e^{g_L} S + dS
             const float eg_last = gb[128];
             mbar_wait(bar_ds, par, abort_flag);
             tc_fence_after_sync();
+            if (c == 4 && tid == 0) GDN_STAMP_ANY(42);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t r[32];
@@ -228,6 +232,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 for (int e = 0; e < 32; ++e) S[q * 32 + e] = fmaf(S[q * 32 + e], eg_last, __uint_as_float(r[e]));
             }
             publish_state();
+            if (c == 4 && tid == 0) GDN_STAMP_ANY(43);
         }
         if (p.state_out) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
@@ -245,9 +250,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     } else if (warp < 12) {
         // =============================================================== output warps
         const int lq = warp & 3;
-        const int row = 32 * lq + lane;
+        const int row = 32 * lq + lane;  // dv index = TMEM lane
         const int otid = tid - 256;
         const uint32_t tm_lane = static_cast<uint32_t>(32 * lq) << 16;
+        // element (token i, dv row) of the swizzled staging tile: i * 128 + off8[i & 7]
+        uint32_t off8[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            off8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
+        const bool packed = p.map.cu_seqlens != nullptr;
         for (int c = 0; c < nchunks; ++c) {
             const uint32_t par = static_cast<uint32_t>(c & 1);
             const int n = chunk_n(c);
@@ -272,14 +283,26 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const int i = 16 * b + e;
-                    const float o = p.scale * fmaf(gb[i], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
-                    *reinterpret_cast<__nv_bfloat16*>(sO + stage_off<D>(i, row >> 3) + (row & 7) * 2) = __float2bfloat16(o);
+                    const float o = fmaf(gb[i], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
+                    *reinterpret_cast<__nv_bfloat16*>(sO + i * 128 + off8[i & 7]) = __float2bfloat16(o);
                 }
             }
+            const long long tok0 = seq_tok0 + static_cast<long long>(c) * kChunk;
+            const bool ragged = packed && n < kChunk;  // a full-box store would spill into the next sequence
+            fence_proxy_async_smem();
+            if (otid == 0) bulk_wait_read<0>();  // earlier stores have finished reading their staging tiles
             named_bar_sync(1, 128);
-            store_staged_tile<D, 128>(sO, p.out, batch, seq_tok0 + static_cast<long long>(c) * kChunk, head, n, otid);
-            // the staging tile used now is rewritten two chunks later, after the next named barrier
+            if (!ragged) {
+                if (otid == 0) {
+                    tma_store_4d(&tmO, sO, 0, head, static_cast<int>(tok0), batch);
+                    tma_store_4d(&tmO, sO + 8192, 64, head, static_cast<int>(tok0), batch);
+                    bulk_commit();
+                }
+            } else {
+                store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid);
+            }
         }
+        if (otid == 0) bulk_wait_read<0>();
     } else if (warp == 12) {
         // =============================================================== producer
         for (int c = 0; c < nchunks; ++c) {
@@ -306,8 +329,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             g1 += __shfl_sync(0xffffffffu, g0, 31);
             // tokens past the end carry the last valid value (their raw gate was taken as 0)
             const float g_last = __shfl_sync(0xffffffffu, (n - 1 < 32) ? g0 : g1, (n - 1) & 31);
-            gb[lane] = __expf(g0);
-            gb[lane + 32] = __expf(g1);
+            gb[lane] = p.scale * __expf(g0);  // the epilogue's factor for S q (P already carries the scale)
+            gb[lane + 32] = p.scale * __expf(g1);
             gb[64 + lane] = __expf(g_last - g0);
             gb[64 + lane + 32] = __expf(g_last - g1);
             if (lane == 0) gb[128] = __expf(g_last);
@@ -340,33 +363,40 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 const uint32_t st = smem_u32(smem + s * L::kStage);
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
+                if (c == 4) GDN_STAMP_ANY(30);
                 // D1 = U^T I  (does not need the state)
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_ss(tmem + kTmD1, make_smem_desc_sw128(st + L::kOffU + ks * 2048, 8192, 1024),
                            make_smem_desc_sw128(smem_u32(sI) + ks * 32, 0, 1024), id_ui, ks > 0);
+                if (c == 4) GDN_STAMP_ANY(31);
                 mbar_wait(bar_sbf, par, abort_flag);
                 tc_fence_after_sync();
+                if (c == 4) GDN_STAMP_ANY(32);
                 // D1 -= S_bf W^T
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ts(tmem + kTmD1, tmem + kTmSbf + ks * 8,
                            make_smem_desc_sw128(st + L::kOffW + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sw, 1);
                 mma_commit(bar_d1);
+                if (c == 4) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
                 const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
                     mma_ts(tO1, tmem + kTmSbf + ks * 8,
                            make_smem_desc_sw128(st + L::kOffQ + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sq, ks > 0);
+                if (c == 4) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
+                if (c == 4) GDN_STAMP_ANY(35);
                 // dS = Un_b K
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
                     mma_ts(tmem + kTmDS, tmem + kTmUnB + ks * 8,
                            make_smem_desc_sw128(st + L::kOffK + ks * 2048, 8192, 1024), id_ds, ks > 0);
                 mma_commit(bar_ds);
+                if (c == 4) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
                 if (c > 0) {
                     mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
@@ -378,6 +408,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                            make_smem_desc_sw128(st + L::kOffP + ks * 32, 0, 1024), id_sq, ks > 0);
                 mma_commit(bar_o);
                 mma_commit(&bar_empty[s]);
+                if (c == 4) GDN_STAMP_ANY(37);
+                if (c == 5) GDN_STAMP_ANY(38);
             }
         }
     }

@@ -34,6 +34,7 @@ struct UWParams {
     int gate_is_raw;      // 1: per-token log-decay (cumsum taken here); 0: already chunk-local cumsum
     TokenView u, w;
     __nv_bfloat16* p_out;  // kWithP: (chunk, v-head, 64, 64) bf16, chunk in global chunk order
+    float p_scale;         // kWithP: factor folded into P (the output scale)
     int kh, vh;
     int* status;
 };
@@ -104,6 +105,9 @@ template <int D, bool kWithP>
 __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
                                                         const __grid_constant__ CUtensorMap tmV,
                                                         const __grid_constant__ CUtensorMap tmQ,
+                                                        const __grid_constant__ CUtensorMap tmUo,
+                                                        const __grid_constant__ CUtensorMap tmWo,
+                                                        const __grid_constant__ CUtensorMap tmPo,
                                                         const UWParams p) {
     using namespace ptx;
     using namespace uw;
@@ -132,6 +136,12 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     const int khead = head / (p.vh / p.kh);
     const ChunkPos cp = locate_chunk(p.map, blockIdx.x);
     const int n = cp.n;
+    // beta and gate of this thread's token: requested first, used after the set-up below
+    float b_mine = 0.f, g_mine = 0.f;
+    if (tid < n) {
+        b_mine = p.beta.load(cp.batch, cp.tok0 + tid, head);
+        if (p.gate.ptr) g_mine = p.gate.load(cp.batch, cp.tok0 + tid, head);
+    }
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -159,12 +169,8 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     }
     // beta and the chunk-local cumulative gate (rows past the end: beta = 0, g = g of the last row)
     if (tid < 64) {
-        float b = 0.f, g = 0.f;
-        if (tid < n) {
-            b = p.beta.load(cp.batch, cp.tok0 + tid, head);
-            if (p.gate.ptr) g = p.gate.load(cp.batch, cp.tok0 + tid, head);
-        }
-        sBeta[tid] = b;
+        float g = g_mine;
+        sBeta[tid] = b_mine;
         if (p.gate_is_raw) {
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1) {
@@ -222,57 +228,46 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     tc_fence_after_sync();
     GDN_STAMP(3);
     {
-        // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63
+        // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63.
+        // The decay factor exp(g_i - g_j) is shared by A (strictly lower part) and P (lower part).
         const int i = 16 * warp + (lane & 15);
         const int cbase = (lane >> 4) * 32;
         const float bi = sBeta[i], gi = sG[i];
-        uint32_t r[32];
+        uint32_t r[32], rq[32];
         tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            float a[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int col = cbase + j + e;
-                a[e] = (col < i && i < n) ? bi * __uint_as_float(r[j + e]) * __expf(gi - sG[col]) : 0.f;
-            }
-            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
-        }
-    }
-    uint32_t bar_load_parity = 0;
-    if (kWithP) {
-        // P rows into a plain [64][64] bf16 staging tile over the (dead) Q tile, then to global
-        const int i = 16 * warp + (lane & 15);
-        const int cbase = (lane >> 4) * 32;
-        const float gi = sG[i];
-        uint32_t r[32];
-        tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 32, r);
+        if (kWithP) tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 32, rq);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-            uint32_t w[4];
+            float a[8], pq[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v[2];
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int col = cbase + j + 2 * e + q;
-                    v[q] = (col <= i && i < n) ? __uint_as_float(r[j + 2 * e + q]) * __expf(gi - sG[col]) : 0.f;
-                }
-                w[e] = pack_bf16(v[0], v[1]);
+            for (int e = 0; e < 8; ++e) {
+                const int col = cbase + j + e;
+                const bool low = col <= i && i < n;
+                const float dec = low ? __expf(gi - sG[col]) : 0.f;
+                a[e] = (col < i) ? bi * __uint_as_float(r[j + e]) * dec : 0.f;
+                if (kWithP) pq[e] = p.p_scale * __uint_as_float(rq[j + e]) * dec;
             }
-            *reinterpret_cast<uint4*>(sV + stage_off<64>(i, (cbase + j) / 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j + 4]) = make_float4(a[4], a[5], a[6], a[7]);
+            if (kWithP) {
+                // P tile staged over the (dead) Q tile in the 64x64 swizzled TMA layout
+                *reinterpret_cast<uint4*>(sV + tile_off(i, (cbase + j) >> 3)) =
+                    make_uint4(pack_bf16(pq[0], pq[1]), pack_bf16(pq[2], pq[3]), pack_bf16(pq[4], pq[5]),
+                               pack_bf16(pq[6], pq[7]));
+            }
         }
     }
+    uint32_t bar_load_parity = 0;
+    if (kWithP) fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     if (kWithP) {
-        uint4* dst = reinterpret_cast<uint4*>(p.p_out + (static_cast<long long>(blockIdx.x) * p.vh + head) * 4096);
-        for (int idx = tid; idx < 512; idx += 128) dst[idx] = *reinterpret_cast<const uint4*>(sV + stage_off<64>(idx >> 3, idx & 7));
-        fence_proxy_async_smem();
-        __syncthreads();  // staging read out: the buffer may now receive the V tile
+        // (fence + barrier above: staged P complete and visible to the TMA engine)
         if (tid == 0) {
+            tma_store_2d(&tmPo, sV, 0, (blockIdx.x * p.vh + head) * 64);
+            bulk_commit();
+            bulk_wait_read<0>();  // the buffer may now receive the V tile
             mbar_arrive_expect_tx(bar_load, L::kTile);
             for (int a = 0; a < NA; ++a)
                 tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
@@ -407,15 +402,26 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
                 v.y = pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
                 v.z = pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
                 v.w = pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-                *reinterpret_cast<uint4*>(stg + stage_off<D>(i, c0 / 8 + q)) = v;
+                *reinterpret_cast<uint4*>(stg + tile_off(i, c0 / 8 + q)) = v;
             }
         }
     }
+    fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
     GDN_STAMP(10);
-    store_staged_tile<D, 128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
-    store_staged_tile<D, 128>(stW, p.w, cp.batch, cp.tok0, head, n, tid);
+    if (p.map.cu_seqlens != nullptr && n < kChunk) {
+        // a full-box store would spill into the next packed sequence: row-predicated stores
+        store_tile_rows<128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
+        store_tile_rows<128>(stW, p.w, cp.batch, cp.tok0, head, n, tid);
+    } else if (tid == 0) {
+        for (int a = 0; a < NA; ++a) {
+            tma_store_4d(&tmUo, stU + a * 8192, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+            tma_store_4d(&tmWo, stW + a * 8192, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+        }
+        bulk_commit();
+        bulk_wait_read<0>();
+    }
     GDN_STAMP(11);
     if (warp == 0) tmem_dealloc(tmem, D);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 2);

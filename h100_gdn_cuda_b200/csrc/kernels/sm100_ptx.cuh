@@ -57,25 +57,25 @@ GDN_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Wait for the phase with the given parity to complete.  Gives up after about
-// `kWaitLimitNs` of wall time, or at once when another thread of the CTA has
-// already given up (`*abort_flag != 0`).  Returns false on give-up and sets the flag.
-constexpr unsigned long long kWaitLimitNs = 2000ull * 1000ull * 1000ull;  // 2 s
-
-GDN_DEVICE unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+// `kWaitLimitCycles` SM clock cycles (a couple of seconds), or at once when another thread of
+// the CTA has already given up (`*abort_flag != 0`).  Returns false on give-up and sets the
+// flag.  The clock is read only once in a while, so a wait that succeeds soon costs a handful
+// of instructions.
+constexpr long long kWaitLimitCycles = 4000ll * 1000ll * 1000ll;
 
 GDN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag != 0) return false;
+    const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0) {
+        if ((++spins & 255u) == 0) {
             if (*abort_flag != 0) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
                 return false;
             }
@@ -129,6 +129,30 @@ GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* 
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
+}
+
+// ------------------------------------------------------------------ TMA stores (shared -> global)
+GDN_DEVICE void tma_store_4d(const void* tmap, const void* src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+GDN_DEVICE void tma_store_2d(const void* tmap, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+GDN_DEVICE void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until at most N of this thread's bulk groups still have to read their shared-memory source
+template <int N>
+GDN_DEVICE void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+GDN_DEVICE void bulk_wait_all() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ------------------------------------------------------------------ tensor memory
