@@ -193,25 +193,32 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const float* gb = gate_buf(c);
             mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);  // gate values visible
             // ---- U_new^T -> two bf16 operand copies (rows past the end zeroed)
+            // decay factors of this thread's 32 tokens, zero past the end of the sequence: read
+            // while the MMA is still running
+            float dec[32];
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4) {
+                const float4 t = *reinterpret_cast<const float4*>(gb + 64 + 32 * hf + 4 * e4);
+                dec[4 * e4] = t.x; dec[4 * e4 + 1] = t.y; dec[4 * e4 + 2] = t.z; dec[4 * e4 + 3] = t.w;
+            }
+            const int nloc = n - 32 * hf;  // tokens of this half that exist
             mbar_wait(bar_d1, par, abort_flag);
             tc_fence_after_sync();
             if (c == 4 && tid == 0) GDN_STAMP_ANY(40);
-#pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-                uint32_t r[16];
-                tmem_ld16(tmem + kTmD1 + tm_lane + 32 * hf + 16 * h2, r);
+            {
+                uint32_t r[32];
+                tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);
                 tmem_wait_ld();
-                uint32_t wa[8], wb[8];
+                uint32_t wa[16], wb[16];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int i0 = 32 * hf + 16 * h2 + 2 * e;
-                    const float u0 = i0 < n ? __uint_as_float(r[2 * e]) : 0.f;
-                    const float u1 = i0 + 1 < n ? __uint_as_float(r[2 * e + 1]) : 0.f;
+                for (int e = 0; e < 16; ++e) {
+                    const float u0 = 2 * e < nloc ? __uint_as_float(r[2 * e]) : 0.f;
+                    const float u1 = 2 * e + 1 < nloc ? __uint_as_float(r[2 * e + 1]) : 0.f;
                     wa[e] = pack_bf16(u0, u1);
-                    wb[e] = pack_bf16(u0 * gb[64 + i0], u1 * gb[64 + i0 + 1]);
+                    wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
                 }
-                tmem_st8(tmem + kTmUnA + tm_lane + 16 * hf + 8 * h2, wa);
-                tmem_st8(tmem + kTmUnB + tm_lane + 16 * hf + 8 * h2, wb);
+                tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
+                tmem_st16(tmem + kTmUnB + tm_lane + 16 * hf, wb);
             }
             tmem_wait_st();
             tc_fence_before_sync();
@@ -267,14 +274,25 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a) + tm_lane;
             const uint32_t tO2 = tmem + kTmO2 + tm_lane;
             mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
+            if (c == 4 && otid == 0) GDN_STAMP_ANY(49);
             mbar_wait(bar_o, par, abort_flag);
             tc_fence_after_sync();
+            if (c == 4 && otid == 0) GDN_STAMP_ANY(50);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 uint32_t r1[16], r2[16];
                 tmem_ld16(tO1 + 16 * b, r1);
                 tmem_ld16(tO2 + 16 * b, r2);
+                // the gate factors of this batch are read before any store to the staging tile, so
+                // that the loads do not queue up behind the stores they might alias
+                float gv[16];
+#pragma unroll
+                for (int e4 = 0; e4 < 4; ++e4) {
+                    const float4 t = *reinterpret_cast<const float4*>(gb + 16 * b + 4 * e4);
+                    gv[4 * e4] = t.x; gv[4 * e4 + 1] = t.y; gv[4 * e4 + 2] = t.z; gv[4 * e4 + 3] = t.w;
+                }
                 tmem_wait_ld();
+                if (c == 4 && otid == 0) GDN_STAMP_ANY(53 + 2 * b);
                 if (b == 3) {
                     tc_fence_before_sync();
                     __syncwarp();
@@ -283,10 +301,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const int i = 16 * b + e;
-                    const float o = fmaf(gb[i], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
+                    const float o = fmaf(gv[e], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
                     *reinterpret_cast<__nv_bfloat16*>(sO + i * 128 + off8[i & 7]) = __float2bfloat16(o);
                 }
+                if (c == 4 && otid == 0) GDN_STAMP_ANY(54 + 2 * b);
             }
+            if (c == 4 && otid == 0) GDN_STAMP_ANY(51);
             const long long tok0 = seq_tok0 + static_cast<long long>(c) * kChunk;
             const bool ragged = packed && n < kChunk;  // a full-box store would spill into the next sequence
             fence_proxy_async_smem();
@@ -301,6 +321,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             } else {
                 store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid);
             }
+            if (c == 4 && otid == 0) GDN_STAMP_ANY(52);
         }
         if (otid == 0) bulk_wait_read<0>();
     } else if (warp == 12) {
@@ -357,18 +378,32 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             constexpr uint32_t id_sw = make_idesc_bf16(128, 64, false, false, true);
             constexpr uint32_t id_sq = make_idesc_bf16(128, 64, false, false);
             constexpr uint32_t id_ds = make_idesc_bf16(128, 128, false, true);
+            // one base descriptor per tile and stage; K-steps are constant offsets from them
+            uint64_t dU[2], dW[2], dQ[2], dK[2], dP[2];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                const uint32_t st = smem_u32(smem + s * L::kStage);
+                dU[s] = make_smem_desc_sw128(st + L::kOffU, 8192, 1024);  // MN-major A
+                dW[s] = make_smem_desc_sw128(st + L::kOffW, 0, 1024);     // K-major B
+                dQ[s] = make_smem_desc_sw128(st + L::kOffQ, 0, 1024);     // K-major B
+                dK[s] = make_smem_desc_sw128(st + L::kOffK, 8192, 1024);  // MN-major B
+                dP[s] = make_smem_desc_sw128(st + L::kOffP, 0, 1024);     // K-major B
+            }
+            const uint64_t dI = make_smem_desc_sw128(smem_u32(sI), 0, 1024);
+            const uint32_t tS = tmem + kTmSbf, tD1 = tmem + kTmD1, tDS = tmem + kTmDS, tO2 = tmem + kTmO2;
+            const uint32_t tUa = tmem + kTmUnA, tUb = tmem + kTmUnB;
             for (int c = 0; c < nchunks; ++c) {
                 const int s = c & 1;
                 const uint32_t par = static_cast<uint32_t>(c & 1);
-                const uint32_t st = smem_u32(smem + s * L::kStage);
+                const uint64_t u = dU[s], w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(30);
                 // D1 = U^T I  (does not need the state)
+                mma_ss_c<false>(tD1, u, dI, id_ui);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ss(tmem + kTmD1, make_smem_desc_sw128(st + L::kOffU + ks * 2048, 8192, 1024),
-                           make_smem_desc_sw128(smem_u32(sI) + ks * 32, 0, 1024), id_ui, ks > 0);
+                for (int ks = 1; ks < 4; ++ks)
+                    mma_ss_c<true>(tD1, desc_advance(u, ks * 2048), desc_advance(dI, ks * 32), id_ui);
                 if (c == 4) GDN_STAMP_ANY(31);
                 mbar_wait(bar_sbf, par, abort_flag);
                 tc_fence_after_sync();
@@ -376,25 +411,23 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // D1 -= S_bf W^T
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    mma_ts(tmem + kTmD1, tmem + kTmSbf + ks * 8,
-                           make_smem_desc_sw128(st + L::kOffW + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sw, 1);
+                    mma_ts_c<true>(tD1, tS + ks * 8, desc_advance(w, kmajor_step(ks, 8192)), id_sw);
                 mma_commit(bar_d1);
                 if (c == 4) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
                 const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
+                mma_ts_c<false>(tO1, tS, q, id_sq);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_ts(tO1, tmem + kTmSbf + ks * 8,
-                           make_smem_desc_sw128(st + L::kOffQ + (ks / 4) * 8192 + (ks % 4) * 32, 0, 1024), id_sq, ks > 0);
+                for (int ks = 1; ks < 8; ++ks)
+                    mma_ts_c<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
                 if (c == 4) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(35);
                 // dS = Un_b K
+                mma_ts_c<false>(tDS, tUb, k, id_ds);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ts(tmem + kTmDS, tmem + kTmUnB + ks * 8,
-                           make_smem_desc_sw128(st + L::kOffK + ks * 2048, 8192, 1024), id_ds, ks > 0);
+                for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tDS, tUb + ks * 8, desc_advance(k, ks * 2048), id_ds);
                 mma_commit(bar_ds);
                 if (c == 4) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
@@ -402,10 +435,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
                     tc_fence_after_sync();
                 }
+                mma_ts_c<false>(tO2, tUa, pp, id_sq);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    mma_ts(tmem + kTmO2, tmem + kTmUnA + ks * 8,
-                           make_smem_desc_sw128(st + L::kOffP + ks * 32, 0, 1024), id_sq, ks > 0);
+                for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
                 mma_commit(bar_o);
                 mma_commit(&bar_empty[s]);
                 if (c == 4) GDN_STAMP_ANY(37);

@@ -207,18 +207,29 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
+        const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sK), 0, 1024);
+        const uint64_t dk1 = desc_advance(dk0, 32 * 128);  // rows 32-63 of the K tile
+        const uint64_t dq0 = make_smem_desc_sw128(smem_u32(sV), 0, 1024);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks / 4) * 8192 + (ks % 4) * 32;
-            const uint64_t a = make_smem_desc_sw128(smem_u32(sK) + off, 0, 1024);
-            const uint64_t b0 = a;
-            const uint64_t b1 = make_smem_desc_sw128(smem_u32(sK) + off + 32 * 128, 0, 1024);
-            mma_ss(tLo, a, b0, idesc, ks > 0);
-            mma_ss(tHi, a, b1, idesc, ks > 0);
+            const uint32_t off = kmajor_step(ks, 8192);
+            const uint64_t a = desc_advance(dk0, off), b1 = desc_advance(dk1, off);
+            if (ks == 0) {
+                mma_ss_c<false>(tLo, a, a, idesc);
+                mma_ss_c<false>(tHi, a, b1, idesc);
+            } else {
+                mma_ss_c<true>(tLo, a, a, idesc);
+                mma_ss_c<true>(tHi, a, b1, idesc);
+            }
             if (kWithP) {  // Q K^T the same way, into columns 32-63
-                const uint64_t q = make_smem_desc_sw128(smem_u32(sV) + off, 0, 1024);
-                mma_ss(tLo + 32, q, b0, idesc, ks > 0);
-                mma_ss(tHi + 32, q, b1, idesc, ks > 0);
+                const uint64_t q = desc_advance(dq0, off);
+                if (ks == 0) {
+                    mma_ss_c<false>(tLo + 32, q, a, idesc);
+                    mma_ss_c<false>(tHi + 32, q, b1, idesc);
+                } else {
+                    mma_ss_c<true>(tLo + 32, q, a, idesc);
+                    mma_ss_c<true>(tHi + 32, q, b1, idesc);
+                }
             }
         }
         mma_commit(bar_mma);
@@ -365,18 +376,16 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     if (tid == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
+        const uint64_t dt1 = make_smem_desc_sw128(smem_u32(sT), 0, 1024);
+        const uint64_t dt2 = make_smem_desc_sw128(smem_u32(sT2), 0, 1024);
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), 8192, 1024);
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 8192, 1024);
+        mma_ss_c<false>(tLo, dt1, dv, idesc);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t a1 = make_smem_desc_sw128(smem_u32(sT) + ks * 32, 0, 1024);
-            const uint64_t b1 = make_smem_desc_sw128(smem_u32(sV) + ks * 2048, 8192, 1024);
-            mma_ss(tLo, a1, b1, idesc, ks > 0);
-        }
+        for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(tLo, desc_advance(dt1, ks * 32), desc_advance(dv, ks * 2048), idesc);
+        mma_ss_c<false>(tHi, dt2, dk, idesc);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t a2 = make_smem_desc_sw128(smem_u32(sT2) + ks * 32, 0, 1024);
-            const uint64_t b2 = make_smem_desc_sw128(smem_u32(sK) + ks * 2048, 8192, 1024);
-            mma_ss(tHi, a2, b2, idesc, ks > 0);
-        }
+        for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(tHi, desc_advance(dt2, ks * 32), desc_advance(dk, ks * 2048), idesc);
         mma_commit(bar_mma);
     }
     __syncwarp();

@@ -273,6 +273,41 @@ GDN_DEVICE void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Variants with the accumulate flag fixed at compile time (no predicate set-up per MMA).
+template <bool kAccumulate>
+GDN_DEVICE void mma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    if (kAccumulate)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+                     "l"(a_desc), "l"(b_desc), "r"(idesc)
+                     : "memory");
+}
+template <bool kAccumulate>
+GDN_DEVICE void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    if (kAccumulate)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+                     "r"(a_tmem), "l"(b_desc), "r"(idesc)
+                     : "memory");
+}
+// Descriptor of the same tile `bytes` further on (the start-address field counts 16-byte units;
+// callers stay within the 256 KB the 14-bit field covers, so the add never carries out of it).
+GDN_DEVICE uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+// byte offset of K-step `ks` (16 bf16) inside a K-major tile of 64-column atoms `atom_bytes` apart
+__host__ __device__ constexpr uint32_t kmajor_step(int ks, uint32_t atom_bytes) {
+    return static_cast<uint32_t>(ks / 4) * atom_bytes + static_cast<uint32_t>(ks % 4) * 32u;
+}
+
 // Make `bar` complete one arrival when every MMA issued so far by this thread is done.
 GDN_DEVICE void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
