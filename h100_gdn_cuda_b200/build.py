@@ -70,5 +70,63 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+EXT_DIR = os.path.join(CSRC, "torch_ext")
+
+
+def ext_path() -> str:
+    import sysconfig
+    return os.path.join(PKG, "gdn_cuda" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_ext(force: bool = False) -> str:
+    """Builds the pybind11/torch extension `gdn_cuda` (C++ host layer over the C ABI) in-tree."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension
+    lib = build(force=False)
+    out = ext_path()
+    srcs = [os.path.join(EXT_DIR, f) for f in ("gdn_api.cpp", "python_api.cpp")]
+    newest = max(os.path.getmtime(f) for f in srcs + [os.path.join(EXT_DIR, "gdn_api.hpp"),
+                                                       os.path.join(PKG, "..", "include", "gdn_b200.h")])
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= newest:
+        return out
+    inc = cpp_extension.include_paths("cuda") if hasattr(cpp_extension, "include_paths") else []
+    try:
+        inc = cpp_extension.include_paths(device_type="cuda")
+    except TypeError:
+        inc = cpp_extension.include_paths(True)
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_home = os.path.dirname(os.path.dirname(nvcc_path()))
+    objs = []
+
+    def cc(src):
+        obj = os.path.join(OBJDIR, os.path.basename(src).replace(".cpp", ".ext.o"))
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=gdn_cuda", "-DTORCH_API_INCLUDE_EXTENSION_H",
+               "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+               "-I", os.path.join(PKG, "..", "include"), "-I", sysconfig.get_paths()["include"],
+               "-I", os.path.join(cuda_home, "include")]
+        for i in inc:
+            cmd += ["-isystem", i]
+        cmd += ["-c", src, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("g++ failed for %s:\n%s" % (src, r.stderr[-4000:]))
+        return obj
+
+    os.makedirs(OBJDIR, exist_ok=True)
+    with ThreadPoolExecutor(max_workers=2) as ex:
+        objs = list(ex.map(cc, srcs))
+    cmd = ["g++", "-shared", "-o", out + ".tmp", *objs, "-L", tlib, "-L", LIBDIR, "-lgdn_b200", "-ltorch", "-ltorch_cpu",
+           "-ltorch_cuda", "-lc10", "-lc10_cuda", "-ltorch_python", "-L", os.path.join(cuda_home, "lib64"), "-lcudart",
+           "-Wl,-rpath,$ORIGIN/lib", "-Wl,-rpath," + tlib]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed:\n%s" % r.stderr[-4000:])
+    os.replace(out + ".tmp", out)
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--ext" in sys.argv:
+        print(build_ext(force="--force" in sys.argv))

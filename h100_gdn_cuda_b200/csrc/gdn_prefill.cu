@@ -2,6 +2,7 @@
 // construction, argument checks and launches of the tcgen05 kernels.
 #include "host_common.hpp"
 #include "kernels/prefill_fused.cuh"
+#include "kernels/prefill_o.cuh"
 #include "kernels/prefill_seq.cuh"
 #include "kernels/prefill_uw.cuh"
 #include "tma_host.hpp"
@@ -195,8 +196,48 @@ int gdn_seq_state_update(const GdnSeqStateArgs* a, gdn_stream_t stream) {
 }
 
 int gdn_compute_o(const GdnComputeOArgs* a, gdn_stream_t stream) {
-    (void)a; (void)stream;
-    return fail(GDN_ERR_UNSUPPORTED, "gdn_compute_o: not built yet");
+    GDN_REQUIRE(a != nullptr, "gdn_compute_o: args is NULL");
+    const GdnShape& s = a->shape;
+    if (int rc = check_shape(s, true)) return rc;
+    if (int rc = require_d128(s, "gdn_compute_o")) return rc;
+    if (int rc = check_token_tensor(a->q, "q", kD)) return rc;
+    if (int rc = check_token_tensor(a->k, "k", kD)) return rc;
+    if (int rc = check_token_tensor(a->u_new, "u", kD)) return rc;
+    if (int rc = check_token_tensor(a->out, "o", kD)) return rc;
+    if (int rc = check_scalar(a->gate_cumsum, "gate", false)) return rc;
+    GDN_REQUIRE(a->chunk_states != nullptr && aligned16(a->chunk_states), "gdn_compute_o: chunk_states must be a 16-byte aligned pointer");
+    GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
+    const int nc = num_chunks(s);
+    if (nc == 0) return GDN_OK;
+    const long long units = static_cast<long long>(nc) * s.num_v_heads;
+    GDN_REQUIRE(units * 128 < (1ll << 31), "gdn_compute_o: too many (chunk, head) units");
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    CUtensorMap tmQ, tmK, tmU, tmH, tmO;
+    if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
+    if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
+    if (int rc = make_token_map(&tmU, a->u_new, s, s.num_v_heads, "u")) return rc;
+    if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "o")) return rc;
+    {
+        uint64_t dims[2] = {128, static_cast<uint64_t>(units) * 128};
+        uint64_t strides[1] = {256};
+        uint32_t box[2] = {64, 128};
+        if (!make_tmap_bf16(&tmH, a->chunk_states, 2, dims, strides, box, true))
+            return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of the chunk states");
+    }
+    OParams p{};
+    p.map = chunk_map(s);
+    p.gate = scalar_view(a->gate_cumsum);
+    p.out = token_view(a->out);
+    p.kh = s.num_k_heads;
+    p.vh = s.num_v_heads;
+    p.scale = a->scale;
+    p.status = d->status;
+    constexpr int smem = OSmem::kBytes;
+    if (int rc = set_smem(gdn_o_kernel, smem)) return rc;
+    gdn_o_kernel<<<dim3(nc, s.num_v_heads), 128, smem, static_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmU, tmH, tmO, p);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
 }
 
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {

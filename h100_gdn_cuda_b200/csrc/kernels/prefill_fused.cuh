@@ -52,7 +52,7 @@ struct FusedSmem {
 };
 
 namespace fused {
-constexpr int kThreads = 448;
+constexpr int kThreads = 512;  // 16 warps = 4 warpgroups (the last holds the producer, the issuer and 2 idle warps)
 constexpr uint32_t kTmSbf = 0;    // bf16 state, 64 columns
 constexpr uint32_t kTmUnA = 64;   // bf16 U_new^T, 32 columns
 constexpr uint32_t kTmUnB = 96;   // bf16 U_new^T .* decay, 32 columns
@@ -62,6 +62,15 @@ constexpr uint32_t kTmDS = 256;   // fp32 state increment, 128 columns
 constexpr uint32_t kTmO1b = 384;  // fp32 S Q^T, odd chunks
 constexpr uint32_t kTmO2 = 448;   // fp32 U_new^T P^T
 
+// Register re-allocation between warpgroups (every warp of the warpgroup executes it).
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -78,7 +87,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     constexpr int D = 128;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sI = smem + L::kOffI;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* bar_full = bars;        // [2]
     uint64_t* bar_empty = bars + 2;   // [2]
@@ -131,20 +139,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, 512);
-    // identity tile (bf16 1.0 = 0x3F80), K-major swizzled
-    for (int idx = tid; idx < 64 * 8; idx += kThreads) {
-        const int r = idx >> 3, ch = idx & 7;
-        uint32_t w0 = 0, w1 = 0, w2 = 0, w3 = 0;
-        if ((r >> 3) == ch) {
-            const uint32_t v = (r & 1) ? 0x3F800000u : 0x00003F80u;
-            const int wi = (r & 7) >> 1;
-            w0 = wi == 0 ? v : 0;
-            w1 = wi == 1 ? v : 0;
-            w2 = wi == 2 ? v : 0;
-            w3 = wi == 3 ? v : 0;
-        }
-        *reinterpret_cast<uint4*>(sI + sw128_offset(r, ch * 8)) = make_uint4(w0, w1, w2, w3);
-    }
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -153,9 +147,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 
     if (warp < 8) {
         // =============================================================== state warps
+        reg_inc<168>();
         const int lq = warp & 3, hf = warp >> 2;
         const int row = 32 * lq + lane;
         const uint32_t tm_lane = static_cast<uint32_t>(32 * lq) << 16;
+        // element (token i, this row) of a swizzled 64 x 128 tile: i * 128 + uoff8[i & 7]
+        uint32_t uoff8[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            uoff8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
         float S[64];
         if (p.state_in) {
             const uint4* src = reinterpret_cast<const uint4*>(p.state_in + seq * p.si_ss + head * p.si_sh +
@@ -192,14 +192,17 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const int n = chunk_n(c);
             const float* gb = gate_buf(c);
             mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);  // gate values visible
-            // ---- U_new^T -> two bf16 operand copies (rows past the end zeroed)
-            // decay factors of this thread's 32 tokens, zero past the end of the sequence: read
-            // while the MMA is still running
-            float dec[32];
+            // ---- U_new^T = U^T - S W^T -> two bf16 operand copies (rows past the end zeroed)
+            // This thread's 32 values of U^T come straight from the TMA tile (element (token, row)
+            // of the swizzled layout), packed two tokens per register while the MMA is running.
+            const uint8_t* sU = smem + (c & 1) * L::kStage + L::kOffU;
+            uint32_t upk[16];
 #pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4) {
-                const float4 t = *reinterpret_cast<const float4*>(gb + 64 + 32 * hf + 4 * e4);
-                dec[4 * e4] = t.x; dec[4 * e4 + 1] = t.y; dec[4 * e4 + 2] = t.z; dec[4 * e4 + 3] = t.w;
+            for (int e = 0; e < 16; ++e) {
+                const int i0 = 32 * hf + 2 * e;
+                const uint32_t lo = *reinterpret_cast<const uint16_t*>(sU + i0 * 128 + uoff8[i0 & 7]);
+                const uint32_t hi = *reinterpret_cast<const uint16_t*>(sU + (i0 + 1) * 128 + uoff8[(i0 + 1) & 7]);
+                upk[e] = lo | (hi << 16);
             }
             const int nloc = n - 32 * hf;  // tokens of this half that exist
             mbar_wait(bar_d1, par, abort_flag);
@@ -207,13 +210,19 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (c == 4 && tid == 0) GDN_STAMP_ANY(40);
             {
                 uint32_t r[32];
-                tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);
+                tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);  // -(S W^T)
+                float dec[32];
+#pragma unroll
+                for (int e4 = 0; e4 < 8; ++e4) {
+                    const float4 t = *reinterpret_cast<const float4*>(gb + 64 + 32 * hf + 4 * e4);
+                    dec[4 * e4] = t.x; dec[4 * e4 + 1] = t.y; dec[4 * e4 + 2] = t.z; dec[4 * e4 + 3] = t.w;
+                }
                 tmem_wait_ld();
                 uint32_t wa[16], wb[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const float u0 = 2 * e < nloc ? __uint_as_float(r[2 * e]) : 0.f;
-                    const float u1 = 2 * e + 1 < nloc ? __uint_as_float(r[2 * e + 1]) : 0.f;
+                    const float u0 = 2 * e < nloc ? bf16_lo(upk[e]) + __uint_as_float(r[2 * e]) : 0.f;
+                    const float u1 = 2 * e + 1 < nloc ? bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]) : 0.f;
                     wa[e] = pack_bf16(u0, u1);
                     wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
                 }
@@ -256,6 +265,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         }
     } else if (warp < 12) {
         // =============================================================== output warps
+        reg_dec<88>();
         const int lq = warp & 3;
         const int row = 32 * lq + lane;  // dv index = TMEM lane
         const int otid = tid - 256;
@@ -324,7 +334,10 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (c == 4 && otid == 0) GDN_STAMP_ANY(52);
         }
         if (otid == 0) bulk_wait_read<0>();
-    } else if (warp == 12) {
+    } else {
+        reg_dec<40>();
+    }
+    if (warp == 12) {
         // =============================================================== producer
         for (int c = 0; c < nchunks; ++c) {
             const int s = c & 1;
@@ -371,75 +384,69 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 tma_load_2d(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
             }
         }
-    } else {
-        // =============================================================== MMA issuer (one thread)
-        if (lane == 0) {
-            constexpr uint32_t id_ui = make_idesc_bf16(128, 64, true, false);
+    } else if (warp == 13) {
+        // =============================================================== MMA issuer
+        // The whole warp runs this loop with warp-uniform values; one elected lane issues.
+        {
             constexpr uint32_t id_sw = make_idesc_bf16(128, 64, false, false, true);
             constexpr uint32_t id_sq = make_idesc_bf16(128, 64, false, false);
             constexpr uint32_t id_ds = make_idesc_bf16(128, 128, false, true);
             // one base descriptor per tile and stage; K-steps are constant offsets from them
-            uint64_t dU[2], dW[2], dQ[2], dK[2], dP[2];
+            uint64_t dW[2], dQ[2], dK[2], dP[2];
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
                 const uint32_t st = smem_u32(smem + s * L::kStage);
-                dU[s] = make_smem_desc_sw128(st + L::kOffU, 8192, 1024);  // MN-major A
                 dW[s] = make_smem_desc_sw128(st + L::kOffW, 0, 1024);     // K-major B
                 dQ[s] = make_smem_desc_sw128(st + L::kOffQ, 0, 1024);     // K-major B
                 dK[s] = make_smem_desc_sw128(st + L::kOffK, 8192, 1024);  // MN-major B
                 dP[s] = make_smem_desc_sw128(st + L::kOffP, 0, 1024);     // K-major B
             }
-            const uint64_t dI = make_smem_desc_sw128(smem_u32(sI), 0, 1024);
             const uint32_t tS = tmem + kTmSbf, tD1 = tmem + kTmD1, tDS = tmem + kTmDS, tO2 = tmem + kTmO2;
             const uint32_t tUa = tmem + kTmUnA, tUb = tmem + kTmUnB;
             for (int c = 0; c < nchunks; ++c) {
                 const int s = c & 1;
                 const uint32_t par = static_cast<uint32_t>(c & 1);
-                const uint64_t u = dU[s], w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
+                const uint64_t w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(30);
-                // D1 = U^T I  (does not need the state)
-                mma_ss_c<false>(tD1, u, dI, id_ui);
-#pragma unroll
-                for (int ks = 1; ks < 4; ++ks)
-                    mma_ss_c<true>(tD1, desc_advance(u, ks * 2048), desc_advance(dI, ks * 32), id_ui);
                 if (c == 4) GDN_STAMP_ANY(31);
                 mbar_wait(bar_sbf, par, abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(32);
-                // D1 -= S_bf W^T
+                // D1 = -(S_bf W^T)
+                mma_ts_w<false>(tD1, tS, w, id_sw);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                    mma_ts_c<true>(tD1, tS + ks * 8, desc_advance(w, kmajor_step(ks, 8192)), id_sw);
-                mma_commit(bar_d1);
+                for (int ks = 1; ks < 8; ++ks)
+                    mma_ts_w<true>(tD1, tS + ks * 8, desc_advance(w, kmajor_step(ks, 8192)), id_sw);
+                mma_commit_w(bar_d1);
                 if (c == 4) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
                 const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
-                mma_ts_c<false>(tO1, tS, q, id_sq);
+                mma_ts_w<false>(tO1, tS, q, id_sq);
 #pragma unroll
                 for (int ks = 1; ks < 8; ++ks)
-                    mma_ts_c<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
+                    mma_ts_w<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
                 if (c == 4) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(35);
                 // dS = Un_b K
-                mma_ts_c<false>(tDS, tUb, k, id_ds);
+                mma_ts_w<false>(tDS, tUb, k, id_ds);
 #pragma unroll
-                for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tDS, tUb + ks * 8, desc_advance(k, ks * 2048), id_ds);
-                mma_commit(bar_ds);
+                for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tDS, tUb + ks * 8, desc_advance(k, ks * 2048), id_ds);
+                mma_commit_w(bar_ds);
                 if (c == 4) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
                 if (c > 0) {
                     mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
                     tc_fence_after_sync();
                 }
-                mma_ts_c<false>(tO2, tUa, pp, id_sq);
+                mma_ts_w<false>(tO2, tUa, pp, id_sq);
 #pragma unroll
-                for (int ks = 1; ks < 4; ++ks) mma_ts_c<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
-                mma_commit(bar_o);
-                mma_commit(&bar_empty[s]);
+                for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
+                mma_commit_w(bar_o);
+                mma_commit_w(&bar_empty[s]);
                 if (c == 4) GDN_STAMP_ANY(37);
                 if (c == 5) GDN_STAMP_ANY(38);
             }

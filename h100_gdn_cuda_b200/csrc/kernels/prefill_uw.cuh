@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
     mbar_wait(bar_load, 0, abort_flag);
     GDN_STAMP(2);
-    if (tid == 0) {
+    if (warp == 0) {  // warp-uniform issue, one elected lane
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
         const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sK), 0, 1024);
@@ -215,24 +215,24 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
             const uint32_t off = kmajor_step(ks, 8192);
             const uint64_t a = desc_advance(dk0, off), b1 = desc_advance(dk1, off);
             if (ks == 0) {
-                mma_ss_c<false>(tLo, a, a, idesc);
-                mma_ss_c<false>(tHi, a, b1, idesc);
+                mma_ss_w<false>(tLo, a, a, idesc);
+                mma_ss_w<false>(tHi, a, b1, idesc);
             } else {
-                mma_ss_c<true>(tLo, a, a, idesc);
-                mma_ss_c<true>(tHi, a, b1, idesc);
+                mma_ss_w<true>(tLo, a, a, idesc);
+                mma_ss_w<true>(tHi, a, b1, idesc);
             }
             if (kWithP) {  // Q K^T the same way, into columns 32-63
                 const uint64_t q = desc_advance(dq0, off);
                 if (ks == 0) {
-                    mma_ss_c<false>(tLo + 32, q, a, idesc);
-                    mma_ss_c<false>(tHi + 32, q, b1, idesc);
+                    mma_ss_w<false>(tLo + 32, q, a, idesc);
+                    mma_ss_w<false>(tHi + 32, q, b1, idesc);
                 } else {
-                    mma_ss_c<true>(tLo + 32, q, a, idesc);
-                    mma_ss_c<true>(tHi + 32, q, b1, idesc);
+                    mma_ss_w<true>(tLo + 32, q, a, idesc);
+                    mma_ss_w<true>(tHi + 32, q, b1, idesc);
                 }
             }
         }
-        mma_commit(bar_mma);
+        mma_commit_w(bar_mma);
     }
     __syncwarp();
     mbar_wait(bar_mma, 0, abort_flag);
@@ -373,20 +373,20 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     GDN_STAMP(8);
     // ---- U = T V (lanes +0), W = T' K (lanes +16)
     if (kWithP) mbar_wait(bar_load, bar_load_parity, abort_flag);
-    if (tid == 0) {
+    if (warp == 0) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
         const uint64_t dt1 = make_smem_desc_sw128(smem_u32(sT), 0, 1024);
         const uint64_t dt2 = make_smem_desc_sw128(smem_u32(sT2), 0, 1024);
         const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), 8192, 1024);
         const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 8192, 1024);
-        mma_ss_c<false>(tLo, dt1, dv, idesc);
+        mma_ss_w<false>(tLo, dt1, dv, idesc);
 #pragma unroll
-        for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(tLo, desc_advance(dt1, ks * 32), desc_advance(dv, ks * 2048), idesc);
-        mma_ss_c<false>(tHi, dt2, dk, idesc);
+        for (int ks = 1; ks < 4; ++ks) mma_ss_w<true>(tLo, desc_advance(dt1, ks * 32), desc_advance(dv, ks * 2048), idesc);
+        mma_ss_w<false>(tHi, dt2, dk, idesc);
 #pragma unroll
-        for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(tHi, desc_advance(dt2, ks * 32), desc_advance(dk, ks * 2048), idesc);
-        mma_commit(bar_mma);
+        for (int ks = 1; ks < 4; ++ks) mma_ss_w<true>(tHi, desc_advance(dt2, ks * 32), desc_advance(dk, ks * 2048), idesc);
+        mma_commit_w(bar_mma);
     }
     __syncwarp();
     mbar_wait(bar_mma, 1, abort_flag);

@@ -300,6 +300,40 @@ GDN_DEVICE void mma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint
                      "r"(a_tmem), "l"(b_desc), "r"(idesc)
                      : "memory");
 }
+// Warp-collective variants: the whole (converged) warp calls them with warp-uniform operands
+// and one elected lane issues the instruction.  Keeping the surrounding control flow
+// warp-uniform lets the descriptors live in uniform registers, which is what the instruction
+// consumes; issuing from inside an `if (lane == 0)` region costs tens of cycles per MMA in
+// register moves.
+template <bool kAccumulate>
+GDN_DEVICE void mma_ss_w(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t.reg .pred pa;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %4, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pa;\n\t}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+        : "memory");
+}
+template <bool kAccumulate>
+GDN_DEVICE void mma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t.reg .pred pa;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %4, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pa;\n\t}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+        : "memory");
+}
+GDN_DEVICE void mma_commit_w(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(
+            smem_u32(bar))
+        : "memory");
+}
+
 // Descriptor of the same tile `bytes` further on (the start-address field counts 16-byte units;
 // callers stay within the 256 KB the 14-bit field covers, so the add never carries out of it).
 GDN_DEVICE uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }

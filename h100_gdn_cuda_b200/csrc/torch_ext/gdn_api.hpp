@@ -1,0 +1,60 @@
+// C++ API `namespace gdn_cuda` over the C ABI of libgdn_b200.so, with the signatures of the
+// reference's csrc/apis/gdn_forward.hpp:15-73 (at::Tensor arguments, an explicit stream).
+// Errors are thrown as std::runtime_error (pybind turns them into RuntimeError).
+#pragma once
+#include <ATen/ATen.h>
+#include <cuda_runtime_api.h>
+
+#include <optional>
+#include <string>
+#include <utility>
+
+namespace gdn_cuda {
+
+enum class InferenceMode : int { Prefill = 0, Decode = 1, SpecVerify = 2, SpecDecode = 3 };
+
+void init(const std::string& library_root, const std::string& cuda_home);
+
+std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                                  at::Tensor& beta, at::Tensor& gate, std::optional<float> scale,
+                                                  std::optional<at::Tensor>& initial_state,
+                                                  std::optional<at::Tensor>& cu_seqlens,
+                                                  std::optional<at::Tensor>& chunk_indices,
+                                                  std::optional<at::Tensor>& cu_chunks,
+                                                  std::optional<int> total_chunks, cudaStream_t stream);
+
+std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                                    std::optional<at::Tensor>& initial_state, at::Tensor& beta,
+                                                    at::Tensor& gate, std::optional<at::Tensor>& cu_seqlens,
+                                                    std::optional<at::Tensor>& num_accepted_tokens,
+                                                    InferenceMode inference_mode, cudaStream_t stream,
+                                                    bool is_qk_norm, std::optional<float> scale);
+
+std::pair<at::Tensor, at::Tensor> fused_gdn_gating(at::Tensor& A_log, at::Tensor& dt_bias, at::Tensor& a,
+                                                   at::Tensor& b, bool is_var_len, cudaStream_t stream);
+
+void bf16_gdn_compute_u_w(at::Tensor& k, at::Tensor& v, at::Tensor& u, at::Tensor& w, at::Tensor& beta,
+                          std::optional<at::Tensor>& gate, const std::string& compiled_dims, cudaStream_t stream,
+                          std::optional<at::Tensor>& cu_seqlens, std::optional<at::Tensor>& chunk_indices);
+
+void bf16_chunked_seq_state_update(at::Tensor& k, at::Tensor& u, at::Tensor& w,
+                                   std::optional<at::Tensor>& initial_state, at::Tensor& state,
+                                   std::optional<at::Tensor>& final_state, std::optional<at::Tensor>& gate,
+                                   const std::string& compiled_dims, cudaStream_t stream,
+                                   std::optional<at::Tensor>& cu_seqlens, std::optional<at::Tensor>& cu_chunks,
+                                   std::optional<int> total_chunks, uint32_t chunk_size);
+
+void bf16_gdn_chunked_compute_O(at::Tensor& q, at::Tensor& state, at::Tensor& k, at::Tensor& u, at::Tensor& o,
+                                std::optional<at::Tensor>& gate, std::optional<float> scale,
+                                const std::string& compiled_dims, cudaStream_t stream,
+                                std::optional<at::Tensor>& cu_seqlens, std::optional<at::Tensor>& chunk_indices,
+                                std::optional<at::Tensor>& cu_chunks, std::optional<int> total_chunks,
+                                uint32_t chunk_size);
+
+void chunk_local_cumsum_bf16(at::Tensor& input, at::Tensor& output, int batch_size, int seq_len, int num_heads,
+                             bool head_first, std::optional<at::Tensor>& cu_seqlens,
+                             std::optional<at::Tensor>& chunk_indices, cudaStream_t stream);
+
+at::Tensor transpose_to_mn_major(at::Tensor& input, cudaStream_t stream, uint32_t alignment = 16);
+
+}  // namespace gdn_cuda

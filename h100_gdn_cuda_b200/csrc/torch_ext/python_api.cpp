@@ -1,0 +1,120 @@
+// pybind11 module `gdn_cuda`: the names, argument order, keywords and defaults of the reference's
+// csrc/python_api.cpp:17-393, forwarding to namespace gdn_cuda (gdn_api.hpp) on the current torch stream.
+#include <ATen/cuda/CUDAContext.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "gdn_api.hpp"
+
+namespace py = pybind11;
+
+static cudaStream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+PYBIND11_MODULE(gdn_cuda, m) {
+    m.doc() = "Gated DeltaNet kernels for B200 (sm_100a) behind the gdn_cuda API";
+
+    m.def("init", &gdn_cuda::init, py::arg("library_root"), py::arg("cuda_home"),
+          "Record the repository root and the CUDA toolkit root for the run-time kernel compiler.");
+
+    m.def(
+        "chunked_forward",
+        [](at::Tensor& q, at::Tensor& k, at::Tensor& v, at::Tensor& beta, at::Tensor& gate, std::optional<float> scale,
+           std::optional<at::Tensor> initial_state, std::optional<at::Tensor> cu_seqlens,
+           std::optional<at::Tensor> chunk_indices, std::optional<at::Tensor> cu_chunks,
+           std::optional<int> total_chunks) {
+            return gdn_cuda::chunked_forward(q, k, v, beta, gate, scale, initial_state, cu_seqlens, chunk_indices,
+                                             cu_chunks, total_chunks, current_stream());
+        },
+        py::arg("query"), py::arg("key"), py::arg("value"), py::arg("beta"), py::arg("gate"),
+        py::arg("scale") = py::none(), py::arg("initial_state") = py::none(), py::arg("cu_seqlens") = py::none(),
+        py::arg("chunk_indices") = py::none(), py::arg("cu_chunks") = py::none(), py::arg("total_chunks") = py::none(),
+        "Chunked (64-token) prefill.  query/key (B,T,kh,d)|(N,kh,d), value (B,T,vh,d)|(N,vh,d), beta bf16 and gate "
+        "fp32 (raw log-decay) (B,T,vh)|(N,vh), initial_state (B|S,vh,d,d) bf16.  Returns (output, final_state).");
+
+    m.def(
+        "recurrent_forward",
+        [](at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor> initial_state, at::Tensor& beta,
+           at::Tensor& gate, std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> num_accepted_tokens,
+           int inference_mode, bool is_qk_norm, std::optional<float> scale) {
+            return gdn_cuda::recurrent_forward(q, k, v, initial_state, beta, gate, cu_seqlens, num_accepted_tokens,
+                                               static_cast<gdn_cuda::InferenceMode>(inference_mode), current_stream(),
+                                               is_qk_norm, scale);
+        },
+        py::arg("query"), py::arg("key"), py::arg("value"), py::arg("initial_state") = py::none(), py::arg("beta"),
+        py::arg("gate"), py::arg("cu_seqlens") = py::none(), py::arg("num_accepted_tokens") = py::none(),
+        py::arg("inference_mode") = 0, py::arg("is_qk_norm") = false, py::arg("scale") = py::none(),
+        "Token recurrence for decode / speculative verify.  Returns (output, new_state); new_state holds one state "
+        "per token when inference_mode == SpecVerify.");
+
+    m.def(
+        "fused_gdn_gating",
+        [](at::Tensor& A_log, at::Tensor& dt_bias, at::Tensor& a, at::Tensor& b, bool is_var_len) {
+            return gdn_cuda::fused_gdn_gating(A_log, dt_bias, a, b, is_var_len, current_stream());
+        },
+        py::arg("A_log"), py::arg("dt_bias"), py::arg("a"), py::arg("b"), py::arg("is_var_len") = false,
+        "(beta, gate) = (sigmoid(b), -exp(A_log) * softplus(a + dt_bias)).");
+
+    m.def(
+        "bf16_gdn_compute_u_w",
+        [](at::Tensor& k, at::Tensor& v, at::Tensor& u, at::Tensor& w, at::Tensor& beta, std::optional<at::Tensor> gate,
+           const std::string& compiled_dims, std::optional<at::Tensor> cu_seqlens,
+           std::optional<at::Tensor> chunk_indices) {
+            gdn_cuda::bf16_gdn_compute_u_w(k, v, u, w, beta, gate, compiled_dims, current_stream(), cu_seqlens,
+                                           chunk_indices);
+        },
+        py::arg("k"), py::arg("v"), py::arg("u"), py::arg("w"), py::arg("beta"), py::arg("gate") = py::none(),
+        py::arg("compiled_dims") = "t", py::arg("cu_seqlens") = py::none(), py::arg("chunk_indices") = py::none(),
+        "Low-level WY/UT transform; writes u and w.");
+
+    m.def(
+        "bf16_chunked_seq_state_update",
+        [](at::Tensor& k, at::Tensor& u, at::Tensor& w, std::optional<at::Tensor>& initial_state, at::Tensor& state,
+           std::optional<at::Tensor>& final_state, std::optional<at::Tensor> gate, const std::string& compiled_dims,
+           std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> cu_chunks, std::optional<int> total_chunks,
+           uint32_t chunk_size) {
+            gdn_cuda::bf16_chunked_seq_state_update(k, u, w, initial_state, state, final_state, gate, compiled_dims,
+                                                    current_stream(), cu_seqlens, cu_chunks, total_chunks, chunk_size);
+        },
+        py::arg("k"), py::arg("u"), py::arg("w"), py::arg("initial_state"), py::arg("state"), py::arg("final_state"),
+        py::arg("gate") = py::none(), py::arg("compiled_dims") = "t", py::arg("cu_seqlens") = py::none(),
+        py::arg("cu_chunks") = py::none(), py::arg("total_chunks") = py::none(), py::arg("chunk_size") = 64u,
+        "Low-level chunk-to-chunk state pass; writes state, final_state and overwrites u with U_new.");
+
+    m.def(
+        "bf16_gdn_chunked_compute_O",
+        [](at::Tensor& q, at::Tensor& state, at::Tensor& k, at::Tensor& u, at::Tensor& o, std::optional<at::Tensor> gate,
+           std::optional<float> scale, const std::string& compiled_dims, std::optional<at::Tensor> cu_seqlens,
+           std::optional<at::Tensor> chunk_indices, std::optional<at::Tensor> cu_chunks, uint32_t chunk_size) {
+            gdn_cuda::bf16_gdn_chunked_compute_O(q, state, k, u, o, gate, scale, compiled_dims, current_stream(),
+                                                 cu_seqlens, chunk_indices, cu_chunks, std::nullopt, chunk_size);
+        },
+        py::arg("q"), py::arg("state"), py::arg("k"), py::arg("u"), py::arg("o"), py::arg("gate") = py::none(),
+        py::arg("scale") = py::none(), py::arg("compiled_dims") = "t", py::arg("cu_seqlens") = py::none(),
+        py::arg("chunk_indices") = py::none(), py::arg("cu_chunks") = py::none(), py::arg("chunk_size") = 64u,
+        "Low-level output stage; writes o.");
+
+    m.def(
+        "chunk_local_cumsum_bf16",
+        [](at::Tensor& input, at::Tensor& output, int batch_size, int seq_len, int num_heads, bool head_first,
+           std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> chunk_indices) {
+            gdn_cuda::chunk_local_cumsum_bf16(input, output, batch_size, seq_len, num_heads, head_first, cu_seqlens,
+                                              chunk_indices, current_stream());
+        },
+        py::arg("input"), py::arg("output"), py::arg("batch_size"), py::arg("seq_len"), py::arg("num_heads"),
+        py::arg("head_first") = false, py::arg("cu_seqlens") = py::none(), py::arg("chunk_indices") = py::none(),
+        "Chunk-local inclusive cumsum (bf16 or fp32 in, fp32 out).");
+
+    m.def(
+        "transpose_to_mn_major",
+        [](at::Tensor& input, uint32_t alignment) {
+            return gdn_cuda::transpose_to_mn_major(input, current_stream(), alignment);
+        },
+        py::arg("input"), py::arg("alignment") = 16u, "Transpose the last two dims to a stride(-2) == 1 layout.");
+
+    py::enum_<gdn_cuda::InferenceMode>(m, "InferenceMode")
+        .value("Prefill", gdn_cuda::InferenceMode::Prefill)
+        .value("Decode", gdn_cuda::InferenceMode::Decode)
+        .value("SpecVerify", gdn_cuda::InferenceMode::SpecVerify)
+        .export_values();
+}

@@ -214,3 +214,41 @@ def test_chunked_errors(gdn):
     big = torch.zeros(1, 64, 1, 256, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         gdn.chunked_forward(big, big, big, p["beta"], p["g"])
+
+
+@pytest.mark.parametrize("varlen", [False, True])
+def test_compute_o_stage(gdn, varlen):
+    """Low-level output stage from oracle-made per-chunk states and U_new; then the three
+    low-level stages chained equal the token recurrence."""
+    if varlen:
+        lens = [65, 1, 200, 64]
+        p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=18, mild_gate=True)
+        cu = p["cu_seqlens"]
+    else:
+        p = synthetic.prefill_inputs(2, 200, 2, 4, 128, seed=18, mild_gate=True)
+        cu = None
+    gc = O.chunk_local_cumsum_ref(p["g"], cu)
+    u_ref, w_ref = O.compute_u_w_ref(*f32(p, "k", "v", "beta"), gc, cu)
+    h_ref, un_ref, s_ref = O.seq_state_update_ref(p["k"].float(), u_ref, w_ref, gc, p["state"].float(), cu)
+    h_bf, un_bf = h_ref.bfloat16(), un_ref.bfloat16()
+    o_ref = O.compute_o_ref(p["q"].float(), p["k"].float(), un_bf.float(), h_bf.float(), gc, None, cu)
+    pd = dev(p)
+    kw = dict(cu_seqlens=pd["cu_seqlens"], chunk_indices=pd["chunk_indices"], cu_chunks=pd["cu_chunks"]) if varlen else {}
+    o = torch.full_like(pd["v"], float("nan"))
+    gdn.bf16_gdn_chunked_compute_O(pd["q"], h_bf.cuda(), pd["k"], un_bf.cuda(), o, gc.cuda(), **kw)
+    check_status(gdn)
+    close(o, o_ref, "O (stage)")
+    # chain of the three low-level wrappers == recurrence
+    u, w = torch.empty_like(pd["v"]), torch.empty_like(pd["v"])
+    kw_uw = dict(cu_seqlens=pd["cu_seqlens"], chunk_indices=pd["chunk_indices"]) if varlen else {}
+    gdn.bf16_gdn_compute_u_w(pd["k"], pd["v"], u, w, pd["beta"], gc.cuda(), **kw_uw)
+    state = torch.empty(h_ref.shape, dtype=torch.bfloat16, device="cuda")
+    final = torch.empty_like(pd["state"])
+    kw_st = dict(cu_seqlens=pd["cu_seqlens"], cu_chunks=pd["cu_chunks"], total_chunks=p["total_chunks"]) if varlen else {}
+    gdn.bf16_chunked_seq_state_update(pd["k"], u, w, pd["state"], state, final, gc.cuda(), **kw_st)
+    o2 = torch.empty_like(pd["v"])
+    gdn.bf16_gdn_chunked_compute_O(pd["q"], state, pd["k"], u, o2, gc.cuda(), **kw)
+    check_status(gdn)
+    o_rec, s_rec = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(), cu_seqlens=cu)
+    close(o2, o_rec, "O (three stages)")
+    close(final, s_rec, "final state (three stages)")
