@@ -43,8 +43,7 @@ struct FusedSmem {
     static constexpr int kTile = kChunk * D * 2;  // 16 KB
     static constexpr int kOffQ = 0, kOffK = kTile, kOffW = 2 * kTile, kOffU = 3 * kTile, kOffP = 4 * kTile;
     static constexpr int kStage = 4 * kTile + 8192;  // Q, K, W, U, P
-    static constexpr int kOffI = 2 * kStage;         // identity 64x64 bf16 K-major
-    static constexpr int kOffO = kOffI + 8192;       // two output staging tiles
+    static constexpr int kOffO = 2 * kStage;         // two output staging tiles
     static constexpr int kOffGate = kOffO + 2 * kTile;  // 3 x { e^g[64], e^{gL-g}[64], e^{gL} }
     static constexpr int kGateStride = (2 * 64 + 4) * 4;
     static constexpr int kOffBar = kOffGate + 3 * kGateStride;
@@ -339,18 +338,28 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     }
     if (warp == 12) {
         // =============================================================== producer
+        // Raw gate values are fetched two chunks ahead into registers (lane l holds tokens l and
+        // l + 32), so that when a stage frees up only the TMA issue remains to be done.
+        auto load_raw = [&](int c, float& a0, float& a1) {
+            a0 = 0.f;
+            a1 = 0.f;
+            if (p.gate.ptr && c < nchunks) {
+                const long long t0 = static_cast<long long>(c) * kChunk + lane;
+                if (t0 < seq_tokens) a0 = p.gate.load(batch, seq_tok0 + t0, head);
+                if (t0 + 32 < seq_tokens) a1 = p.gate.load(batch, seq_tok0 + t0 + 32, head);
+            }
+        };
+        float ra0, ra1, rb0, rb1;  // raw gates of chunks c and c + 1
+        load_raw(0, ra0, ra1);
+        load_raw(1, rb0, rb1);
         for (int c = 0; c < nchunks; ++c) {
             const int s = c & 1;
-            mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
-            // chunk-local cumulative gate: lane l holds tokens l and l + 32
-            float* gb = gate_buf(c);
             const int n = chunk_n(c);
-            float g0 = 0.f, g1 = 0.f;
-            if (p.gate.ptr) {
-                const long long t0 = static_cast<long long>(c) * kChunk + lane;
-                if (t0 < seq_tokens) g0 = p.gate.load(batch, seq_tok0 + t0, head);
-                if (t0 + 32 < seq_tokens) g1 = p.gate.load(batch, seq_tok0 + t0 + 32, head);
-            }
+            float g0 = ra0, g1 = ra1;
+            ra0 = rb0;
+            ra1 = rb1;
+            load_raw(c + 2, rb0, rb1);
+            // chunk-local cumulative gate
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1) {
                 const float y0 = __shfl_up_sync(0xffffffffu, g0, m);
@@ -363,11 +372,16 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             g1 += __shfl_sync(0xffffffffu, g0, 31);
             // tokens past the end carry the last valid value (their raw gate was taken as 0)
             const float g_last = __shfl_sync(0xffffffffu, (n - 1 < 32) ? g0 : g1, (n - 1) & 31);
-            gb[lane] = p.scale * __expf(g0);  // the epilogue's factor for S q (P already carries the scale)
-            gb[lane + 32] = p.scale * __expf(g1);
-            gb[64 + lane] = __expf(g_last - g0);
-            gb[64 + lane + 32] = __expf(g_last - g1);
-            if (lane == 0) gb[128] = __expf(g_last);
+            const float e0 = p.scale * __expf(g0), e1 = p.scale * __expf(g1);  // epilogue factor for S q
+            const float d0 = __expf(g_last - g0), d1 = __expf(g_last - g1);
+            const float el = __expf(g_last);
+            mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
+            float* gb = gate_buf(c);
+            gb[lane] = e0;
+            gb[lane + 32] = e1;
+            gb[64 + lane] = d0;
+            gb[64 + lane + 32] = d1;
+            if (lane == 0) gb[128] = el;
             __syncwarp();
             if (lane == 0) {
                 uint8_t* st = smem + s * L::kStage;
@@ -376,12 +390,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 mbar_arrive_expect_tx(&bar_full[s], L::kStage);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
-                    tma_load_4d(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
                     tma_load_4d(st + L::kOffW + a * 8192, &tmW, &bar_full[s], a * 64, head, tok, batch);
+                    tma_load_4d(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
+                }
+                tma_load_2d(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
                     tma_load_4d(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
                     tma_load_4d(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
                 }
-                tma_load_2d(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
             }
         }
     } else if (warp == 13) {

@@ -42,18 +42,15 @@ struct UWParams {
 template <int D>
 struct UWSmem {
     static constexpr int kTile = kChunk * D * 2;  // K or V tile; later the U / W staging tile
-    static constexpr int kLdA = 68;               // fp32 row strides chosen for conflict-free
-    static constexpr int kLdX = 68;               //   MMA fragment loads
-    static constexpr int kLdT = 40;
+    static constexpr int kLd = 68;                // fp32 row stride, conflict-free for MMA fragment loads
     static constexpr int kOffK = 0;
     static constexpr int kOffV = kOffK + kTile;
-    static constexpr int kOffA = kOffV + kTile;          // A fp32 [64][68]; later T and T' (8 KB each)
-    static constexpr int kOffX = kOffA + 64 * kLdA * 4;  // X fp32 [64][68]
-    static constexpr int kOffTmp = kOffX + 64 * kLdX * 4;  // fp32 [32][40]
-    static constexpr int kOffVec = kOffTmp + 32 * kLdT * 4;  // beta[64], g[64], e^g[64]
-    static constexpr int kOffBar = kOffVec + 3 * 64 * 4;     // 2 mbarriers, tmem slot, abort flag
-    static constexpr int kBytes = kOffBar + 64 + 1024;       // + alignment slack
-    static_assert(64 * kLdA * 4 >= 2 * 8192, "T and T' must fit over A");
+    static constexpr int kOffA = kOffV + kTile;           // A, overwritten block by block with X = (I+A)^-1;
+                                                          // blocks above the diagonal are scratch; later T and T'
+    static constexpr int kOffVec = kOffA + 64 * kLd * 4;  // beta[64], g[64], e^g[64]
+    static constexpr int kOffBar = kOffVec + 3 * 64 * 4;  // 2 mbarriers, tmem slot, abort flag
+    static constexpr int kBytes = kOffBar + 64 + 1024;    // + alignment slack
+    static_assert(64 * kLd * 4 >= 2 * 8192, "T and T' must fit over A");
     static_assert(kOffA % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
@@ -102,7 +99,7 @@ __device__ __forceinline__ void store_block(const float* d, float sign, float* m
 //     P = tril(Q K^T .* exp(g_i - g_j))   (bf16, 64x64 per unit),
 // from a Q tile that is loaded into the buffer the V tile later occupies.
 template <int D, bool kWithP>
-__global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
+__global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
                                                         const __grid_constant__ CUtensorMap tmV,
                                                         const __grid_constant__ CUtensorMap tmQ,
                                                         const __grid_constant__ CUtensorMap tmUo,
@@ -113,16 +110,14 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
     using namespace uw;
     using L = UWSmem<D>;
     constexpr int NA = D / 64;  // 64-column swizzle atoms per tile
-    constexpr int LDA = L::kLdA, LDX = L::kLdX, LDT = L::kLdT;
+    constexpr int LD = L::kLd;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sK = smem + L::kOffK;
     uint8_t* sV = smem + L::kOffV;
     uint8_t* sT = smem + L::kOffA;
     uint8_t* sT2 = sT + 8192;
-    float* sA = reinterpret_cast<float*>(smem + L::kOffA);
-    float* sX = reinterpret_cast<float*>(smem + L::kOffX);
-    float* sTmp = reinterpret_cast<float*>(smem + L::kOffTmp);
+    float* sA = reinterpret_cast<float*>(smem + L::kOffA);  // A, then X in place
     float* sBeta = reinterpret_cast<float*>(smem + L::kOffVec);
     float* sG = sBeta + 64;
     float* sEg = sG + 64;
@@ -180,8 +175,6 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
         }
         sG[tid] = g;
     }
-    // X starts as zero (blocks above the diagonal are read by the block products)
-    for (int idx = tid; idx < 64 * LDX / 4; idx += 128) reinterpret_cast<float4*>(sX)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
     if (tid < 64) {
         float g = sG[tid];
@@ -259,8 +252,8 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
                 a[e] = (col < i) ? bi * __uint_as_float(r[j + e]) * dec : 0.f;
                 if (kWithP) pq[e] = p.p_scale * __uint_as_float(rq[j + e]) * dec;
             }
-            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
-            *reinterpret_cast<float4*>(&sA[i * LDA + cbase + j + 4]) = make_float4(a[4], a[5], a[6], a[7]);
+            *reinterpret_cast<float4*>(&sA[i * LD + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<float4*>(&sA[i * LD + cbase + j + 4]) = make_float4(a[4], a[5], a[6], a[7]);
             if (kWithP) {
                 // P tile staged over the (dead) Q tile in the 64x64 swizzled TMA layout
                 *reinterpret_cast<uint4*>(sV + tile_off(i, (cbase + j) >> 3)) =
@@ -278,18 +271,14 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
         if (tid == 0) {
             tma_store_2d(&tmPo, sV, 0, (blockIdx.x * p.vh + head) * 64);
             bulk_commit();
-            bulk_wait_read<0>();  // the buffer may now receive the V tile
-            mbar_arrive_expect_tx(bar_load, L::kTile);
-            for (int a = 0; a < NA; ++a)
-                tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
         }
-        bar_load_parity = 1;
+        bar_load_parity = 1;  // the V tile follows into the same buffer once the store has read it
     }
 
     GDN_STAMP(4);
-    // ---- X = (I + A)^-1 : diagonal 16x16 blocks, one column per thread
-    if (lane < 16) {
-        const int b = warp, j = lane;
+    // ---- X = (I + A)^-1, in place.  Diagonal 16x16 blocks: one column per thread.
+    {
+        const int b = warp, j = lane & 15;
         float x[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = (i == j) ? 1.f : 0.f;
@@ -297,70 +286,98 @@ __global__ void __launch_bounds__(128, 3) gdn_uw_kernel(const __grid_constant__ 
         for (int i = 1; i < 16; ++i) {
             float acc = 0.f;
 #pragma unroll
-            for (int m = 0; m < i; ++m) acc = fmaf(sA[(16 * b + i) * LDA + 16 * b + m], x[m], acc);
+            for (int m = 0; m < i; ++m) acc = fmaf(sA[(16 * b + i) * LD + 16 * b + m], x[m], acc);
             if (i > j) x[i] = -acc;
         }
+        __syncwarp();  // the block is private to this warp: every lane has read it
+        if (lane < 16) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) sX[(16 * b + i) * LDX + 16 * b + j] = x[i];
+            for (int i = 0; i < 16; ++i) sA[(16 * b + i) * LD + 16 * b + j] = x[i];
+        }
     }
     __syncthreads();
+    if (kWithP && tid == 0) {
+        bulk_wait_read<0>();  // the P store has read the buffer: the V tile may land there
+        mbar_arrive_expect_tx(bar_load, L::kTile);
+        for (int a = 0; a < NA; ++a)
+            tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+    }
     GDN_STAMP(5);
-    // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half)
+    // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half).
+    // The intermediate A_10 X_00 is parked in the unused block above the diagonal.
     {
         const int pr = warp >> 1, n0 = 8 * (warp & 1);
         const int i0 = 16 * (2 * pr + 1), j0 = 16 * (2 * pr);
         float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) mma_block(d, sA, LDA, i0, j0 + 8 * ks, sX, LDX, j0 + 8 * ks, j0 + n0, lane);
-        store_block(d, 1.f, sTmp, LDT, 16 * pr, n0, lane);
+        for (int ks = 0; ks < 2; ++ks) mma_block(d, sA, LD, i0, j0 + 8 * ks, sA, LD, j0 + 8 * ks, j0 + n0, lane);
+        store_block(d, 1.f, sA, LD, j0, i0 + n0, lane);
         __syncthreads();
         float e[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) mma_block(e, sX, LDX, i0, i0 + 8 * ks, sTmp, LDT, 16 * pr + 8 * ks, n0, lane);
-        __syncthreads();  // everyone is done with this level's scratch
-        store_block(e, -1.f, sX, LDX, i0, j0 + n0, lane);
+        for (int ks = 0; ks < 2; ++ks) mma_block(e, sA, LD, i0, i0 + 8 * ks, sA, LD, j0 + 8 * ks, i0 + n0, lane);
+        store_block(e, -1.f, sA, LD, i0, j0 + n0, lane);
     }
     __syncthreads();
     GDN_STAMP(6);
-    // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result
+    // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result.
+    // The intermediate goes to the unused upper-right quadrant; K-steps that would only meet the
+    // (zero, here scratch) blocks above the diagonal are skipped.
     {
         const int rb = warp >> 1, cb = warp & 1;
         float d[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
+        for (int ks = 0; ks < 4; ++ks) {
+            if (ks >= 2 * cb) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-                mma_block(d[nt], sA, LDA, 32 + 16 * rb, 8 * ks, sX, LDX, 8 * ks, 16 * cb + 8 * nt, lane);
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_block(d[nt], sA, LD, 32 + 16 * rb, 8 * ks, sA, LD, 8 * ks, 16 * cb + 8 * nt, lane);
+            }
+        }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) store_block(d[nt], 1.f, sTmp, LDT, 16 * rb, 16 * cb + 8 * nt, lane);
+        for (int nt = 0; nt < 2; ++nt) store_block(d[nt], 1.f, sA, LD, 16 * rb, 32 + 16 * cb + 8 * nt, lane);
         __syncthreads();
         float e[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
+        for (int ks = 0; ks < 4; ++ks) {
+            if (ks < 2 * (rb + 1)) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-                mma_block(e[nt], sX, LDX, 32 + 16 * rb, 32 + 8 * ks, sTmp, LDT, 8 * ks, 16 * cb + 8 * nt, lane);
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_block(e[nt], sA, LD, 32 + 16 * rb, 32 + 8 * ks, sA, LD, 8 * ks, 32 + 16 * cb + 8 * nt, lane);
+            }
+        }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) store_block(e[nt], -1.f, sX, LDX, 32 + 16 * rb, 16 * cb + 8 * nt, lane);
+        for (int nt = 0; nt < 2; ++nt) store_block(e[nt], -1.f, sA, LD, 32 + 16 * rb, 16 * cb + 8 * nt, lane);
     }
     __syncthreads();
 
     GDN_STAMP(7);
-    // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles (over A)
+    // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles written over X:
+    //      every thread first pulls its 32 values of X into registers
     {
         const int i = tid >> 1, c0 = (tid & 1) * 32;
+        float xs[32], bt[32], eg[32];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 t = *reinterpret_cast<const float4*>(&sA[i * LD + c0 + 4 * q]);
+            const bool valid = ((c0 + 4 * q) >> 4) <= (i >> 4);  // blocks above the diagonal hold scratch
+            xs[4 * q] = valid ? t.x : 0.f; xs[4 * q + 1] = valid ? t.y : 0.f;
+            xs[4 * q + 2] = valid ? t.z : 0.f; xs[4 * q + 3] = valid ? t.w : 0.f;
+            const float4 tb = *reinterpret_cast<const float4*>(&sBeta[c0 + 4 * q]);
+            bt[4 * q] = tb.x; bt[4 * q + 1] = tb.y; bt[4 * q + 2] = tb.z; bt[4 * q + 3] = tb.w;
+            const float4 te = *reinterpret_cast<const float4*>(&sEg[c0 + 4 * q]);
+            eg[4 * q] = te.x; eg[4 * q + 1] = te.y; eg[4 * q + 2] = te.z; eg[4 * q + 3] = te.w;
+        }
+        __syncthreads();
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-            const float4 xa = *reinterpret_cast<const float4*>(&sX[i * LDX + c0 + ch * 8]);
-            const float4 xb = *reinterpret_cast<const float4*>(&sX[i * LDX + c0 + ch * 8 + 4]);
-            const float xs[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
             uint32_t t1[4], t2[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = c0 + ch * 8 + e * 2;
-                const float v0 = xs[2 * e] * sBeta[j], v1 = xs[2 * e + 1] * sBeta[j + 1];
+                const int j = ch * 8 + e * 2;
+                const float v0 = xs[j] * bt[j], v1 = xs[j + 1] * bt[j + 1];
                 t1[e] = pack_bf16(v0, v1);
-                t2[e] = pack_bf16(v0 * sEg[j], v1 * sEg[j + 1]);
+                t2[e] = pack_bf16(v0 * eg[j], v1 * eg[j + 1]);
             }
             const uint32_t off = sw128_offset(i, c0 + ch * 8);
             *reinterpret_cast<uint4*>(sT + off) = make_uint4(t1[0], t1[1], t1[2], t1[3]);
