@@ -11,13 +11,18 @@ constexpr int kChunk = 64;
 // CTA (0,0) writes clock64() stamps to a global buffer.
 #ifdef GDN_PHASE_TIMING
 __device__ long long g_phase_stamps[64];
+__device__ __forceinline__ long long gdn_clock_ordered() {
+    long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+    return t;
+}
 #define GDN_STAMP(i)                                                                  \
     do {                                                                              \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_stamps[i] = clock64(); \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
     } while (0)
 #define GDN_STAMP_ANY(i)                                                   \
     do {                                                                  \
-        if (blockIdx.x == 0 && blockIdx.y == 0) g_phase_stamps[i] = clock64(); \
+        if (blockIdx.x == 0 && blockIdx.y == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
     } while (0)
 #else
 #define GDN_STAMP(i) \

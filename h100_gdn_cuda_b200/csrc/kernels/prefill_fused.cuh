@@ -375,7 +375,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const float e0 = p.scale * __expf(g0), e1 = p.scale * __expf(g1);  // epilogue factor for S q
             const float d0 = __expf(g_last - g0), d1 = __expf(g_last - g1);
             const float el = __expf(g_last);
+            if (c == 4 && lane == 0) GDN_STAMP_ANY(20);
             mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
+            if (c == 4 && lane == 0) GDN_STAMP_ANY(21);
             float* gb = gate_buf(c);
             gb[lane] = e0;
             gb[lane + 32] = e1;
@@ -383,21 +385,22 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             gb[64 + lane + 32] = d1;
             if (lane == 0) gb[128] = el;
             __syncwarp();
-            if (lane == 0) {
+            {
+                // warp-uniform issue: one elected lane arms the barrier and launches the loads
                 uint8_t* st = smem + s * L::kStage;
                 const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
                 const int prow = ((gchunk0 + c) * p.vh + head) * 64;
-                mbar_arrive_expect_tx(&bar_full[s], L::kStage);
+                mbar_arrive_expect_tx_w(&bar_full[s], L::kStage);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
-                    tma_load_4d(st + L::kOffW + a * 8192, &tmW, &bar_full[s], a * 64, head, tok, batch);
-                    tma_load_4d(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
+                    tma_load_4d_w(st + L::kOffW + a * 8192, &tmW, &bar_full[s], a * 64, head, tok, batch);
+                    tma_load_4d_w(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
                 }
-                tma_load_2d(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
+                tma_load_2d_w(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
-                    tma_load_4d(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
-                    tma_load_4d(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
+                    tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
+                    tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
                 }
             }
         }
@@ -424,6 +427,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 const int s = c & 1;
                 const uint32_t par = static_cast<uint32_t>(c & 1);
                 const uint64_t w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
+                if (c == 4) GDN_STAMP_ANY(29);
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
                 if (c == 4) GDN_STAMP_ANY(30);

@@ -123,6 +123,45 @@ GDN_DEVICE void tma_load_4d(void* dst, const void* tmap, uint64_t* bar, int c0, 
         "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+// Warp-collective TMA loads: the converged warp calls them with warp-uniform arguments and one
+// elected lane issues (keeps the tensor-map address and coordinates in uniform registers).
+GDN_DEVICE void tma_load_4d_w(void* dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];\n\t}\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0),
+        "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+GDN_DEVICE void tma_load_2d_w(void* dst, const void* tmap, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];\n\t}\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+GDN_DEVICE void mbar_arrive_expect_tx_w(uint64_t* bar, uint32_t bytes) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}\n" ::"r"(smem_u32(bar)),
+        "r"(bytes)
+        : "memory");
+}
+// Pull a tile into L2 ahead of the load that will fetch it into shared memory.
+GDN_DEVICE void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+GDN_DEVICE void tma_prefetch_2d(const void* tmap, int c0, int c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(c0), "r"(c1)
+                 : "memory");
+}
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(
