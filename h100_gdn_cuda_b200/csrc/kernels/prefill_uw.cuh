@@ -14,10 +14,10 @@
 //   U = T V    : M=64 N=D K=64, A = T (bf16, written by the CTA), B = the V tile read MN-major;
 //   W = T' K   : M=64 N=D K=64, A = T' = X diag(beta e^g), B = the K tile read MN-major;
 //                U and W are interleaved the same way (U in lanes +0, W in lanes +16).
-// The unit-lower-triangular inverse runs in fp32 accuracy: the 16x16 diagonal blocks by
+// The unit-lower-triangular inverse: the 16x16 diagonal blocks in fp32 by
 // forward substitution (one column per thread), then two levels of recursive doubling
-// (16 -> 32 -> 64) whose block products use warp-level tensor-core MMAs on TF32 operands
-// split into a high and a low part (three MMAs per product, error ~2^-21).
+// (16 -> 32 -> 64) whose block products use warp-level tensor-core MMAs on TF32 operands with
+// fp32 accumulation.
 // Tensor memory: D columns.  Shared memory: K and V tiles (later the U/W staging), A (later
 // T and T'), X, and a small scratch: about 73 KB.
 #pragma once
@@ -55,11 +55,10 @@ struct UWSmem {
 };
 
 namespace uw {
-// fp32 -> (hi, lo) TF32 parts
-__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-    const float r = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
 }
 __device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint32_t* b) {
     asm volatile(
@@ -67,25 +66,20 @@ __device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
-// d(16x8) += A(16x8 at [r0][k0] of `am`) * B(8x8 at [k0b][n0] of `bm`), fp32-accurate
+// d(16x8) += A(16x8 at [r0][k0] of `am`) * B(8x8 at [k0b][n0] of `bm`), TF32 operands, fp32 accumulation.
+// The operands are entries of A and of (I+A)^-1 blocks; their TF32 rounding (2^-11) perturbs the
+// inverse by well under the bf16 rounding (2^-9) its result receives anyway.
 __device__ __forceinline__ void mma_block(float* d, const float* am, int lda, int r0, int k0, const float* bm,
                                           int ldb, int k0b, int n0, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    float af[4], bf[2];
-    af[0] = am[(r0 + g) * lda + k0 + t];
-    af[1] = am[(r0 + g + 8) * lda + k0 + t];
-    af[2] = am[(r0 + g) * lda + k0 + t + 4];
-    af[3] = am[(r0 + g + 8) * lda + k0 + t + 4];
-    bf[0] = bm[(k0b + t) * ldb + n0 + g];
-    bf[1] = bm[(k0b + t + 4) * ldb + n0 + g];
-    uint32_t ah[4], al[4], bh[2], bl[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) split_tf32(af[i], ah[i], al[i]);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) split_tf32(bf[i], bh[i], bl[i]);
-    mma_tf32(d, al, bh);
-    mma_tf32(d, ah, bl);
-    mma_tf32(d, ah, bh);
+    uint32_t a[4], b[2];
+    a[0] = to_tf32(am[(r0 + g) * lda + k0 + t]);
+    a[1] = to_tf32(am[(r0 + g + 8) * lda + k0 + t]);
+    a[2] = to_tf32(am[(r0 + g) * lda + k0 + t + 4]);
+    a[3] = to_tf32(am[(r0 + g + 8) * lda + k0 + t + 4]);
+    b[0] = to_tf32(bm[(k0b + t) * ldb + n0 + g]);
+    b[1] = to_tf32(bm[(k0b + t + 4) * ldb + n0 + g]);
+    mma_tf32(d, a, b);
 }
 // store -d (16x8) at [r0][n0]
 __device__ __forceinline__ void store_block(const float* d, float sign, float* m, int ld, int r0, int n0, int lane) {
