@@ -73,6 +73,7 @@ SYMBOLS = {
     "gdn_last_error": (C.c_char_p, []),
     "gdn_version": (C.c_int, []),
     "gdn_device_status": (C.c_int, [C.c_int, C.POINTER(C.c_int)]),
+    "gdn_jit_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_int)]),
     "gdn_fused_gating": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "gdn_chunk_local_cumsum": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
                                          C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),

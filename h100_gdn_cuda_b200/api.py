@@ -176,7 +176,7 @@ def transpose_to_mn_major(input: torch.Tensor, alignment: int = 16) -> torch.Ten
 
 def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=None, cu_seqlens=None,
                       num_accepted_tokens=None, inference_mode: int = 0, is_qk_norm: bool = False,
-                      scale: Optional[float] = None, *, inplace_state: bool = False):
+                      scale: Optional[float] = None, *, inplace_state: bool = False, _max_head_dim: int = 256):
     """Token recurrence for decode / speculative verify / short prefill; python_api.cpp:107-122
     and csrc/apis/gdn_forward.cpp:134-206.
 
@@ -194,7 +194,7 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
     _require(key.shape[-1] == d, "query and key head dims differ")
     dv_in = value.shape[-1]
     d_al, dv_al = _aligned_dim(d), _aligned_dim(dv_in)
-    _require(d_al <= 256 and dv_al <= 256, "head dims above 256 are not supported")
+    _require(d_al <= _max_head_dim and dv_al <= _max_head_dim, "head dims above %d are not supported" % _max_head_dim)
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     q, k, v = _pad_last(query, d_al), _pad_last(key, d_al), _pad_last(value, dv_al)

@@ -1,7 +1,9 @@
 // C-ABI entry points of libgdn_b200.so: runtime, helper kernels and the recurrent
 // (decode / speculative-verify) path.  The chunked-prefill entry points live in
 // gdn_prefill.cu.  See include/gdn_b200.h for the contract of each function.
+#include "heuristics.hpp"
 #include "host_common.hpp"
+#include "jit/jit.hpp"
 #include "kernels/helpers.cuh"
 #include "kernels/recurrent.cuh"
 
@@ -54,10 +56,33 @@ static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st) 
         GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set[dev] = true;
     }
-    const int per_sm = DK <= 128 ? 4 : 2;  // matches the kernel's launch bounds
+    const int per_sm = recurrent_ctas_per_sm<DK>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
     gdn_recurrent_kernel<DK><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
     GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+// Head dimensions without a prebuilt kernel (or every call when GDN_JIT_RECURRENT=1) go through
+// the run-time compiler: a three-line translation unit instantiates the kernel body for DK.
+static int launch_recurrent_jit(const RecurrentParams& p, int dk, int sms, cudaStream_t st) {
+    const RecurrentConfig cfg = recurrent_config(dk, p.num_tiles, sms);
+    char src[512];
+    snprintf(src, sizeof(src),
+             "#include \"kernels/recurrent.cuh\"\n"
+             "extern \"C\" __global__ void __launch_bounds__(%d, %d) gdn_recurrent_jit(const gdn::RecurrentParams p) {\n"
+             "    gdn::gdn_recurrent_body<%d>(p);\n}\n",
+             kRecThreads, cfg.ctas_per_sm, dk);
+    jit::LoadedKernel k;
+    std::string err;
+    if (int rc = jit::get_kernel("recurrent_dk" + std::to_string(dk), src, "gdn_recurrent_jit", &k, &err))
+        return fail(rc, "%s", err.c_str());
+    GDN_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  cfg.smem_bytes));
+    RecurrentParams pc = p;
+    void* args[] = {&pc};
+    GDN_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(k.kernel), dim3(static_cast<unsigned>(cfg.grid)),
+                              dim3(kRecThreads), args, cfg.smem_bytes, st));
     return GDN_OK;
 }
 
@@ -67,6 +92,7 @@ int gdn_init(const char* library_root, const char* cuda_home) {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     g_library_root = library_root ? library_root : "";
     g_cuda_home = cuda_home ? cuda_home : "";
+    jit::set_roots(g_library_root, g_cuda_home);
     return GDN_OK;
 }
 
@@ -181,8 +207,8 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     GDN_REQUIRE(a != nullptr, "gdn_recurrent_forward: args is NULL");
     if (int rc = check_shape(a->shape, false)) return rc;
     const GdnShape& s = a->shape;
-    GDN_REQUIRE(s.head_dim_k % 64 == 0 && s.head_dim_k <= 256,
-                "gdn_recurrent_forward: dk must be 64, 128, 192 or 256 (got %d)", s.head_dim_k);
+    GDN_REQUIRE(s.head_dim_k % 64 == 0 && s.head_dim_k <= 512,
+                "gdn_recurrent_forward: dk must be a multiple of 64 up to 512 (got %d)", s.head_dim_k);
     GDN_REQUIRE(s.head_dim_v % 32 == 0, "gdn_recurrent_forward: dv must be a multiple of 32 (got %d)", s.head_dim_v);
     if (int rc = check_token_tensor(a->q, "q", s.head_dim_k)) return rc;
     if (int rc = check_token_tensor(a->k, "k", s.head_dim_k)) return rc;
@@ -223,13 +249,14 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     GDN_REQUIRE(p.num_tiles < (1ll << 31), "gdn_recurrent_forward: too many state tiles");
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);
     switch (s.head_dim_k) {
         case 64: return launch_recurrent<64>(p, d->sms, st);
         case 128: return launch_recurrent<128>(p, d->sms, st);
         case 192: return launch_recurrent<192>(p, d->sms, st);
         case 256: return launch_recurrent<256>(p, d->sms, st);
     }
-    return fail(GDN_ERR_UNSUPPORTED, "unsupported dk %d", s.head_dim_k);
+    return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);  // 320 .. 512: compiled on first use
 }
 
 }  // extern "C"

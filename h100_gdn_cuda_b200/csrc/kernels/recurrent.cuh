@@ -98,8 +98,10 @@ __device__ __forceinline__ float hsum(f2 v) {
 }
 }  // namespace rec
 
+// Body of the kernel as a device function: the ahead-of-time entry points below and the
+// entry point the run-time compiler generates (csrc/gdn_jit.cu) both instantiate it.
 template <int DK>
-__global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurrent_kernel(const RecurrentParams p) {
+__device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     using namespace ptx;
     using namespace rec;
     using Stage = RecStage<DK>;
@@ -434,6 +436,16 @@ __global__ void __launch_bounds__(kRecThreads, (DK <= 128 ? 4 : 2)) gdn_recurren
         g_first = g_next;
     }
     if (tid == 0 && abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+template <int DK>
+constexpr int recurrent_ctas_per_sm() {
+    return DK <= 128 ? 4 : 2;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK>()) gdn_recurrent_kernel(const RecurrentParams p) {
+    gdn_recurrent_body<DK>(p);
 }
 
 }  // namespace gdn

@@ -6,9 +6,20 @@
 // Every wait in this file is bounded: when the limit runs out the wait returns false
 // and the caller records an error status instead of spinning forever.
 #pragma once
-#include <cuda_bf16.h>
+#ifdef __CUDACC_RTC__
+// NVRTC has no C library headers: spell the fixed-width types out.
+typedef unsigned char uint8_t;
+typedef unsigned short uint16_t;
+typedef unsigned int uint32_t;
+typedef int int32_t;
+typedef unsigned long long uint64_t;
+typedef long long int64_t;
+typedef unsigned long long uintptr_t;
+#else
 #include <cuda_runtime.h>
 #include <stdint.h>
+#endif
+#include <cuda_bf16.h>
 
 namespace gdn {
 namespace ptx {

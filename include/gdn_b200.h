@@ -104,6 +104,16 @@ int gdn_version(void);
  * the reference, whose device asserts trap (kernels/common/common.hpp:485-493). */
 int gdn_device_status(int device, int* status_out);
 
+/* Replaces Compiler::build (csrc/jit/compiler.hpp:82-103): compiles `source`, a complete CUDA
+ * translation unit that may include the library's kernel headers ("kernels/...") and defines
+ * an extern "C" kernel, to an sm_100a cubin, or finds it in the on-disk cache
+ * ($JIT_CACHE_DIR or ~/.gdn_b200/cache, directory kernel.<name>.<hash>).  NVRTC is used when it
+ * can be loaded and JIT_USE_NVRTC is not 0, otherwise <cuda_home>/bin/nvcc.  Needs gdn_init()
+ * first and no GPU.  Writes the cubin path and whether it was a cache hit.  The library uses this
+ * itself for kernels it has no prebuilt instance of (recurrent head dims above 256). */
+int gdn_jit_compile(const char* name, const char* source, char* cubin_path_out, size_t cubin_path_cap,
+                    int* cache_hit_out);
+
 /* ---------------------------------------------------------------- helpers
  * Replaces kernels::gdn_gating (src/gdn_ops.cu:13-33; kernel gdn_helpers.cuh:41-122):
  *   beta = sigmoid(b),  gate = -exp(A_log[h]) * softplus(a + dt_bias[h])   (softplus(x) = x for x > 20)

@@ -1,0 +1,58 @@
+"""Run-time compiled kernels on the GPU: the recurrent kernel built at run time gives the same
+bits as the prebuilt one, and a head dimension without a prebuilt kernel (320) is compiled on
+first use and matches the oracle (tolerances as in test_recurrent_gpu.py)."""
+import os
+
+import pytest
+import torch
+
+from oracle import gdn_oracle as O
+from h100_gdn_cuda_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture()
+def gdn(tmp_path, monkeypatch):
+    import h100_gdn_cuda_b200 as g
+    from h100_gdn_cuda_b200 import build
+    build.build()
+    monkeypatch.setenv("JIT_CACHE_DIR", str(tmp_path))
+    g.init(ROOT, os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+    return g
+
+
+def _run(gdn, p, beta, g):
+    pd = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in p.items()}
+    return gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], beta.cuda(), g.cuda(), is_qk_norm=True,
+                                 inference_mode=1)
+
+
+@pytest.mark.parametrize("use_nvrtc", ["1", "0"])
+def test_jit_recurrent_equals_prebuilt(gdn, monkeypatch, tmp_path, use_nvrtc):
+    p = synthetic.decode_inputs(8, 2, 2, 4, 128, seed=5)
+    beta, g = O.gating_ref(p["A_log"], p["dt_bias"], p["a"], p["b"])
+    beta = beta.bfloat16()
+    o_ref, s_ref = _run(gdn, p, beta, g)
+    monkeypatch.setenv("GDN_JIT_RECURRENT", "1")
+    monkeypatch.setenv("JIT_USE_NVRTC", use_nvrtc)
+    o, s = _run(gdn, p, beta, g)
+    assert torch.equal(o, o_ref) and torch.equal(s, s_ref)
+    assert any(d.startswith("kernel.recurrent_dk128.") for d in os.listdir(tmp_path))
+    o2, s2 = _run(gdn, p, beta, g)  # second call: module already loaded
+    assert torch.equal(o2, o_ref)
+
+
+def test_head_dim_without_prebuilt_kernel(gdn):
+    p = synthetic.decode_inputs(3, 2, 1, 2, 320, seed=6)
+    beta, g = O.gating_ref(p["A_log"], p["dt_bias"], p["a"], p["b"])
+    beta = beta.bfloat16()
+    pd = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in p.items()}
+    from h100_gdn_cuda_b200 import api
+    # the Python wrapper limits head dims to 256 like the reference; go through the C ABI limits directly
+    o, s = api.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], beta.cuda(), g.cuda(), is_qk_norm=True,
+                                 inference_mode=1, _max_head_dim=512)
+    o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), beta.float(), g,
+                                   p["state"].float(), is_qk_norm=True)
+    assert O.rel_fro(o.float().cpu(), o_ref) < 1e-2 and O.rel_fro(s.float().cpu(), s_ref) < 1e-2
