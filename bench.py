@@ -295,7 +295,6 @@ def main():
         seq_ms += stage_ev[1].elapsed_time(stage_ev[2])
     uw_ms /= args.steps
     seq_ms /= args.steps
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---------------- end to end from host buffers
     out_host = torch.empty(B, T, vh, d, dtype=torch.bfloat16).pin_memory()
@@ -353,6 +352,8 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms_dec_kernel = e0.elapsed_time(e1) / dsteps
+    # the sampler ran across every timed region above (prefill resident, end to end, decode)
+    clocks = sampler.stop() if rank == 0 else None
     dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
 
     if rank != 0:
