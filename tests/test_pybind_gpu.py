@@ -1,0 +1,98 @@
+"""The C++/pybind11 `gdn_cuda` extension (same module surface as the reference's
+csrc/python_api.cpp) gives the same bits as the ctypes mirror, and raises RuntimeError."""
+import pytest
+import torch
+
+from h100_gdn_cuda_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import h100_gdn_cuda_b200 as py
+    from h100_gdn_cuda_b200 import build
+    build.build()
+    build.build_ext()
+    from h100_gdn_cuda_b200 import gdn_cuda as ext
+    return py, ext
+
+
+def dev(d):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in d.items()}
+
+
+def test_surface(mods):
+    _, ext = mods
+    for name in ("init", "chunked_forward", "recurrent_forward", "fused_gdn_gating", "bf16_gdn_compute_u_w",
+                 "bf16_chunked_seq_state_update", "bf16_gdn_chunked_compute_O", "chunk_local_cumsum_bf16",
+                 "transpose_to_mn_major", "InferenceMode"):
+        assert hasattr(ext, name)
+    assert int(ext.Prefill) == 0 and int(ext.Decode) == 1 and int(ext.SpecVerify) == 2
+
+
+def test_chunked_forward_same_bits(mods):
+    py, ext = mods
+    p = dev(synthetic.prefill_inputs(2, 200, 2, 4, 128, seed=3, mild_gate=True))
+    o1, s1 = py.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"])
+    o2, s2 = ext.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"])
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    v = dev(synthetic.varlen_inputs([65, 1, 200], 2, 4, 100, seed=4))
+    a = (v["q"], v["k"], v["v"], v["beta"], v["g"], None, v["state"], v["cu_seqlens"], v["chunk_indices"],
+         v["cu_chunks"], v["total_chunks"])
+    o1, s1 = py.chunked_forward(*a)
+    o2, s2 = ext.chunked_forward(*a)
+    assert o2.shape == v["v"].shape and torch.equal(o1, o2) and torch.equal(s1, s2)
+
+
+def test_recurrent_and_helpers_same_bits(mods):
+    py, ext = mods
+    d = dev(synthetic.decode_inputs(8, 4, 2, 4, 128, seed=5, spec=True))
+    b1, g1 = py.fused_gdn_gating(d["A_log"], d["dt_bias"], d["a"], d["b"])
+    b2, g2 = ext.fused_gdn_gating(d["A_log"], d["dt_bias"], d["a"], d["b"], False)
+    assert torch.equal(b1, b2) and torch.equal(g1, g2)
+    for mode in (1, 2):
+        o1, s1 = py.recurrent_forward(d["q"], d["k"], d["v"], d["state"], b1, g1, None, d["num_accepted_tokens"],
+                                      mode, True)
+        o2, s2 = ext.recurrent_forward(d["q"], d["k"], d["v"], d["state"], b2, g2, None, d["num_accepted_tokens"],
+                                       mode, True)
+        mask = torch.arange(4, device="cuda")[None, :] < d["num_accepted_tokens"][:, None]
+        assert torch.equal(o1[mask], o2[mask]) and s1.shape == s2.shape
+        if mode == 1:
+            assert torch.equal(s1, s2)
+    x = torch.randn(3, 70, 5, device="cuda")
+    assert torch.equal(py.transpose_to_mn_major(x), ext.transpose_to_mn_major(x))
+    out1 = torch.empty(3, 70, 5, device="cuda")
+    out2 = torch.empty(3, 70, 5, device="cuda")
+    py.chunk_local_cumsum_bf16(x, out1, 3, 70, 5, True)
+    ext.chunk_local_cumsum_bf16(x, out2, 3, 70, 5, True)
+    assert torch.equal(out1, out2)
+
+
+def test_low_level_chain_same_bits(mods):
+    py, ext = mods
+    p = dev(synthetic.prefill_inputs(1, 130, 2, 4, 128, seed=6, mild_gate=True))
+    gc = torch.empty_like(p["g"])
+    ext.chunk_local_cumsum_bf16(p["g"], gc, 1, 130, 4, True)
+    res = []
+    for m in (py, ext):
+        u, w = torch.empty_like(p["v"]), torch.empty_like(p["v"])
+        m.bf16_gdn_compute_u_w(p["k"], p["v"], u, w, m.transpose_to_mn_major(p["beta"]), m.transpose_to_mn_major(gc))
+        state = torch.empty(1, 3, 4, 128, 128, dtype=torch.bfloat16, device="cuda")
+        final = torch.empty_like(p["state"])
+        m.bf16_chunked_seq_state_update(p["k"], u, w, p["state"], state, final, gc)
+        o = torch.empty_like(p["v"])
+        m.bf16_gdn_chunked_compute_O(p["q"], state, p["k"], u, o, gc)
+        res.append((u, w, state, final, o))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
+def test_errors_raise(mods):
+    _, ext = mods
+    p = dev(synthetic.prefill_inputs(1, 64, 1, 1, 128, seed=1))
+    with pytest.raises(RuntimeError):
+        ext.chunked_forward(p["q"].float(), p["k"], p["v"], p["beta"], p["g"])
+    big = torch.zeros(1, 64, 1, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        ext.chunked_forward(big, big, big, p["beta"], p["g"])
