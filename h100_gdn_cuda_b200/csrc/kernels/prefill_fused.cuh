@@ -378,6 +378,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (c == 4 && lane == 0) GDN_STAMP_ANY(20);
             mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
             if (c == 4 && lane == 0) GDN_STAMP_ANY(21);
+            if (c == 4 && lane == 0) GDN_STAMP_ANY(23);
             float* gb = gate_buf(c);
             gb[lane] = e0;
             gb[lane + 32] = e1;
@@ -402,6 +403,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
                     tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
                 }
+                if (c == 4 && lane == 0) GDN_STAMP_ANY(22);
             }
         }
     } else if (warp == 13) {
