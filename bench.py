@@ -58,6 +58,16 @@ def uw_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
     return 2.0 * c * (4 * c * d) + (2.0 / 3.0) * c ** 3
 
 
+# DRAM read + write bytes per launch seen by one ncu capture (dram__bytes_read.sum +
+# dram__bytes_write.sum), divided by the units that launch processed.  Traffic is proportional
+# to the units (every CTA streams its own tiles), so a full launch is units x this figure.
+#   gdn_fused_seq_kernel: B=2 T=4096 vh=32 capture, 238.13 MB read + 55.48 MB written, 4096 units
+#   gdn_recurrent_kernel: B=128 capture, 136.37 MB read + 84.43 MB written, 128 sequence-tokens
+#                         (part of the written state was still in L2 when the launch ended)
+NCU_FUSED_TRAFFIC_PER_UNIT = (238.132736e6 + 55.481856e6) / 4096
+NCU_DECODE_TRAFFIC_PER_TOKEN = (136.369664e6 + 84.427008e6) / 128
+
+
 def decode_bytes_per_token(kh, vh, d) -> float:
     return vh * (2 * d * d * 2) + 2 * (2 * kh * d + 2 * vh * d) + vh * 4
 
@@ -404,7 +414,8 @@ def main():
         "gpu_launches": 2 * args.steps,
         "roofline": {"kernel": "gdn_fused_seq_kernel (state propagation + output)", "bound": "tensor",
                      "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": achieved / peaks["tflops"], "traffic": units * NCU_FUSED_TRAFFIC_PER_UNIT,
+                     "traffic_source": "ncu capture at B=2 scaled by units", "peak_source": peaks["source"],
                      "ms_per_launch": seq_ms, "flops_per_launch": seq_flops},
         "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_fused_seq_kernel_ms": seq_ms,
                     "uw_tflops": units * uw_kernel_flops_per_unit(d) / (uw_ms * 1e-3) / 1e12,
@@ -416,7 +427,8 @@ def main():
                                 "achieved": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                 "unit": "GB/s", "frac": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                 "frac_of_nominal_8TBs": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / 8000.0,
-                                "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes}},
+                                "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes,
+                                "traffic": dB * NCU_DECODE_TRAFFIC_PER_TOKEN}},
         "clocks": clocks,
     }
     if cpu is not None:
