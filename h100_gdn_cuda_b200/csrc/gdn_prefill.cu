@@ -86,20 +86,23 @@ int set_smem(K kernel, int bytes) {
 
 int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& v, const GdnTokenTensor& u,
               const GdnTokenTensor& w, const GdnTokenScalar& beta, const GdnTokenScalar& gate, bool gate_is_raw,
-              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* p_out = nullptr,
-              const CUtensorMap* tm_p = nullptr, float p_scale = 1.f) {
+              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* blocks = nullptr,
+              float p_scale = 1.f) {
+    // With q (the whole-layer path) U, W and P go to `blocks` (one contiguous block per unit) and
+    // u / w are not used; without it (the low-level wrapper) U and W go to the caller's tensors.
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
     CUtensorMap tmK, tmV, tmQ, tmUo, tmWo;
     if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
     if (int rc = make_token_map(&tmV, v, s, s.num_v_heads, "v")) return rc;
-    if (int rc = make_token_map(&tmUo, u, s, s.num_v_heads, "u")) return rc;
-    if (int rc = make_token_map(&tmWo, w, s, s.num_v_heads, "w")) return rc;
-    const CUtensorMap tmPo = tm_p ? *tm_p : tmK;
     if (q) {
         if (int rc = make_token_map(&tmQ, *q, s, s.num_k_heads, "q")) return rc;
+        tmUo = tmK;
+        tmWo = tmK;
     } else {
+        if (int rc = make_token_map(&tmUo, u, s, s.num_v_heads, "u")) return rc;
+        if (int rc = make_token_map(&tmWo, w, s, s.num_v_heads, "w")) return rc;
         tmQ = tmK;
     }
     UWParams p{};
@@ -112,15 +115,15 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
     p.kh = s.num_k_heads;
     p.vh = s.num_v_heads;
     p.status = d->status;
-    p.p_out = static_cast<__nv_bfloat16*>(p_out);
+    p.blocks = static_cast<uint8_t*>(blocks);
     p.p_scale = p_scale;
     constexpr int smem = UWSmem<kD>::kBytes;
     if (q) {
         if (int rc = set_smem(gdn_uw_kernel<kD, true>, smem)) return rc;
-        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, tmPo, p);
+        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
     } else {
         if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
-        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, tmPo, p);
+        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
     }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
@@ -242,13 +245,10 @@ int gdn_compute_o(const GdnComputeOArgs* a, gdn_stream_t stream) {
 
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
-    const size_t tokens = s->cu_seqlens ? static_cast<size_t>(s->total_tokens)
-                                        : static_cast<size_t>(s->batch) * static_cast<size_t>(s->seq_len);
     const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
-    // U and W, (tokens, vh, 128) bf16 each, then P, (chunks, vh, 64, 64) bf16
-    return 2 * tokens * static_cast<size_t>(s->num_v_heads) * kD * 2 +
-           chunks * static_cast<size_t>(s->num_v_heads) * 8192 + 256;
+    // one block of U, W (64 x 128 bf16 each) and P (64 x 64 bf16) per (chunk, v-head)
+    return chunks * static_cast<size_t>(s->num_v_heads) * kUnitBlockBytes + 256;
 }
 
 int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
@@ -272,22 +272,9 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     const bool packed = s.cu_seqlens != nullptr;
-    const long long tokens_per_batch = packed ? s.total_tokens : s.seq_len;
-    const long long tokens = packed ? s.total_tokens : static_cast<long long>(s.batch) * s.seq_len;
-    GdnTokenTensor u, w;
-    u.ptr = a->workspace;
-    u.stride_head = kD;
-    u.stride_token = static_cast<int64_t>(s.num_v_heads) * kD;
-    u.stride_batch = packed ? 0 : tokens_per_batch * u.stride_token;
-    w = u;
-    w.ptr = static_cast<__nv_bfloat16*>(a->workspace) + tokens * s.num_v_heads * kD;
-
     void* const* ev = a->stage_events;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[0]), st));
     GDN_REQUIRE(!packed || s.cu_chunks, "gdn_chunked_forward: packed mode needs cu_chunks");
-    __nv_bfloat16* pbuf = static_cast<__nv_bfloat16*>(a->workspace) + 2 * tokens * s.num_v_heads * kD;
-    const long long units = static_cast<long long>(num_chunks(s)) * s.num_v_heads;
-    GDN_REQUIRE(units * 64 < (1ll << 31), "gdn_chunked_forward: too many (chunk, head) units");
     if (num_chunks(s) == 0) {
         if (ev) {
             GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
@@ -295,23 +282,15 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         }
         return GDN_OK;
     }
-    CUtensorMap tmP;
-    {
-        uint64_t dims[2] = {64, static_cast<uint64_t>(units) * 64};
-        uint64_t strides[1] = {128};
-        uint32_t box[2] = {64, 64};
-        if (!make_tmap_bf16(&tmP, pbuf, 2, dims, strides, box, true))
-            return fail(GDN_ERR_CUDA, "could not encode the TMA descriptor of the P scratch");
-    }
-    if (int rc = launch_uw(s, a->k, a->v, u, w, a->beta, a->gate, true, d, st, &a->q, pbuf, &tmP, a->scale)) return rc;
+    const GdnTokenTensor none{};
+    if (int rc = launch_uw(s, a->k, a->v, none, none, a->beta, a->gate, true, d, st, &a->q, a->workspace, a->scale))
+        return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
     {
-        CUtensorMap tmQ, tmK, tmW, tmU, tmO;
+        CUtensorMap tmQ, tmK, tmO;
         if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
         if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
-        if (int rc = make_token_map(&tmW, w, s, s.num_v_heads, "w")) return rc;
-        if (int rc = make_token_map(&tmU, u, s, s.num_v_heads, "u")) return rc;
         if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "out")) return rc;
         FusedParams p{};
         p.map = chunk_map(s);
@@ -327,9 +306,10 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         p.vh = s.num_v_heads;
         p.scale = a->scale;
         p.status = d->status;
+        p.blocks = static_cast<const uint8_t*>(a->workspace);
         constexpr int smem = FusedSmem::kBytes;
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
-        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmW, tmU, tmP, tmO, p);
+        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
         GDN_CUDA(cudaGetLastError());
     }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));

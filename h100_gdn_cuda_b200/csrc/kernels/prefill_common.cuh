@@ -34,6 +34,11 @@ __device__ __forceinline__ long long gdn_clock_ordered() {
 #endif
 
 // per-token scalar tensor (beta or gate) as the kernels see it
+// Scratch of gdn_chunked_forward: one contiguous block per (global chunk, v-head) unit, laid out
+// exactly as the shared-memory images the state kernel wants (128-byte-swizzled 64 x 64 atoms):
+// U (16 KB), W (16 KB), P (8 KB).  One untiled bulk copy moves a whole block in either direction.
+constexpr int kUnitBlockBytes = 2 * kChunk * 128 * 2 + kChunk * kChunk * 2;
+
 struct ScalarView {
     const void* ptr;
     int is_f32;

@@ -14,7 +14,8 @@
 //   warps 0-7   state warps: own the fp32 state in registers (row = TMEM lane, 64 columns each),
 //               run the two passes of the chain
 //   warps 8-11  output warps: O epilogue (scale, transpose through shared memory, coalesced stores)
-//   warp 12     producer: chunk-local gate cumsum + TMA loads of Q, K, W, U, P two chunks ahead
+//   warp 12     producer: chunk-local gate cumsum; per chunk one bulk copy of its U, W, P block of
+//               the scratch and tensor copies of Q and K, into a two-stage ring
 //   warp 13     one thread issues every tcgen05.mma and commits completion onto mbarriers
 // All operands are transposed so that the 128 state rows are the MMA M dimension; S_bf, Un_a,
 // Un_b are bf16 A operands in tensor memory; Q, K, W, U, P tiles are used as TMA delivered them.
@@ -36,13 +37,15 @@ struct FusedParams {
     int kh, vh;
     float scale;
     int* status;
+    const uint8_t* blocks;  // U, W, P of every (global chunk, v-head): kUnitBlockBytes each
 };
 
 struct FusedSmem {
     static constexpr int D = 128;
     static constexpr int kTile = kChunk * D * 2;  // 16 KB
-    static constexpr int kOffQ = 0, kOffK = kTile, kOffW = 2 * kTile, kOffU = 3 * kTile, kOffP = 4 * kTile;
-    static constexpr int kStage = 4 * kTile + 8192;  // Q, K, W, U, P
+    // U, W, P in the order of a unit block of the scratch, so that one bulk copy fills all three
+    static constexpr int kOffQ = 0, kOffK = kTile, kOffU = 2 * kTile, kOffW = 3 * kTile, kOffP = 4 * kTile;
+    static constexpr int kStage = 2 * kTile + kUnitBlockBytes;  // Q, K, U, W, P
     static constexpr int kOffO = 2 * kStage;         // two output staging tiles
     static constexpr int kOffGate = kOffO + 2 * kTile;  // 3 x { e^g[64], e^{gL-g}[64], e^{gL} }
     static constexpr int kGateStride = (2 * 64 + 4) * 4;
@@ -77,9 +80,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 
 __global__ void __launch_bounds__(fused::kThreads, 1)
     gdn_fused_seq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmU,
-                         const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmO,
-                         const FusedParams p) {
+                         const __grid_constant__ CUtensorMap tmO, const FusedParams p) {
     using namespace ptx;
     using namespace fused;
     using L = FusedSmem;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const int nloc = n - 32 * hf;  // tokens of this half that exist
             mbar_wait(bar_d1, par, abort_flag);
             tc_fence_after_sync();
-            if (c == 4 && tid == 0) GDN_STAMP_ANY(40);
+            if (c == 40 && tid == 0) GDN_STAMP_ANY(40);
             {
                 uint32_t r[32];
                 tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);  // -(S W^T)
@@ -232,12 +233,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_un);
-            if (c == 4 && tid == 0) GDN_STAMP_ANY(41);
+            if (c == 40 && tid == 0) GDN_STAMP_ANY(41);
             // ---- S <- e^{g_L} S + dS
             const float eg_last = gb[128];
             mbar_wait(bar_ds, par, abort_flag);
             tc_fence_after_sync();
-            if (c == 4 && tid == 0) GDN_STAMP_ANY(42);
+            if (c == 40 && tid == 0) GDN_STAMP_ANY(42);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 uint32_t r[32];
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 for (int e = 0; e < 32; ++e) S[q * 32 + e] = fmaf(S[q * 32 + e], eg_last, __uint_as_float(r[e]));
             }
             publish_state();
-            if (c == 4 && tid == 0) GDN_STAMP_ANY(43);
+            if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
         }
         if (p.state_out) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
@@ -282,11 +283,11 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             uint8_t* sO = smem + L::kOffO + (c & 1) * L::kTile;
             const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a) + tm_lane;
             const uint32_t tO2 = tmem + kTmO2 + tm_lane;
-            mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
-            if (c == 4 && otid == 0) GDN_STAMP_ANY(49);
-            mbar_wait(bar_o, par, abort_flag);
+            mbar_wait_relaxed<200>(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
+            if (c == 40 && otid == 0) GDN_STAMP_ANY(49);
+            mbar_wait_relaxed<100>(bar_o, par, abort_flag);
             tc_fence_after_sync();
-            if (c == 4 && otid == 0) GDN_STAMP_ANY(50);
+            if (c == 40 && otid == 0) GDN_STAMP_ANY(50);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 uint32_t r1[16], r2[16];
@@ -301,7 +302,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     gv[4 * e4] = t.x; gv[4 * e4 + 1] = t.y; gv[4 * e4 + 2] = t.z; gv[4 * e4 + 3] = t.w;
                 }
                 tmem_wait_ld();
-                if (c == 4 && otid == 0) GDN_STAMP_ANY(53 + 2 * b);
+                if (c == 40 && otid == 0) GDN_STAMP_ANY(53 + 2 * b);
                 if (b == 3) {
                     tc_fence_before_sync();
                     __syncwarp();
@@ -313,9 +314,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     const float o = fmaf(gv[e], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
                     *reinterpret_cast<__nv_bfloat16*>(sO + i * 128 + off8[i & 7]) = __float2bfloat16(o);
                 }
-                if (c == 4 && otid == 0) GDN_STAMP_ANY(54 + 2 * b);
+                if (c == 40 && otid == 0) GDN_STAMP_ANY(54 + 2 * b);
             }
-            if (c == 4 && otid == 0) GDN_STAMP_ANY(51);
+            if (c == 40 && otid == 0) GDN_STAMP_ANY(51);
             const long long tok0 = seq_tok0 + static_cast<long long>(c) * kChunk;
             const bool ragged = packed && n < kChunk;  // a full-box store would spill into the next sequence
             fence_proxy_async_smem();
@@ -330,7 +331,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             } else {
                 store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid);
             }
-            if (c == 4 && otid == 0) GDN_STAMP_ANY(52);
+            if (c == 40 && otid == 0) GDN_STAMP_ANY(52);
         }
         if (otid == 0) bulk_wait_read<0>();
     } else {
@@ -375,10 +376,10 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const float e0 = p.scale * __expf(g0), e1 = p.scale * __expf(g1);  // epilogue factor for S q
             const float d0 = __expf(g_last - g0), d1 = __expf(g_last - g1);
             const float el = __expf(g_last);
-            if (c == 4 && lane == 0) GDN_STAMP_ANY(20);
-            mbar_wait(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
-            if (c == 4 && lane == 0) GDN_STAMP_ANY(21);
-            if (c == 4 && lane == 0) GDN_STAMP_ANY(23);
+            if (c == 40 && lane == 0) GDN_STAMP_ANY(20);
+            mbar_wait_relaxed<200>(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
+            if (c == 40 && lane == 0) GDN_STAMP_ANY(21);
+            if (c == 40 && lane == 0) GDN_STAMP_ANY(23);
             float* gb = gate_buf(c);
             gb[lane] = e0;
             gb[lane + 32] = e1;
@@ -390,20 +391,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // warp-uniform issue: one elected lane arms the barrier and launches the loads
                 uint8_t* st = smem + s * L::kStage;
                 const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
-                const int prow = ((gchunk0 + c) * p.vh + head) * 64;
+                const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kUnitBlockBytes;
                 mbar_arrive_expect_tx_w(&bar_full[s], L::kStage);
-#pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    tma_load_4d_w(st + L::kOffW + a * 8192, &tmW, &bar_full[s], a * 64, head, tok, batch);
-                    tma_load_4d_w(st + L::kOffU + a * 8192, &tmU, &bar_full[s], a * 64, head, tok, batch);
-                }
-                tma_load_2d_w(st + L::kOffP, &tmP, &bar_full[s], 0, prow);
+                bulk_load_w(st + L::kOffU, blk, kUnitBlockBytes, &bar_full[s]);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
                     tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
                 }
-                if (c == 4 && lane == 0) GDN_STAMP_ANY(22);
+                if (c == 40 && lane == 0) GDN_STAMP_ANY(22);
             }
         }
     } else if (warp == 13) {
@@ -429,37 +425,37 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 const int s = c & 1;
                 const uint32_t par = static_cast<uint32_t>(c & 1);
                 const uint64_t w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
-                if (c == 4) GDN_STAMP_ANY(29);
+                if (c == 40) GDN_STAMP_ANY(29);
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
-                if (c == 4) GDN_STAMP_ANY(30);
-                if (c == 4) GDN_STAMP_ANY(31);
+                if (c == 40) GDN_STAMP_ANY(30);
+                if (c == 40) GDN_STAMP_ANY(31);
                 mbar_wait(bar_sbf, par, abort_flag);
                 tc_fence_after_sync();
-                if (c == 4) GDN_STAMP_ANY(32);
+                if (c == 40) GDN_STAMP_ANY(32);
                 // D1 = -(S_bf W^T)
                 mma_ts_w<false>(tD1, tS, w, id_sw);
 #pragma unroll
                 for (int ks = 1; ks < 8; ++ks)
                     mma_ts_w<true>(tD1, tS + ks * 8, desc_advance(w, kmajor_step(ks, 8192)), id_sw);
                 mma_commit_w(bar_d1);
-                if (c == 4) GDN_STAMP_ANY(33);
+                if (c == 40) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
                 const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
                 mma_ts_w<false>(tO1, tS, q, id_sq);
 #pragma unroll
                 for (int ks = 1; ks < 8; ++ks)
                     mma_ts_w<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
-                if (c == 4) GDN_STAMP_ANY(34);
+                if (c == 40) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
-                if (c == 4) GDN_STAMP_ANY(35);
+                if (c == 40) GDN_STAMP_ANY(35);
                 // dS = Un_b K
                 mma_ts_w<false>(tDS, tUb, k, id_ds);
 #pragma unroll
                 for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tDS, tUb + ks * 8, desc_advance(k, ks * 2048), id_ds);
                 mma_commit_w(bar_ds);
-                if (c == 4) GDN_STAMP_ANY(36);
+                if (c == 40) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
                 if (c > 0) {
                     mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
@@ -470,8 +466,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
                 mma_commit_w(bar_o);
                 mma_commit_w(&bar_empty[s]);
-                if (c == 4) GDN_STAMP_ANY(37);
-                if (c == 5) GDN_STAMP_ANY(38);
+                if (c == 40) GDN_STAMP_ANY(37);
+                if (c == 41) GDN_STAMP_ANY(38);
             }
         }
     }

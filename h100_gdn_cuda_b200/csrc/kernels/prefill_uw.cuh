@@ -33,7 +33,7 @@ struct UWParams {
     ScalarView gate;      // ptr == NULL: no decay
     int gate_is_raw;      // 1: per-token log-decay (cumsum taken here); 0: already chunk-local cumsum
     TokenView u, w;
-    __nv_bfloat16* p_out;  // kWithP: (chunk, v-head, 64, 64) bf16, chunk in global chunk order
+    uint8_t* blocks;       // kWithP: one kUnitBlockBytes block per (global chunk, v-head), see below
     float p_scale;         // kWithP: factor folded into P (the output scale)
     int kh, vh;
     int* status;
@@ -98,7 +98,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
                                                         const __grid_constant__ CUtensorMap tmQ,
                                                         const __grid_constant__ CUtensorMap tmUo,
                                                         const __grid_constant__ CUtensorMap tmWo,
-                                                        const __grid_constant__ CUtensorMap tmPo,
                                                         const UWParams p) {
     using namespace ptx;
     using namespace uw;
@@ -263,7 +262,8 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     if (kWithP) {
         // (fence + barrier above: staged P complete and visible to the TMA engine)
         if (tid == 0) {
-            tma_store_2d(&tmPo, sV, 0, (blockIdx.x * p.vh + head) * 64);
+            bulk_store(p.blocks + (static_cast<size_t>(blockIdx.x) * p.vh + head) * kUnitBlockBytes + 2 * L::kTile, sV,
+                       kChunk * kChunk * 2);
             bulk_commit();
         }
         bar_load_parity = 1;  // the V tile follows into the same buffer once the store has read it
@@ -430,7 +430,15 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     tc_fence_before_sync();
     __syncthreads();
     GDN_STAMP(10);
-    if (p.map.cu_seqlens != nullptr && n < kChunk) {
+    if (kWithP) {
+        // U and W staging tiles are adjacent: one copy (rows past the end of a sequence are zero)
+        static_assert(L::kOffV == L::kOffK + L::kTile, "U and W staging tiles must be adjacent");
+        if (tid == 0) {
+            bulk_store(p.blocks + (static_cast<size_t>(blockIdx.x) * p.vh + head) * kUnitBlockBytes, stU, 2 * L::kTile);
+            bulk_commit();
+            bulk_wait_read<0>();
+        }
+    } else if (p.map.cu_seqlens != nullptr && n < kChunk) {
         // a full-box store would spill into the next packed sequence: row-predicated stores
         store_tile_rows<128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
         store_tile_rows<128>(stW, p.w, cp.batch, cp.tok0, head, n, tid);

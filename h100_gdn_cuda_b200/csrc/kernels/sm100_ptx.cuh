@@ -94,6 +94,27 @@ GDN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fl
     }
 }
 
+// The same wait for warps that are not on a critical path: sleeps `kSleepNs` between polls so
+// that the polling does not take issue slots and shared-memory queue entries from the warps
+// that are.
+template <unsigned kSleepNs>
+GDN_DEVICE bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        __nanosleep(kSleepNs);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0) {
+            if (*abort_flag != 0) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ proxies / fences
 GDN_DEVICE void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -180,8 +201,23 @@ GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* 
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+// The same as a warp-collective call (warp-uniform arguments, one elected lane issues).
+GDN_DEVICE void bulk_load_w(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 
 // ------------------------------------------------------------------ TMA stores (shared -> global)
+// Untiled bulk copy shared -> global (bulk-group completion); same alignment rules as bulk_load.
+GDN_DEVICE void bulk_store(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                     reinterpret_cast<uint64_t>(dst)),
+                 "r"(smem_u32(src)), "r"(bytes)
+                 : "memory");
+}
 GDN_DEVICE void tma_store_4d(const void* tmap, const void* src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(tmap)),
