@@ -1,5 +1,6 @@
 // C-ABI entry points of the chunked-prefill path (see include/gdn_b200.h): tensor-map
 // construction, argument checks and launches of the tcgen05 kernels.
+#include "heuristics.hpp"
 #include "host_common.hpp"
 #include "kernels/prefill_fused.cuh"
 #include "kernels/prefill_o.cuh"
@@ -114,16 +115,18 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
     p.w = token_view(w);
     p.kh = s.num_k_heads;
     p.vh = s.num_v_heads;
+    p.num_chunks = nc;
     p.status = d->status;
     p.blocks = static_cast<uint8_t*>(blocks);
     p.p_scale = p_scale;
     constexpr int smem = UWSmem<kD>::kBytes;
+    const int grid = uw_grid(static_cast<long long>(nc) * s.num_v_heads, d->sms);
     if (q) {
         if (int rc = set_smem(gdn_uw_kernel<kD, true>, smem)) return rc;
-        gdn_uw_kernel<kD, true><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
+        gdn_uw_kernel<kD, true><<<grid, 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
     } else {
         if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
-        gdn_uw_kernel<kD, false><<<dim3(nc, s.num_v_heads), 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
+        gdn_uw_kernel<kD, false><<<grid, 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
     }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;

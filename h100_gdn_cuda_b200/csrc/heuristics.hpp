@@ -32,4 +32,9 @@ struct PrefillConfig {
 
 inline PrefillConfig prefill_config() { return PrefillConfig{4, 512}; }
 
+// Grid of the persistent WY/UT kernel: every CTA slot of the GPU, or one CTA per unit if fewer.
+inline int uw_grid(long long units, int sms) {
+    return static_cast<int>(std::min<long long>(units, static_cast<long long>(sms) * prefill_config().uw_ctas_per_sm));
+}
+
 }  // namespace gdn

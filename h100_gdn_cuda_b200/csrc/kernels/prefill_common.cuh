@@ -16,9 +16,18 @@ __device__ __forceinline__ long long gdn_clock_ordered() {
     asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
     return t;
 }
+#ifndef GDN_STAMP_BX
+#define GDN_STAMP_BX 0
+#define GDN_STAMP_BY 0
+#endif
 #define GDN_STAMP(i)                                                                  \
     do {                                                                              \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
+        if (blockIdx.x == GDN_STAMP_BX && blockIdx.y == GDN_STAMP_BY && threadIdx.x == 0)              \
+            g_phase_stamps[i] = gdn_clock_ordered();                                                  \
+    } while (0)
+#define GDN_STAMP_IF(cond, i)                                                   \
+    do {                                                                        \
+        if ((cond) && threadIdx.x == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
     } while (0)
 #define GDN_STAMP_ANY(i)                                                   \
     do {                                                                  \
@@ -28,17 +37,20 @@ __device__ __forceinline__ long long gdn_clock_ordered() {
 #define GDN_STAMP(i) \
     do {             \
     } while (0)
+#define GDN_STAMP_IF(cond, i) \
+    do {                      \
+    } while (0)
 #define GDN_STAMP_ANY(i) \
     do {                 \
     } while (0)
 #endif
 
-// per-token scalar tensor (beta or gate) as the kernels see it
 // Scratch of gdn_chunked_forward: one contiguous block per (global chunk, v-head) unit, laid out
 // exactly as the shared-memory images the state kernel wants (128-byte-swizzled 64 x 64 atoms):
 // U (16 KB), W (16 KB), P (8 KB).  One untiled bulk copy moves a whole block in either direction.
 constexpr int kUnitBlockBytes = 2 * kChunk * 128 * 2 + kChunk * kChunk * 2;
 
+// per-token scalar tensor (beta or gate) as the kernels see it
 struct ScalarView {
     const void* ptr;
     int is_f32;

@@ -36,6 +36,7 @@ struct UWParams {
     uint8_t* blocks;       // kWithP: one kUnitBlockBytes block per (global chunk, v-head), see below
     float p_scale;         // kWithP: factor folded into P (the output scale)
     int kh, vh;
+    int num_chunks;
     int* status;
 };
 
@@ -120,16 +121,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head = blockIdx.y;
-    const int khead = head / (p.vh / p.kh);
-    const ChunkPos cp = locate_chunk(p.map, blockIdx.x);
-    const int n = cp.n;
-    // beta and gate of this thread's token: requested first, used after the set-up below
-    float b_mine = 0.f, g_mine = 0.f;
-    if (tid < n) {
-        b_mine = p.beta.load(cp.batch, cp.tok0 + tid, head);
-        if (p.gate.ptr) g_mine = p.gate.load(cp.batch, cp.tok0 + tid, head);
-    }
 
     if (tid == 0) {
         *abort_flag = 0;
@@ -144,7 +135,33 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     const uint32_t tmem = *tmem_slot;
     const uint32_t tLo = tmem, tHi = tmem + (16u << 16);  // the two interleaved M=64 accumulators
 
-    GDN_STAMP(0);
+    // Persistent CTA: units (chunk, v-head) are walked with the grid as stride, heads fastest, so
+    // that the CTAs running at one time share K and Q tiles of a k-head group in L2.  Barriers,
+    // tensor memory and the tensor-map fetches are set up once per CTA instead of once per unit
+    // (a CTA per unit spent a quarter of its life being launched and retired).
+    const int total_units = p.num_chunks * p.vh;
+    uint32_t it = 0;
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++it) {
+    const int chunk = unit / p.vh, head = unit - chunk * p.vh;
+    const int khead = head / (p.vh / p.kh);
+    const ChunkPos cp = locate_chunk(p.map, chunk);
+    const int n = cp.n;
+#ifdef GDN_PHASE_TIMING
+    const bool stamp_on = blockIdx.x == GDN_STAMP_BX && it == GDN_STAMP_BY;
+#define GDN_STAMP_UW(i) GDN_STAMP_IF(stamp_on, i)
+#else
+#define GDN_STAMP_UW(i)
+#endif
+    // beta and gate of this thread's token: requested first, used after the set-up below
+    float b_mine = 0.f, g_mine = 0.f;
+    if (tid < n) {
+        b_mine = p.beta.load(cp.batch, cp.tok0 + tid, head);
+        if (p.gate.ptr) g_mine = p.gate.load(cp.batch, cp.tok0 + tid, head);
+    }
+    // one load phase per unit without P, two with it; two MMA phases per unit
+    const uint32_t load_par0 = kWithP ? 0u : (it & 1u);
+
+    GDN_STAMP_UW(0);
     if (tid == 0) {
         mbar_arrive_expect_tx(bar_load, 2 * L::kTile);
         for (int a = 0; a < NA; ++a) {
@@ -186,10 +203,10 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    GDN_STAMP(1);
+    GDN_STAMP_UW(1);
     // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
-    mbar_wait(bar_load, 0, abort_flag);
-    GDN_STAMP(2);
+    mbar_wait(bar_load, load_par0, abort_flag);
+    GDN_STAMP_UW(2);
     if (warp == 0) {  // warp-uniform issue, one elected lane
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
@@ -223,7 +240,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     __syncwarp();
     mbar_wait(bar_mma, 0, abort_flag);
     tc_fence_after_sync();
-    GDN_STAMP(3);
+    GDN_STAMP_UW(3);
     {
         // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63.
         // The decay factor exp(g_i - g_j) is shared by A (strictly lower part) and P (lower part).
@@ -262,14 +279,14 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     if (kWithP) {
         // (fence + barrier above: staged P complete and visible to the TMA engine)
         if (tid == 0) {
-            bulk_store(p.blocks + (static_cast<size_t>(blockIdx.x) * p.vh + head) * kUnitBlockBytes + 2 * L::kTile, sV,
+            bulk_store(p.blocks + static_cast<size_t>(unit) * kUnitBlockBytes + 2 * L::kTile, sV,
                        kChunk * kChunk * 2);
             bulk_commit();
         }
         bar_load_parity = 1;  // the V tile follows into the same buffer once the store has read it
     }
 
-    GDN_STAMP(4);
+    GDN_STAMP_UW(4);
     // ---- X = (I + A)^-1, in place.  Diagonal 16x16 blocks: one column per thread.
     {
         const int b = warp, j = lane & 15;
@@ -296,7 +313,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         for (int a = 0; a < NA; ++a)
             tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
     }
-    GDN_STAMP(5);
+    GDN_STAMP_UW(5);
     // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half).
     // The intermediate A_10 X_00 is parked in the unused block above the diagonal.
     {
@@ -313,7 +330,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         store_block(e, -1.f, sA, LD, i0, j0 + n0, lane);
     }
     __syncthreads();
-    GDN_STAMP(6);
+    GDN_STAMP_UW(6);
     // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result.
     // The intermediate goes to the unused upper-right quadrant; K-steps that would only meet the
     // (zero, here scratch) blocks above the diagonal are skipped.
@@ -345,7 +362,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    GDN_STAMP(7);
+    GDN_STAMP_UW(7);
     // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles written over X:
     //      every thread first pulls its 32 values of X into registers
     {
@@ -381,7 +398,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     fence_proxy_async_smem();
     __syncthreads();
 
-    GDN_STAMP(8);
+    GDN_STAMP_UW(8);
     // ---- U = T V (lanes +0), W = T' K (lanes +16)
     if (kWithP) mbar_wait(bar_load, bar_load_parity, abort_flag);
     if (warp == 0) {
@@ -403,7 +420,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     mbar_wait(bar_mma, 1, abort_flag);
     tc_fence_after_sync();
 
-    GDN_STAMP(9);
+    GDN_STAMP_UW(9);
     // ---- accumulators -> bf16 -> staged tiles (over the K and V tiles) -> coalesced stores
     uint8_t* stU = sK;
     uint8_t* stW = sV;
@@ -429,12 +446,12 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
-    GDN_STAMP(10);
+    GDN_STAMP_UW(10);
     if (kWithP) {
         // U and W staging tiles are adjacent: one copy (rows past the end of a sequence are zero)
         static_assert(L::kOffV == L::kOffK + L::kTile, "U and W staging tiles must be adjacent");
         if (tid == 0) {
-            bulk_store(p.blocks + (static_cast<size_t>(blockIdx.x) * p.vh + head) * kUnitBlockBytes, stU, 2 * L::kTile);
+            bulk_store(p.blocks + static_cast<size_t>(unit) * kUnitBlockBytes, stU, 2 * L::kTile);
             bulk_commit();
             bulk_wait_read<0>();
         }
@@ -450,7 +467,9 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         bulk_commit();
         bulk_wait_read<0>();
     }
-    GDN_STAMP(11);
+    GDN_STAMP_UW(11);
+    __syncthreads();  // staging tiles and vectors are free for the next unit
+    }                 // unit loop
     if (warp == 0) tmem_dealloc(tmem, D);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 2);
 }
