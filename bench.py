@@ -58,14 +58,33 @@ def uw_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
     return 2.0 * c * (4 * c * d) + (2.0 / 3.0) * c ** 3
 
 
+# Algorithmic HBM bytes of the two prefill kernels per (64-token chunk, v-head) unit at d = 128:
+#   gdn_uw_kernel        : K, Q tiles 16 KB each per k-head (shared by the vh/kh v-heads of a group),
+#                          V tile 16 KB in; U, W 16 KB each and P 8 KB out
+#   gdn_fused_seq_kernel : U, W, P 40 KB and K, Q (shared as above) in; O 16 KB out
+# Both sit well below the ridge of the measured peaks (1636 TFLOP/s / 6546 GB/s = 250 FLOP/B):
+# 4.37 MFLOP / 72 KB = 61 FLOP/B and 7.34 MFLOP / 72 KB = 102 FLOP/B at vh/kh = 2, so HBM is the
+# roof that bounds them.
+def uw_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
+    tile = c * d * 2
+    return 2 * tile * kh / vh + tile + 2 * tile + c * c * 2
+
+
+def seq_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
+    tile = c * d * 2
+    return 2 * tile + c * c * 2 + 2 * tile * kh / vh + tile
+
+
 # DRAM read + write bytes per launch seen by one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum), divided by the units that launch processed.  Traffic is proportional
 # to the units (every CTA streams its own tiles), so a full launch is units x this figure.
-#   gdn_fused_seq_kernel: B=2 T=4096 vh=32 capture, 238.13 MB read + 55.48 MB written, 4096 units
-#   gdn_recurrent_kernel: B=128 capture, 136.37 MB read + 84.43 MB written, 128 sequence-tokens
-#                         (part of the written state was still in L2 when the launch ended)
-NCU_FUSED_TRAFFIC_PER_UNIT = (238.132736e6 + 55.481856e6) / 4096
-NCU_DECODE_TRAFFIC_PER_TOKEN = (136.369664e6 + 84.427008e6) / 128
+#   gdn_uw_kernel        : B=2 T=4096 vh=32 capture, 135.86 MB read + 116.63 MB written, 4096 units
+#   gdn_fused_seq_kernel : same capture, 238.14 MB read + 50.45 MB written, 4096 units
+#   gdn_recurrent_kernel : B=128 capture, 136.37 MB read + 87.44 MB written, 128 sequence-tokens
+# (written data still in L2 when a launch ends is not counted by the DRAM counters)
+NCU_UW_TRAFFIC_PER_UNIT = (135.861248e6 + 116.629248e6) / 4096
+NCU_FUSED_TRAFFIC_PER_UNIT = (238.144000e6 + 50.446592e6) / 4096
+NCU_DECODE_TRAFFIC_PER_TOKEN = (136.370432e6 + 87.435776e6) / 128
 
 
 def decode_bytes_per_token(kh, vh, d) -> float:
@@ -401,8 +420,18 @@ def main():
         cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": what}
 
     seq_flops = units * seq_kernel_flops_per_unit(d)
-    achieved = seq_flops / (seq_ms * 1e-3) / 1e12
+    uw_flops = units * uw_kernel_flops_per_unit(d)
     total_flops = units * flops_per_unit(d)
+    uw_bytes = units * uw_kernel_bytes_per_unit(kh, vh, d)
+    seq_bytes = units * seq_kernel_bytes_per_unit(kh, vh, d)
+    # the dominant kernel is the one with the longer launch; both are HBM-bound (see above)
+    if uw_ms >= seq_ms:
+        dom = ("gdn_uw_kernel (WY/UT transform + intra-chunk attention block)", uw_ms, uw_bytes, uw_flops,
+               units * NCU_UW_TRAFFIC_PER_UNIT)
+    else:
+        dom = ("gdn_fused_seq_kernel (state propagation + output)", seq_ms, seq_bytes, seq_flops,
+               units * NCU_FUSED_TRAFFIC_PER_UNIT)
+    achieved = dom[2] / (dom[1] * 1e-3) / 1e9
     line = {
         "metric": "prefill_tokens_per_s", "value": world * tokens / (ms_res * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res,
@@ -412,15 +441,20 @@ def main():
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
         "gpu_launches": 2 * args.steps,
-        "roofline": {"kernel": "gdn_fused_seq_kernel (state propagation + output)", "bound": "tensor",
-                     "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": achieved / peaks["tflops"], "traffic": units * NCU_FUSED_TRAFFIC_PER_UNIT,
+        "roofline": {"kernel": dom[0], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": dom[4],
                      "traffic_source": "ncu capture at B=2 scaled by units", "peak_source": peaks["source"],
-                     "ms_per_launch": seq_ms, "flops_per_launch": seq_flops},
+                     "ms_per_launch": dom[1], "bytes_per_launch": dom[2], "flops_per_launch": dom[3],
+                     "flop_per_byte": dom[3] / dom[2]},
         "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_fused_seq_kernel_ms": seq_ms,
-                    "uw_tflops": units * uw_kernel_flops_per_unit(d) / (uw_ms * 1e-3) / 1e12,
+                    "uw_gbs": uw_bytes / (uw_ms * 1e-3) / 1e9, "uw_frac_of_hbm_peak": uw_bytes / (uw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                    "fused_gbs": seq_bytes / (seq_ms * 1e-3) / 1e9,
+                    "fused_frac_of_hbm_peak": seq_bytes / (seq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                    "uw_tflops": uw_flops / (uw_ms * 1e-3) / 1e12, "fused_tflops": seq_flops / (seq_ms * 1e-3) / 1e12,
                     "whole_step_tflops": total_flops / (ms_res * 1e-3) / 1e12,
-                    "whole_step_frac_of_tensor_peak": total_flops / (ms_res * 1e-3) / 1e12 / peaks["tflops"]},
+                    "whole_step_frac_of_tensor_peak": total_flops / (ms_res * 1e-3) / 1e12 / peaks["tflops"],
+                    "whole_step_hbm_gbs": (uw_bytes + seq_bytes) / (ms_res * 1e-3) / 1e9,
+                    "whole_step_frac_of_hbm_peak": (uw_bytes + seq_bytes) / (ms_res * 1e-3) / 1e9 / peaks["hbm_gbs"]},
         "decode": {"metric": "decode_tokens_per_s", "value": world * dB / (ms_dec * 1e-3), "unit": "tokens/s",
                    "config": "B=256 T=1 kh=16 vh=32 d=128, qk-norm, fused gating, per GPU", "ms_per_step": ms_dec,
                    "roofline": {"kernel": "gdn_recurrent_kernel", "bound": "hbm",
