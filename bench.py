@@ -14,7 +14,8 @@ The printed JSON line carries:
   e2e        the same through the public API from pinned HOST buffers: host->device copies of
              q, k, v, beta, gate and the state and the device->host copy of O and the final
              state are inside the timed region
-  roofline   for the dominant kernel (the state/output kernel), timed live with CUDA events
+  roofline   for the dominant kernel (the longer of the two prefill launches), timed live with CUDA
+             events, against the HBM roof that bounds both of them
   decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, fused gating) and its
              HBM roofline fraction
   cpu_baseline  the fp32 CPU token recurrence (the oracle) on a bounded sample, rank 0, N=1
@@ -40,6 +41,7 @@ sys.path.insert(0, ROOT)
 CFG = dict(B=4, T=4096, kh=16, vh=32, d=128)
 DECODE = dict(B=256, T=1, kh=16, vh=32, d=128)
 CHUNK = 64
+WORKLOAD = "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128 chunk=64 per GPU"
 
 
 def flops_per_unit(d: int, c: int = CHUNK) -> float:
@@ -193,7 +195,7 @@ def run_reference(args):
         "impl": "reference", "metric": "prefill_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128", "l2": "not applicable (CPU)"},
+        "config": {"workload": WORKLOAD, "sharding": "rank 0 only", "l2": "not applicable (CPU)"},
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                          "sample": "each step = B=1 x T=%d of the prefill config, fp32 torch token recurrence" % sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -436,7 +438,7 @@ def main():
         "metric": "prefill_tokens_per_s", "value": world * tokens / (ms_res * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128 chunk=64 per GPU",
+        "config": {"workload": WORKLOAD,
                    "sharding": "by sequence, no collective", "l2": "inputs (0.41 GB per step) larger than L2"},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
