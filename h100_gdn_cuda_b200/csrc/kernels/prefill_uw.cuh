@@ -61,6 +61,11 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return r;
 }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void mma_tf32(float* d, const uint32_t* a, const uint32_t* b) {
     asm volatile(
         "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     __syncthreads();
     if (tid < 64) {
         const float g = sEg[tid];
-        sG[tid] = g;
+        sG[tid] = g * 1.4426950408889634f;  // from here on the gate times log2(e): decay factors are ex2 of differences
         sEg[tid] = __expf(g);
     }
     __syncthreads();
@@ -255,12 +260,17 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         for (int j = 0; j < 32; j += 8) {
             float a[8], pq[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int col = cbase + j + e;
-                const bool low = col <= i && i < n;
-                const float dec = low ? __expf(gi - sG[col]) : 0.f;
-                a[e] = (col < i) ? bi * __uint_as_float(r[j + e]) * dec : 0.f;
-                if (kWithP) pq[e] = p.p_scale * __uint_as_float(rq[j + e]) * dec;
+            for (int e4 = 0; e4 < 2; ++e4) {
+                const float4 gc = *reinterpret_cast<const float4*>(sG + cbase + j + 4 * e4);
+                const float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = cbase + j + 4 * e4 + e;
+                    const bool low = col <= i && i < n;
+                    const float dec = low ? ex2(gi - gcv[e]) : 0.f;
+                    a[4 * e4 + e] = (col < i) ? bi * __uint_as_float(r[j + 4 * e4 + e]) * dec : 0.f;
+                    if (kWithP) pq[4 * e4 + e] = p.p_scale * __uint_as_float(rq[j + 4 * e4 + e]) * dec;
+                }
             }
             *reinterpret_cast<float4*>(&sA[i * LD + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
             *reinterpret_cast<float4*>(&sA[i * LD + cbase + j + 4]) = make_float4(a[4], a[5], a[6], a[7]);
