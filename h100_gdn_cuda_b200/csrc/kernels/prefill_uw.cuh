@@ -303,12 +303,21 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         float x[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] = (i == j) ? 1.f : 0.f;
+        // x_j = 1, x_i = -sum_{m<i} A_im x_m.  Rows are read with 16-byte loads (one address for all
+        // lanes: a broadcast); the terms that have been ready for a while are summed in one chain,
+        // so that only the newest term waits on x_{i-1}.
 #pragma unroll
         for (int i = 1; i < 16; ++i) {
+            float a[16];
+#pragma unroll
+            for (int q = 0; q < (i + 3) / 4; ++q) {
+                const float4 t = *reinterpret_cast<const float4*>(&sA[(16 * b + i) * LD + 16 * b + 4 * q]);
+                a[4 * q] = t.x; a[4 * q + 1] = t.y; a[4 * q + 2] = t.z; a[4 * q + 3] = t.w;
+            }
             float acc = 0.f;
 #pragma unroll
-            for (int m = 0; m < i; ++m) acc = fmaf(sA[(16 * b + i) * LD + 16 * b + m], x[m], acc);
-            if (i > j) x[i] = -acc;
+            for (int m = 0; m + 1 < i; ++m) acc = fmaf(a[m], x[m], acc);
+            if (i > j) x[i] = -fmaf(a[i - 1], x[i - 1], acc);
         }
         __syncwarp();  // the block is private to this warp: every lane has read it
         if (lane < 16) {
