@@ -96,7 +96,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     uint64_t* bar_ds = bars + 7;
     uint64_t* bar_o = bars + 8;
     uint64_t* bar_ofree = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* bar_full2 = bars + 10;  // [2]: P, K, Q of a stage (bar_full: U, W and the gate vectors)
+    uint64_t* bar_go = bars + 12;     // state warps are past their chunk-boundary work: the epilogue may run
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -130,6 +132,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         mbar_init(&bar_full[1], 1);
         mbar_init(&bar_empty[0], 1);
         mbar_init(&bar_empty[1], 1);
+        mbar_init(&bar_full2[0], 1);
+        mbar_init(&bar_full2[1], 1);
+        mbar_init(bar_go, 8);
         mbar_init(bar_sbf, 8);
         mbar_init(bar_d1, 1);
         mbar_init(bar_un, 8);
@@ -205,6 +210,10 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 upk[e] = lo | (hi << 16);
             }
             const int nloc = n - 32 * hf;  // tokens of this half that exist
+            // The state warps now idle until D1 arrives: the window in which the output warps (which
+            // share the schedulers) run the previous chunk's epilogue without slowing the chain down.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_go);
             mbar_wait(bar_d1, par, abort_flag);
             tc_fence_after_sync();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(40);
@@ -250,6 +259,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             publish_state();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
         }
+        if (lane == 0) mbar_arrive(bar_go);  // releases the last chunk's epilogue
         if (p.state_out) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
                                                  static_cast<long long>(row) * D + 64 * hf);
@@ -286,6 +296,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             mbar_wait_relaxed<200>(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
             if (c == 40 && otid == 0) GDN_STAMP_ANY(49);
             mbar_wait_relaxed<100>(bar_o, par, abort_flag);
+            mbar_wait_relaxed<50>(bar_go, static_cast<uint32_t>((c + 1) & 1), abort_flag);
             tc_fence_after_sync();
             if (c == 40 && otid == 0) GDN_STAMP_ANY(50);
 #pragma unroll
@@ -392,13 +403,16 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 uint8_t* st = smem + s * L::kStage;
                 const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
                 const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kUnitBlockBytes;
-                mbar_arrive_expect_tx_w(&bar_full[s], L::kStage);
-                bulk_load_w(st + L::kOffU, blk, kUnitBlockBytes, &bar_full[s]);
+                // what the serial chain needs first (W for the first MMA, U for the pass that follows)
+                // goes first and on its own barrier; P, K, Q are not needed before the second MMA group
+                mbar_arrive_expect_tx_w(&bar_full[s], 2 * L::kTile);
+                bulk_load_w(st + L::kOffU, blk, 2 * L::kTile, &bar_full[s]);
+                mbar_arrive_expect_tx_w(&bar_full2[s], L::kStage - 2 * L::kTile);
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
-                    tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full[s], a * 64, khead, tok, batch);
-                }
+                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full2[s], a * 64, khead, tok, batch);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full2[s], a * 64, khead, tok, batch);
+                bulk_load_w(st + L::kOffP, blk + 2 * L::kTile, kChunk * kChunk * 2, &bar_full2[s]);
                 if (c == 40 && lane == 0) GDN_STAMP_ANY(22);
             }
         }
@@ -441,6 +455,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 mma_commit_w(bar_d1);
                 if (c == 40) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
+                mbar_wait(&bar_full2[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
+                tc_fence_after_sync();
                 const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
                 mma_ts_w<false>(tO1, tS, q, id_sq);
 #pragma unroll
