@@ -5,6 +5,7 @@
 #include "kernels/prefill_fused.cuh"
 #include "kernels/prefill_o.cuh"
 #include "kernels/prefill_seq.cuh"
+#include "kernels/prefill_segments.cuh"
 #include "kernels/prefill_uw.cuh"
 #include "tma_host.hpp"
 
@@ -250,8 +251,15 @@ size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
     const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
-    // one block of U, W (64 x 128 bf16 each) and P (64 x 64 bf16) per (chunk, v-head)
-    return chunks * static_cast<size_t>(s->num_v_heads) * kUnitBlockBytes + 256;
+    // one block of U, W (64 x 128 bf16 each) and P (64 x 64 bf16) per (chunk, v-head); for a
+    // segmented run (few long padded sequences) three fp32 states per chain and segment on top
+    size_t bytes = chunks * static_cast<size_t>(s->num_v_heads) * kUnitBlockBytes + 256;
+    if (!s->cu_seqlens) {
+        const long long chains = static_cast<long long>(s->batch) * s->num_v_heads;
+        const SegmentPlan plan = prefill_segments(chains, (s->seq_len + kChunk - 1) / kChunk, false);
+        if (plan.num_segments > 1) bytes += static_cast<size_t>(chains) * plan.num_segments * 3 * kD * kD * sizeof(float) + 256;
+    }
+    return bytes;
 }
 
 int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
@@ -312,8 +320,38 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         p.blocks = static_cast<const uint8_t*>(a->workspace);
         constexpr int smem = FusedSmem::kBytes;
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
-        gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
-        GDN_CUDA(cudaGetLastError());
+        const long long chains = static_cast<long long>(s.batch) * s.num_v_heads;
+        const SegmentPlan plan = prefill_segments(chains, (s.seq_len + kChunk - 1) / kChunk, packed);
+        if (plan.num_segments <= 1) {
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            GDN_CUDA(cudaGetLastError());
+        } else {
+            // composite transitions of all segments, their start states, then all segments at once
+            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kUnitBlockBytes;
+            uint8_t* extra = static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256;
+            float* seg_mn = reinterpret_cast<float*>(extra);
+            float* seg_start = seg_mn + static_cast<size_t>(chains) * plan.num_segments * 2 * kD * kD;
+            p.seg_chunks = plan.seg_chunks;
+            p.num_segments = plan.num_segments;
+            p.seg_mn = seg_mn;
+            p.seg_start = seg_start;
+            p.mode = 1;
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, 2 * plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            GDN_CUDA(cudaGetLastError());
+            SegCombineParams cp{};
+            cp.seg_mn = seg_mn;
+            cp.seg_start = seg_start;
+            cp.state_in = p.state_in;
+            cp.si_ss = p.si_ss;
+            cp.si_sh = p.si_sh;
+            cp.vh = s.num_v_heads;
+            cp.num_segments = plan.num_segments;
+            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / 16), 128, 0, st>>>(cp);
+            GDN_CUDA(cudaGetLastError());
+            p.mode = 2;
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            GDN_CUDA(cudaGetLastError());
+        }
     }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
     return GDN_OK;

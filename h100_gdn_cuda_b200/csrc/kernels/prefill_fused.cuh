@@ -38,6 +38,17 @@ struct FusedParams {
     float scale;
     int* status;
     const uint8_t* blocks;  // U, W, P of every (global chunk, v-head): kUnitBlockBytes each
+    // Segmented runs (padded mode, few long sequences; see gdn_chunked_forward).  The state obeys
+    // S' = S M_c + N_c per chunk, so a segment of chunks has a composite (M, N) as well.
+    //   mode 0: one CTA walks the whole sequence (blockIdx.z = 0).
+    //   mode 1: blockIdx.z = 2 * segment + kind; no output.  kind 0 starts from S = 0 and ends with
+    //           N of the segment; kind 1 starts from S = I with U taken as 0 and ends with M.
+    //           Both are written in fp32 to seg_mn[((chain * num_segments + segment) * 2 + kind)].
+    //   mode 2: blockIdx.z = segment; starts from seg_start[chain * num_segments + segment] (fp32),
+    //           writes the output of its chunks; the last segment writes the final state.
+    int mode, seg_chunks, num_segments;
+    float* seg_mn;
+    const float* seg_start;
 };
 
 struct FusedSmem {
@@ -119,7 +130,21 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         batch = seq;
         gchunk0 = seq * p.map.chunks_per_seq;
     }
-    const int nchunks = static_cast<int>((seq_tokens + kChunk - 1) / kChunk);
+    int nchunks = static_cast<int>((seq_tokens + kChunk - 1) / kChunk);
+    // A segment is handled as a sequence of its own: shift the token and chunk origins.
+    const int segment = p.mode == 1 ? static_cast<int>(blockIdx.z >> 1) : (p.mode == 2 ? static_cast<int>(blockIdx.z) : 0);
+    const int seg_kind = p.mode == 1 ? static_cast<int>(blockIdx.z & 1) : 0;
+    const bool emit_o = p.mode != 1;
+    const bool zero_u = p.mode == 1 && seg_kind == 1;
+    if (p.mode != 0) {
+        const int c0 = min(segment * p.seg_chunks, nchunks);
+        const int c1 = min(c0 + p.seg_chunks, nchunks);
+        seq_tok0 += static_cast<long long>(c0) * kChunk;
+        seq_tokens = min(seq_tokens - static_cast<long long>(c0) * kChunk, static_cast<long long>(c1 - c0) * kChunk);
+        gchunk0 += c0;
+        nchunks = c1 - c0;
+    }
+    const long long chain = static_cast<long long>(seq) * p.vh + head;
     auto chunk_n = [&](int c) {
         const long long rem = seq_tokens - static_cast<long long>(c) * kChunk;
         return rem < kChunk ? static_cast<int>(rem) : kChunk;
@@ -162,7 +187,18 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         for (int k = 0; k < 8; ++k)
             uoff8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
         float S[64];
-        if (p.state_in) {
+        if (p.mode == 2) {
+            const float4* src = reinterpret_cast<const float4*>(p.seg_start + (chain * p.num_segments + segment) * (D * D) +
+                                                                static_cast<long long>(row) * D + 64 * hf);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                const float4 v = __ldg(src + q);
+                S[4 * q] = v.x; S[4 * q + 1] = v.y; S[4 * q + 2] = v.z; S[4 * q + 3] = v.w;
+            }
+        } else if (p.mode == 1) {
+#pragma unroll
+            for (int q = 0; q < 64; ++q) S[q] = (seg_kind == 1 && row == 64 * hf + q) ? 1.f : 0.f;
+        } else if (p.state_in) {
             const uint4* src = reinterpret_cast<const uint4*>(p.state_in + seq * p.si_ss + head * p.si_sh +
                                                               static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll
@@ -207,7 +243,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 const int i0 = 32 * hf + 2 * e;
                 const uint32_t lo = *reinterpret_cast<const uint16_t*>(sU + i0 * 128 + uoff8[i0 & 7]);
                 const uint32_t hi = *reinterpret_cast<const uint16_t*>(sU + (i0 + 1) * 128 + uoff8[(i0 + 1) & 7]);
-                upk[e] = lo | (hi << 16);
+                upk[e] = zero_u ? 0u : (lo | (hi << 16));
             }
             const int nloc = n - 32 * hf;  // tokens of this half that exist
             // The state warps now idle until D1 arrives: the window in which the output warps (which
@@ -260,7 +296,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
         }
         if (lane == 0) mbar_arrive(bar_go);  // releases the last chunk's epilogue
-        if (p.state_out) {
+        if (p.mode == 1) {
+            float4* d4 = reinterpret_cast<float4*>(p.seg_mn + ((chain * p.num_segments + segment) * 2 + seg_kind) * (D * D) +
+                                                   static_cast<long long>(row) * D + 64 * hf);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) d4[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
+        } else if (p.state_out && (p.mode == 0 || segment == p.num_segments - 1)) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
                                                  static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll
@@ -286,7 +327,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         for (int k = 0; k < 8; ++k)
             off8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
         const bool packed = p.map.cu_seqlens != nullptr;
-        for (int c = 0; c < nchunks; ++c) {
+        for (int c = 0; c < (emit_o ? nchunks : 0); ++c) {
             const uint32_t par = static_cast<uint32_t>(c & 1);
             const int n = chunk_n(c);
             const float* gb = gate_buf(c);
@@ -457,11 +498,13 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // O1 = S_bf Q^T
                 mbar_wait(&bar_full2[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
-                const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
-                mma_ts_w<false>(tO1, tS, q, id_sq);
+                if (emit_o) {
+                    const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
+                    mma_ts_w<false>(tO1, tS, q, id_sq);
 #pragma unroll
-                for (int ks = 1; ks < 8; ++ks)
-                    mma_ts_w<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
+                    for (int ks = 1; ks < 8; ++ks)
+                        mma_ts_w<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
+                }
                 if (c == 40) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
@@ -473,14 +516,16 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 mma_commit_w(bar_ds);
                 if (c == 40) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
-                if (c > 0) {
-                    mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
-                    tc_fence_after_sync();
-                }
-                mma_ts_w<false>(tO2, tUa, pp, id_sq);
+                if (emit_o) {
+                    if (c > 0) {
+                        mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
+                        tc_fence_after_sync();
+                    }
+                    mma_ts_w<false>(tO2, tUa, pp, id_sq);
 #pragma unroll
-                for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
-                mma_commit_w(bar_o);
+                    for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
+                    mma_commit_w(bar_o);
+                }
                 mma_commit_w(&bar_empty[s]);
                 if (c == 40) GDN_STAMP_ANY(37);
                 if (c == 41) GDN_STAMP_ANY(38);

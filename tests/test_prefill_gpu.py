@@ -132,6 +132,21 @@ def test_chunked_forward_padded(gdn, B, T, kh, vh, d, mild):
     close(s, s_ref, "final state")
 
 
+@pytest.mark.parametrize("B,T,kh,vh,with_state", [(1, 6161, 1, 2, True), (3, 6144, 4, 8, True), (1, 9000, 2, 2, False),
+                                                 (2, 16384 + 70, 1, 1, True)])
+def test_chunked_forward_segmented(gdn, B, T, kh, vh, with_state):
+    """Few long padded sequences take the segmented path (composite transitions per segment, start
+    states chained in fp32, all segments at once); the result must still be the token recurrence."""
+    p = synthetic.prefill_inputs(B, T, kh, vh, 128, seed=T, with_state=with_state)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"],
+                                   p["state"].float() if with_state else None)
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"])
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final state")
+
+
 def test_chunked_forward_no_state_custom_scale(gdn):
     p = synthetic.prefill_inputs(2, 300, 2, 4, 128, seed=77, with_state=False, mild_gate=True)
     o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], None, scale=0.5)
