@@ -18,6 +18,7 @@ The printed JSON line carries:
              events, against the HBM roof that bounds both of them
   decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, fused gating) and its
              HBM roofline fraction
+  long_context  the B=2, T=131072 layer with the value heads sharded over the N ranks (strong scaling)
   cpu_baseline  the fp32 CPU token recurrence (the oracle) on a bounded sample, rank 0, N=1
 
 `--impl reference` times only that CPU recurrence (the reference library's own sm_90a kernels
@@ -243,6 +244,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-long-context", action="store_true", help="skip the B=2 T=131072 head-sharded leg")
     ap.add_argument("--only", default=None, choices=["prefill", "decode"],
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
@@ -407,7 +409,35 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms_dec_kernel = e0.elapsed_time(e1) / dsteps
-    # the sampler ran across every timed region above (prefill resident, end to end, decode)
+    # ---------------- long context: B=2, T=131072, the 32 value heads sharded over the ranks
+    # (each rank takes vh / world v-heads with their q/k heads; no collective).  Strong scaling:
+    # every rank works on the same two sequences, the layer's time is the slowest rank's.
+    lc = None
+    if not args.no_long_context and vh % world == 0 and kh % world == 0:
+        lB, lT, lvh, lkh = 2, 131072, vh // world, kh // world
+        gen = torch.Generator(device=dev).manual_seed(7 + rank)
+        lq = torch.nn.functional.normalize(torch.randn(lB, lT, lkh, d, device=dev, generator=gen), dim=-1).bfloat16()
+        lk = torch.nn.functional.normalize(torch.randn(lB, lT, lkh, d, device=dev, generator=gen), dim=-1).bfloat16()
+        lv = torch.randn(lB, lT, lvh, d, device=dev, generator=gen).bfloat16()
+        lbeta = torch.sigmoid(torch.randn(lB, lT, lvh, device=dev, generator=gen)).bfloat16()
+        lg = -torch.nn.functional.softplus(torch.randn(lB, lT, lvh, device=dev, generator=gen)) * 0.1
+        ls0 = (torch.randn(lB, lvh, d, d, device=dev, generator=gen) * 0.02).bfloat16()
+        lws = torch.empty(gdn.api.chunked_forward_workspace_bytes(lB, lT, lvh), dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            gdn.chunked_forward(lq, lk, lv, lbeta, lg, None, ls0, _workspace=lws)
+        barrier()
+        lsteps = 5
+        e0.record()
+        for _ in range(lsteps):
+            gdn.chunked_forward(lq, lk, lv, lbeta, lg, None, ls0, _workspace=lws)
+        e1.record()
+        barrier()
+        ms_lc = max_over_ranks(e0.elapsed_time(e1) / lsteps)
+        lc = {"metric": "prefill_tokens_per_s", "value": lB * lT / (ms_lc * 1e-3), "unit": "tokens/s", "scaling": "strong",
+              "config": "B=2 T=131072 kh=16 vh=32 d=128, value heads sharded over %d GPU(s): %d v-heads per GPU" % (world, lvh),
+              "ms_per_step": ms_lc}
+        del lq, lk, lv, lbeta, lg, ls0, lws
+    # the sampler ran across every timed region above (prefill resident, end to end, decode, long context)
     clocks = sampler.stop() if rank == 0 else None
     dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
 
@@ -465,6 +495,7 @@ def main():
                                 "frac_of_nominal_8TBs": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / 8000.0,
                                 "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes,
                                 "traffic": dB * NCU_DECODE_TRAFFIC_PER_TOKEN}},
+        "long_context": lc,
         "clocks": clocks,
     }
     if cpu is not None:
