@@ -265,11 +265,20 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
     torch.cuda.set_device(local)
     if world > 1:
+        # NCCL prints a version banner on stdout when it initialises; stdout must carry the one JSON
+        # line only, so it points at stderr until the first collective has run.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if rank == 0:
         build.build()
     if world > 1:
         dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
     gdn.init(ROOT, os.environ.get("CUDA_HOME", "/usr/local/cuda"))
     peaks = load_peaks()
     dev = torch.device("cuda", local)
