@@ -121,8 +121,9 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     float* sG = sBeta + 64;
     float* sEg = sG + 64;
     uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
-    uint64_t* bar_mma = bar_load + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_load + 2);
+    uint64_t* bar_mma = bar_load + 1;   // first MMA groups: one commit per issuing warp
+    uint64_t* bar_mma2 = bar_load + 2;  // U and W MMAs: two issuing warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_load + 3);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -130,7 +131,8 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar_load, 1);
-        mbar_init(bar_mma, 1);
+        mbar_init(bar_mma, kWithP ? 4 : 2);
+        mbar_init(bar_mma2, 2);
         mbar_fence_init();
     }
     if (warp == 0) tmem_alloc(tmem_slot, D);
@@ -212,38 +214,30 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
     mbar_wait(bar_load, load_par0, abort_flag);
     GDN_STAMP_UW(2);
-    if (warp == 0) {  // warp-uniform issue, one elected lane
+    // Every accumulator has its own issuing warp (warp-uniform issue, one elected lane): the issue
+    // rate of one warp, not the tensor pipe, is what bounds these small MMAs.
+    //   warp 0: K K^T columns 0-31 (lanes +0)    warp 1: K K^T columns 32-63 (lanes +16)
+    //   warp 2: Q K^T columns 0-31               warp 3: Q K^T columns 32-63
+    if (warp < (kWithP ? 4 : 2)) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
         const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sK), 0, 1024);
-        const uint64_t dk1 = desc_advance(dk0, 32 * 128);  // rows 32-63 of the K tile
         const uint64_t dq0 = make_smem_desc_sw128(smem_u32(sV), 0, 1024);
+        const uint64_t da = (warp & 2) ? dq0 : dk0;                             // A: Q or K tile
+        const uint64_t db = (warp & 1) ? desc_advance(dk0, 32 * 128) : dk0;     // B: rows 32-63 or 0-31 of K
+        const uint32_t tacc = ((warp & 1) ? tHi : tLo) + ((warp & 2) ? 32u : 0u);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = kmajor_step(ks, 8192);
-            const uint64_t a = desc_advance(dk0, off), b1 = desc_advance(dk1, off);
-            if (ks == 0) {
-                mma_ss_w<false>(tLo, a, a, idesc);
-                mma_ss_w<false>(tHi, a, b1, idesc);
-            } else {
-                mma_ss_w<true>(tLo, a, a, idesc);
-                mma_ss_w<true>(tHi, a, b1, idesc);
-            }
-            if (kWithP) {  // Q K^T the same way, into columns 32-63
-                const uint64_t q = desc_advance(dq0, off);
-                if (ks == 0) {
-                    mma_ss_w<false>(tLo + 32, q, a, idesc);
-                    mma_ss_w<false>(tHi + 32, q, b1, idesc);
-                } else {
-                    mma_ss_w<true>(tLo + 32, q, a, idesc);
-                    mma_ss_w<true>(tHi + 32, q, b1, idesc);
-                }
-            }
+            if (ks == 0)
+                mma_ss_w<false>(tacc, desc_advance(da, off), desc_advance(db, off), idesc);
+            else
+                mma_ss_w<true>(tacc, desc_advance(da, off), desc_advance(db, off), idesc);
         }
         mma_commit_w(bar_mma);
     }
     __syncwarp();
-    mbar_wait(bar_mma, 0, abort_flag);
+    mbar_wait(bar_mma, it & 1u, abort_flag);
     tc_fence_after_sync();
     GDN_STAMP_UW(3);
     {
@@ -420,23 +414,19 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     GDN_STAMP_UW(8);
     // ---- U = T V (lanes +0), W = T' K (lanes +16)
     if (kWithP) mbar_wait(bar_load, bar_load_parity, abort_flag);
-    if (warp == 0) {
+    if (warp < 2) {  // warp 0 issues U, warp 1 issues W
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
-        const uint64_t dt1 = make_smem_desc_sw128(smem_u32(sT), 0, 1024);
-        const uint64_t dt2 = make_smem_desc_sw128(smem_u32(sT2), 0, 1024);
-        const uint64_t dv = make_smem_desc_sw128(smem_u32(sV), 8192, 1024);
-        const uint64_t dk = make_smem_desc_sw128(smem_u32(sK), 8192, 1024);
-        mma_ss_w<false>(tLo, dt1, dv, idesc);
+        const uint64_t dt = make_smem_desc_sw128(smem_u32(warp ? sT2 : sT), 0, 1024);
+        const uint64_t db = make_smem_desc_sw128(smem_u32(warp ? sK : sV), 8192, 1024);  // read MN-major
+        const uint32_t tacc = warp ? tHi : tLo;
+        mma_ss_w<false>(tacc, dt, db, idesc);
 #pragma unroll
-        for (int ks = 1; ks < 4; ++ks) mma_ss_w<true>(tLo, desc_advance(dt1, ks * 32), desc_advance(dv, ks * 2048), idesc);
-        mma_ss_w<false>(tHi, dt2, dk, idesc);
-#pragma unroll
-        for (int ks = 1; ks < 4; ++ks) mma_ss_w<true>(tHi, desc_advance(dt2, ks * 32), desc_advance(dk, ks * 2048), idesc);
-        mma_commit_w(bar_mma);
+        for (int ks = 1; ks < 4; ++ks) mma_ss_w<true>(tacc, desc_advance(dt, ks * 32), desc_advance(db, ks * 2048), idesc);
+        mma_commit_w(bar_mma2);
     }
     __syncwarp();
-    mbar_wait(bar_mma, 1, abort_flag);
+    mbar_wait(bar_mma2, it & 1u, abort_flag);
     tc_fence_after_sync();
 
     GDN_STAMP_UW(9);
