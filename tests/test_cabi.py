@@ -66,3 +66,19 @@ def test_struct_sizes_match_c(lib):
                                      _cabi.RecurrentArgs, _cabi.ComputeUWArgs, _cabi.SeqStateArgs,
                                      _cabi.ComputeOArgs, _cabi.ChunkedArgs)]
     assert sizes == py
+
+
+def test_workspace_bytes(lib):
+    """Scratch of chunked_forward: 40 KB per (64-token chunk, v-head); for few long padded sequences
+    three fp32 states per chain and segment on top (the segmented state propagation)."""
+    from h100_gdn_cuda_b200 import api
+    unit = 2 * 64 * 128 * 2 + 64 * 64 * 2
+    assert api.chunked_forward_workspace_bytes(4, 4096, 32) == 4 * 64 * 32 * unit + 256
+    assert api.chunked_forward_workspace_bytes(1, 65, 2) == 2 * 2 * unit + 256        # ragged tail: whole chunks
+    # packed mode counts chunks, not tokens
+    assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True) == 6 * 4 * unit + 256
+    # B=2, T=131072, 4 v-heads: 8 chains -> 16 segments
+    long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4)
+    assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 16 * 3 * 128 * 128 * 4 + 256
+    # 128 chains: never segmented
+    assert api.chunked_forward_workspace_bytes(4, 131072, 32) == 4 * 2048 * 32 * unit + 256
