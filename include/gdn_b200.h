@@ -209,7 +209,10 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * fp32 or bf16 gate, token-major beta; writes `out` (like v) and final_state.  The per-chunk
  * state tensor of the reference is never materialised.  `workspace` is caller-provided device
  * memory of at least gdn_chunked_forward_workspace_bytes(&shape) bytes, 256-byte aligned; its
- * contents need not be initialised and are garbage afterwards. */
+ * contents need not be initialised and are garbage afterwards.  It holds one 40 KiB block per
+ * 64-token chunk and v-head (U, W and the intra-chunk attention block) and, when few long padded
+ * sequences are propagated in segments, three fp32 states (192 KiB) per (sequence, v-head) and
+ * segment. */
 typedef struct {
     GdnShape shape;
     GdnTokenTensor q, k, v, out;
@@ -241,7 +244,8 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  *     GDN_STATIC_SCRATCH_BYTES (80 MiB + 256 bytes).  The scratch holds U and W (512 bytes per
  *     token and v-head) and the intra-chunk attention blocks (8 KiB per 64-token chunk and
  *     v-head), so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
- *     tokens of 32 v-heads.  Larger problems are refused with GDN_ERR_WORKSPACE and a message.
+ *     tokens of 32 v-heads (less where long sequences of few heads add their segment states).
+ *     Larger problems are refused with GDN_ERR_WORKSPACE and a message.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address; make that first
  *     call outside any stream capture.
