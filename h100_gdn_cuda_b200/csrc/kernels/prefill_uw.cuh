@@ -48,7 +48,7 @@ struct UWSmem {
     static constexpr int kOffV = kOffK + kTile;
     static constexpr int kOffA = kOffV + kTile;           // A, overwritten block by block with X = (I+A)^-1;
                                                           // blocks above the diagonal are scratch; later T and T'
-    static constexpr int kOffVec = kOffA + 64 * kLd * 4;  // beta[64], g[64], e^g[64]
+    static constexpr int kOffVec = kOffA + 64 * kLd * 4;  // beta[64], g log2(e) [64], beta e^g [64]
     static constexpr int kOffBar = kOffVec + 3 * 64 * 4;  // 2 mbarriers, tmem slot, abort flag
     static constexpr int kBytes = kOffBar + 64 + 1024;    // + alignment slack
     static_assert(64 * kLd * 4 >= 2 * 8192, "T and T' must fit over A");
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     float* sA = reinterpret_cast<float*>(smem + L::kOffA);  // A, then X in place
     float* sBeta = reinterpret_cast<float*>(smem + L::kOffVec);
     float* sG = sBeta + 64;
-    float* sEg = sG + 64;
+    float* sEg = sG + 64;  // beta e^g per token
     uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* bar_mma = bar_load + 1;   // first MMA groups: one commit per issuing warp
     uint64_t* bar_mma2 = bar_load + 2;  // U and W MMAs: two issuing warps
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     if (tid < 64) {
         const float g = sEg[tid];
         sG[tid] = g * 1.4426950408889634f;  // from here on the gate times log2(e): decay factors are ex2 of differences
-        sEg[tid] = __expf(g);
+        sEg[tid] = b_mine * __expf(g);  // beta e^g: the column factor of T' = X diag(beta e^g)
     }
     __syncthreads();
 
@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
                 const int j = ch * 8 + e * 2;
                 const float v0 = xs[j] * bt[j], v1 = xs[j + 1] * bt[j + 1];
                 t1[e] = pack_bf16(v0, v1);
-                t2[e] = pack_bf16(v0 * eg[j], v1 * eg[j + 1]);
+                t2[e] = pack_bf16(xs[j] * eg[j], xs[j + 1] * eg[j + 1]);
             }
             const uint32_t off = sw128_offset(i, c0 + ch * 8);
             *reinterpret_cast<uint4*>(sT + off) = make_uint4(t1[0], t1[1], t1[2], t1[3]);

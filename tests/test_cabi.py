@@ -82,3 +82,35 @@ def test_workspace_bytes(lib):
     assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 16 * 3 * 128 * 128 * 4 + 256
     # 128 chains: never segmented
     assert api.chunked_forward_workspace_bytes(4, 131072, 32) == 4 * 2048 * 32 * unit + 256
+
+
+def test_segment_plan_heuristic():
+    """Host-side choice of the number of segments for the state propagation (heuristics.hpp)."""
+    import subprocess, tempfile, textwrap
+    src = textwrap.dedent('''
+        #include <cstdio>
+        #include "heuristics.hpp"
+        int main() {
+            const long long chains[] = {8, 16, 32, 64, 128, 2, 8, 8};
+            const int chunks[] = {2048, 2048, 2048, 2048, 64, 97, 2048, 40};
+            const bool packed[] = {false, false, false, false, false, false, true, false};
+            for (int i = 0; i < 8; ++i) {
+                const gdn::SegmentPlan p = gdn::prefill_segments(chains[i], chunks[i], packed[i]);
+                std::printf("%d %d\\n", p.num_segments, p.seg_chunks);
+            }
+            return 0;
+        }''')
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "h.cpp")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "h")
+        subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(ROOT, "h100_gdn_cuda_b200", "csrc"), c, "-o", exe])
+        rows = [tuple(int(x) for x in l.split()) for l in subprocess.check_output([exe]).decode().splitlines()]
+    assert rows[0] == (16, 128)          # 8 chains: two CTA waves of short segments beat one of long ones
+    assert rows[1][0] == 9               # 16 chains: 9 segments fill 144 SMs in the second pass
+    assert rows[2][0] >= 2               # 32 chains: still worth it
+    assert rows[3] == (1, 2048)          # 64 chains: three passes cost more than they save
+    assert rows[4] == (1, 64)            # the benchmark shape is never segmented
+    assert rows[5][0] == 3 and rows[5][0] * rows[5][1] >= 97
+    assert rows[6] == (1, 2048)          # packed mode: not segmented
+    assert rows[7] == (1, 40)            # too short for 32-chunk segments
