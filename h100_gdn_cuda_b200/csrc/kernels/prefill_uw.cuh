@@ -5,21 +5,24 @@
 // sm90_bf16_compute_u_w (gdn_cuda/include/gdn_cuda/kernels/sm90_bf16_gdn_compute_u_w.cuh:153-667),
 // using the canonical W (gate folded in before the solve).
 //
-// One CTA of 128 threads per unit, three CTAs per SM.  tcgen05 tensor cores do the three
-// big contractions with the TMA-loaded tiles used as they are:
-//   K K^T      : two M=64 N=32 K=D MMAs (columns 0-31 and 32-63 of the result) whose
-//                accumulators are interleaved in the same tensor-memory columns (lanes +0 and
-//                +16 of every 32-lane quarter), so one 32-lane load hands every thread of a
-//                warp half a row;
+// Persistent CTAs of 128 threads (four per SM) walk the (chunk, v-head) units.  tcgen05 tensor
+// cores do the big contractions with the TMA-loaded tiles used as they are:
+//   K K^T, Q K^T : M=64 N=32 K=D MMAs, one accumulator per issuing warp (columns 0-31 and 32-63 of
+//                each product); the two halves of a product are interleaved in the same
+//                tensor-memory columns (lanes +0 and +16 of every 32-lane quarter), so one 32-lane
+//                load hands every thread of a warp half a row;
 //   U = T V    : M=64 N=D K=64, A = T (bf16, written by the CTA), B = the V tile read MN-major;
 //   W = T' K   : M=64 N=D K=64, A = T' = X diag(beta e^g), B = the K tile read MN-major;
 //                U and W are interleaved the same way (U in lanes +0, W in lanes +16).
-// The unit-lower-triangular inverse: the 16x16 diagonal blocks in fp32 by
-// forward substitution (one column per thread), then two levels of recursive doubling
-// (16 -> 32 -> 64) whose block products use warp-level tensor-core MMAs on TF32 operands with
-// fp32 accumulation.
-// Tensor memory: D columns.  Shared memory: K and V tiles (later the U/W staging), A (later
-// T and T'), X, and a small scratch: about 73 KB.
+// One pass over the first accumulators forms A (fp32, shared memory) and, with kWithP, the
+// intra-chunk attention block P (bf16) with one ex2 per element.  The unit-lower-triangular
+// inverse: the 16x16 diagonal blocks in fp32 by forward substitution (one column per thread),
+// then two levels of recursive doubling (16 -> 32 -> 64) whose block products use warp-level
+// tensor-core MMAs on TF32 operands with fp32 accumulation, all in place.
+// Tensor memory: D columns.  Shared memory (52 KB): the K tile (later the U staging tile), a
+// second tile buffer (Q, then the staged P, then V, then the W staging tile) and A (later T, T').
+// With kWithP (the whole-layer path) U, W, P leave as one contiguous unit block by bulk copies;
+// without it U and W go to the caller's token-major tensors.
 #pragma once
 #include <cuda.h>
 
