@@ -5,6 +5,7 @@
 // tiles); what remains to choose is how many CTAs share an SM and how large a persistent grid is.
 #pragma once
 #include <algorithm>
+#include <cstdlib>
 
 namespace gdn {
 
@@ -37,7 +38,7 @@ inline PrefillConfig prefill_config() { return PrefillConfig{4, 512}; }
 // S' = S M_c + N_c per chunk, so the sequence is cut into P segments: one launch finds every
 // segment's composite (M, N) (two CTAs per chain and segment), a small kernel chains them into the
 // segments' start states, and a second launch of the state kernel produces the output of all
-// segments at once.  Three passes instead of one, P segments wide: worth it from P = 3 on.
+// segments at once.  Three passes instead of one, P segments wide.
 // The plan must not depend on the device (the scratch size is computed without one), so it is
 // made for the 148 SMs of a B200.
 struct SegmentPlan {
@@ -48,18 +49,22 @@ inline SegmentPlan prefill_segments(long long chains, int chunks_per_seq, bool p
     SegmentPlan plan{1, chunks_per_seq};
     if (packed || chains <= 0) return plan;
     constexpr long long kSms = 148;
-    // cost model in units of "one chunk of the state kernel": a CTA wave of the first pass costs
-    // 0.8 per chunk (no output), of the second 1.0; waves = CTAs / SMs rounded up
-    auto waves = [&](long long ctas) { return static_cast<double>((ctas + kSms - 1) / kSms); };
-    const double n = chunks_per_seq;
-    double best = waves(chains) * n * 0.75;  // segment only for a gain of a quarter or more
-    for (int P = 2; P <= 16 && chunks_per_seq / P >= 32; ++P) {
-        const double len = static_cast<double>((chunks_per_seq + P - 1) / P);
-        const double cost = waves(2 * chains * P) * len * 0.8 + waves(chains * P) * len;
+    // Cost model fitted to measurements (B=1..2, T=4096..131072, 4..32 v-heads), in units of "one
+    // chunk of the state kernel": a CTA costs its chunks plus about 3 for start-up and pipeline
+    // fill; a launch costs that times its CTA waves.  Plans whose second launch needs more than
+    // one wave, or whose first needs more than two, measured worse than the model and are not made.
+    auto waves = [&](long long ctas) { return (ctas + kSms - 1) / kSms; };
+    constexpr int kFixed = 3, kMinSegment = 32;
+    double best = 0.8 * static_cast<double>(waves(chains) * (chunks_per_seq + kFixed));
+    for (int P = 2; P <= 16 && chunks_per_seq / P >= kMinSegment; ++P) {
+        const long long w1 = waves(2 * chains * P), w3 = waves(chains * P);
+        if (w3 > 1 || w1 > 2) break;
+        const int len = (chunks_per_seq + P - 1) / P;
+        const double cost = static_cast<double>((w1 + w3) * (len + kFixed));
         if (cost < best) {
             best = cost;
             plan.num_segments = P;
-            plan.seg_chunks = (chunks_per_seq + P - 1) / P;
+            plan.seg_chunks = len;
         }
     }
     return plan;
