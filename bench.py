@@ -81,12 +81,12 @@ def seq_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float
 # DRAM read + write bytes per launch seen by one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum), divided by the units that launch processed.  Traffic is proportional
 # to the units (every CTA streams its own tiles), so a full launch is units x this figure.
-#   gdn_uw_kernel        : B=2 T=4096 vh=32 capture, 135.86 MB read + 116.63 MB written, 4096 units
-#   gdn_fused_seq_kernel : same capture, 238.14 MB read + 50.45 MB written, 4096 units
+#   gdn_uw_kernel        : B=2 T=4096 vh=32 capture, 135.84 MB read + 116.15 MB written, 4096 units
+#   gdn_fused_seq_kernel : same capture, 238.15 MB read + 50.26 MB written, 4096 units
 #   gdn_recurrent_kernel : B=128 capture, 136.37 MB read + 87.44 MB written, 128 sequence-tokens
 # (written data still in L2 when a launch ends is not counted by the DRAM counters)
-NCU_UW_TRAFFIC_PER_UNIT = (135.861248e6 + 116.629248e6) / 4096
-NCU_FUSED_TRAFFIC_PER_UNIT = (238.144000e6 + 50.446592e6) / 4096
+NCU_UW_TRAFFIC_PER_UNIT = (135.840512e6 + 116.147456e6) / 4096
+NCU_FUSED_TRAFFIC_PER_UNIT = (238.145280e6 + 50.258944e6) / 4096
 NCU_DECODE_TRAFFIC_PER_TOKEN = (136.370432e6 + 87.435776e6) / 128
 
 
