@@ -489,10 +489,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 tc_fence_after_sync();
                 if (c == 40) GDN_STAMP_ANY(32);
                 // D1 = -(S_bf W^T)
-                mma_ts_w<false>(tD1, tS, w, id_sw);
-#pragma unroll
-                for (int ks = 1; ks < 8; ++ks)
-                    mma_ts_w<true>(tD1, tS + ks * 8, desc_advance(w, kmajor_step(ks, 8192)), id_sw);
+                mma_ts_k128_w<false>(tD1, tS, w, id_sw);
                 mma_commit_w(bar_d1);
                 if (c == 40) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
@@ -500,19 +497,14 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 tc_fence_after_sync();
                 if (emit_o) {
                     const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
-                    mma_ts_w<false>(tO1, tS, q, id_sq);
-#pragma unroll
-                    for (int ks = 1; ks < 8; ++ks)
-                        mma_ts_w<true>(tO1, tS + ks * 8, desc_advance(q, kmajor_step(ks, 8192)), id_sq);
+                    mma_ts_k128_w<false>(tO1, tS, q, id_sq);
                 }
                 if (c == 40) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
                 if (c == 40) GDN_STAMP_ANY(35);
                 // dS = Un_b K
-                mma_ts_w<false>(tDS, tUb, k, id_ds);
-#pragma unroll
-                for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tDS, tUb + ks * 8, desc_advance(k, ks * 2048), id_ds);
+                mma_ts_k64_w<false, 128>(tDS, tUb, k, id_ds);
                 mma_commit_w(bar_ds);
                 if (c == 40) GDN_STAMP_ANY(36);
                 // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
@@ -521,9 +513,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                         mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
                         tc_fence_after_sync();
                     }
-                    mma_ts_w<false>(tO2, tUa, pp, id_sq);
-#pragma unroll
-                    for (int ks = 1; ks < 4; ++ks) mma_ts_w<true>(tO2, tUa + ks * 8, desc_advance(pp, ks * 32), id_sq);
+                    mma_ts_k64_w<false, 2>(tO2, tUa, pp, id_sq);
                     mma_commit_w(bar_o);
                 }
                 mma_commit_w(&bar_empty[s]);

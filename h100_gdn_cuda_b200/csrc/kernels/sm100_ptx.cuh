@@ -411,6 +411,54 @@ GDN_DEVICE void mma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint
         "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(kAccumulate ? 1 : 0)
         : "memory");
 }
+// Eight K-steps (K = 128) of one accumulation as a single warp-collective issue: A from tensor
+// memory (8 columns per step), B a K-major tile of two 64-column atoms 8192 bytes apart.  One
+// election serves all eight instructions.
+template <bool kAccumulateFirst>
+GDN_DEVICE void mma_ts_k128_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t.reg .pred pa;\n\t.reg .pred pt;\n\t.reg .b32 ta;\n\t.reg .b64 bd;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pa;\n\t"
+        "add.u32 ta, %1, 8;\n\tadd.u64 bd, %2, 2;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 16;\n\tadd.u64 bd, %2, 4;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 24;\n\tadd.u64 bd, %2, 6;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 32;\n\tadd.u64 bd, %2, 512;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 40;\n\tadd.u64 bd, %2, 514;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 48;\n\tadd.u64 bd, %2, 516;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 56;\n\tadd.u64 bd, %2, 518;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(kAccumulateFirst ? 1 : 0)
+        : "memory");
+}
+// Four K-steps (K = 64) the same way; the B descriptor advances by `kStep16` 16-byte units per step
+// (2 for a K-major tile, 128 for an MN-major one).
+template <bool kAccumulateFirst, int kStep16>
+GDN_DEVICE void mma_ts_k64_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t.reg .pred pa;\n\t.reg .pred pt;\n\t.reg .b32 ta;\n\t.reg .b64 bd;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %4, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pa;\n\t"
+        "add.u32 ta, %1, 8;\n\tadd.u64 bd, %2, %5;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 16;\n\tadd.u64 bd, %2, %6;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t"
+        "add.u32 ta, %1, 24;\n\tadd.u64 bd, %2, %7;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], bd, %3, pt;\n\t}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(kAccumulateFirst ? 1 : 0), "n"(kStep16), "n"(2 * kStep16),
+        "n"(3 * kStep16)
+        : "memory");
+}
 GDN_DEVICE void mma_commit_w(uint64_t* bar) {
     asm volatile(
         "{\n\t.reg .pred pe;\n\t"
