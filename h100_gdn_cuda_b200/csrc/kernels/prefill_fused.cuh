@@ -264,12 +264,22 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 }
                 tmem_wait_ld();
                 uint32_t wa[16], wb[16];
+                if (nloc >= 32) {  // every token of this half exists (all chunks but a ragged last one)
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float u0 = 2 * e < nloc ? bf16_lo(upk[e]) + __uint_as_float(r[2 * e]) : 0.f;
-                    const float u1 = 2 * e + 1 < nloc ? bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]) : 0.f;
-                    wa[e] = pack_bf16(u0, u1);
-                    wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
+                    for (int e = 0; e < 16; ++e) {
+                        const float u0 = bf16_lo(upk[e]) + __uint_as_float(r[2 * e]);
+                        const float u1 = bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]);
+                        wa[e] = pack_bf16(u0, u1);
+                        wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float u0 = 2 * e < nloc ? bf16_lo(upk[e]) + __uint_as_float(r[2 * e]) : 0.f;
+                        const float u1 = 2 * e + 1 < nloc ? bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]) : 0.f;
+                        wa[e] = pack_bf16(u0, u1);
+                        wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
+                    }
                 }
                 tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
                 tmem_st16(tmem + kTmUnB + tm_lane + 16 * hf, wb);
