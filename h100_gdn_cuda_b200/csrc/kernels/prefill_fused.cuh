@@ -84,6 +84,31 @@ template <int N>
 __device__ __forceinline__ void reg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// two fp32 values in one 64-bit register pair, and the two-wide fp32 instructions on them
+using f2 = unsigned long long;
+__device__ __forceinline__ f2 pk(float lo, float hi) {
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpk(f2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f2 add2(f2 a, f2 b) {
+    f2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -267,10 +292,14 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 if (nloc >= 32) {  // every token of this half exists (all chunks but a ragged last one)
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const float u0 = bf16_lo(upk[e]) + __uint_as_float(r[2 * e]);
-                        const float u1 = bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]);
+                        const f2 u2 = add2(pk(bf16_lo(upk[e]), bf16_hi(upk[e])),
+                                           pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
+                        const f2 ud = mul2(u2, pk(dec[2 * e], dec[2 * e + 1]));
+                        float u0, u1, d0, d1;
+                        unpk(u2, u0, u1);
+                        unpk(ud, d0, d1);
                         wa[e] = pack_bf16(u0, u1);
-                        wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
+                        wb[e] = pack_bf16(d0, d1);
                     }
                 } else {
 #pragma unroll
@@ -291,6 +320,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (c == 40 && tid == 0) GDN_STAMP_ANY(41);
             // ---- S <- e^{g_L} S + dS
             const float eg_last = gb[128];
+            const f2 eg2 = pk(eg_last, eg_last);
             mbar_wait(bar_ds, par, abort_flag);
             tc_fence_after_sync();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(42);
@@ -300,7 +330,11 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 tmem_ld32(tmem + kTmDS + tm_lane + 64 * hf + 32 * q, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) S[q * 32 + e] = fmaf(S[q * 32 + e], eg_last, __uint_as_float(r[e]));
+                for (int e = 0; e < 16; ++e) {
+                    const f2 s2 = fma2(pk(S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]), eg2,
+                                       pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
+                    unpk(s2, S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]);
+                }
             }
             publish_state();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
