@@ -324,19 +324,31 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             mbar_wait(bar_ds, par, abort_flag);
             tc_fence_after_sync();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(42);
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t r[32];
-                tmem_ld32(tmem + kTmDS + tm_lane + 64 * hf + 32 * q, r);
+            {
+                // both halves of this thread's 64 increments are requested at once; the new bf16
+                // state of a half is on its way to tensor memory while the other half is computed
+                uint32_t r0[32], r1[32];
+                tmem_ld32(tmem + kTmDS + tm_lane + 64 * hf, r0);
+                tmem_ld32(tmem + kTmDS + tm_lane + 64 * hf + 32, r1);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const f2 s2 = fma2(pk(S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]), eg2,
-                                       pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
-                    unpk(s2, S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]);
+                for (int q = 0; q < 2; ++q) {
+                    const uint32_t* r = q ? r1 : r0;
+                    uint32_t w[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const f2 s2 = fma2(pk(S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]), eg2,
+                                           pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
+                        unpk(s2, S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]);
+                        w[e] = pack_bf16(S[q * 32 + 2 * e], S[q * 32 + 2 * e + 1]);
+                    }
+                    tmem_st16(tmem + kTmSbf + tm_lane + 32 * hf + 16 * q, w);
                 }
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sbf);
             }
-            publish_state();
             if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
         }
         if (lane == 0) mbar_arrive(bar_go);  // releases the last chunk's epilogue
