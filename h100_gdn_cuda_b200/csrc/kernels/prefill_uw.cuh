@@ -64,6 +64,20 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return r;
 }
+using f2 = unsigned long long;  // two fp32 values in a 64-bit register pair
+__device__ __forceinline__ f2 pk(float lo, float hi) {
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpk(f2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -249,6 +263,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         const int i = 16 * warp + (lane & 15);
         const int cbase = (lane >> 4) * 32;
         const float bi = sBeta[i], gi = sG[i];
+        const f2 bi2 = pk(bi, bi), ps2 = pk(p.p_scale, p.p_scale);
         uint32_t r[32], rq[32];
         tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
         if (kWithP) tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 32, rq);
@@ -261,12 +276,18 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
                 const float4 gc = *reinterpret_cast<const float4*>(sG + cbase + j + 4 * e4);
                 const float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int col = cbase + j + 4 * e4 + e;
-                    const bool low = col <= i && i < n;
-                    const float dec = low ? ex2(gi - gcv[e]) : 0.f;
-                    a[4 * e4 + e] = (col < i) ? bi * __uint_as_float(r[j + 4 * e4 + e]) * dec : 0.f;
-                    if (kWithP) pq[4 * e4 + e] = p.p_scale * __uint_as_float(rq[j + 4 * e4 + e]) * dec;
+                for (int e = 0; e < 4; e += 2) {
+                    // two columns at a time with the two-wide fp32 multiplies; the diagonal entry of
+                    // A (which the mask col <= i lets through) is zeroed after the loop
+                    const int col = cbase + j + 4 * e4 + e, k = j + 4 * e4 + e;
+                    const float d0 = (col <= i && i < n) ? ex2(gi - gcv[e]) : 0.f;
+                    const float d1 = (col + 1 <= i && i < n) ? ex2(gi - gcv[e + 1]) : 0.f;
+                    const f2 dec2 = pk(d0, d1);
+                    unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), bi2), dec2), a[4 * e4 + e],
+                         a[4 * e4 + e + 1]);
+                    if (kWithP)
+                        unpk(mul2(mul2(pk(__uint_as_float(rq[k]), __uint_as_float(rq[k + 1])), ps2), dec2),
+                             pq[4 * e4 + e], pq[4 * e4 + e + 1]);
                 }
             }
             *reinterpret_cast<float4*>(&sA[i * LD + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
@@ -278,6 +299,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
                                pack_bf16(pq[6], pq[7]));
             }
         }
+        if (i >= cbase && i < cbase + 32) sA[i * LD + i] = 0.f;  // A is strictly lower triangular
     }
     uint32_t bar_load_parity = 0;
     if (kWithP) fence_proxy_async_smem();
