@@ -291,14 +291,21 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 uint32_t wa[16], wb[16];
                 if (nloc >= 32) {  // every token of this half exists (all chunks but a ragged last one)
 #pragma unroll
+                    // the plain copy is on its way to tensor memory while the scaled one is computed
+                    f2 u2[16];
+#pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const f2 u2 = add2(pk(bf16_lo(upk[e]), bf16_hi(upk[e])),
-                                           pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
-                        const f2 ud = mul2(u2, pk(dec[2 * e], dec[2 * e + 1]));
-                        float u0, u1, d0, d1;
-                        unpk(u2, u0, u1);
-                        unpk(ud, d0, d1);
+                        u2[e] = add2(pk(bf16_lo(upk[e]), bf16_hi(upk[e])),
+                                     pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
+                        float u0, u1;
+                        unpk(u2[e], u0, u1);
                         wa[e] = pack_bf16(u0, u1);
+                    }
+                    tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        float d0, d1;
+                        unpk(mul2(u2[e], pk(dec[2 * e], dec[2 * e + 1])), d0, d1);
                         wb[e] = pack_bf16(d0, d1);
                     }
                 } else {
@@ -310,7 +317,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                         wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
                     }
                 }
-                tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
+                if (nloc < 32) tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
                 tmem_st16(tmem + kTmUnB + tm_lane + 16 * hf, wb);
             }
             tmem_wait_st();
