@@ -215,6 +215,20 @@ def run_only(args, gdn, synthetic, dev, peaks):
         t = {k: p[k].to(dev) for k in ("q", "k", "v", "beta", "g", "state")}
         run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"])
         work, unit = B * T, "tokens/s"
+    elif args.only == "long":
+        # one GPU's share of the long-context configuration: B=2, T=131072, `--heads` v-heads
+        B, T, lvh = args.batch or 2, 131072, args.heads or 4
+        lkh = max(1, lvh * kh // vh)
+        gen = torch.Generator(device=dev).manual_seed(7)
+        t = {"q": torch.nn.functional.normalize(torch.randn(B, T, lkh, d, device=dev, generator=gen), dim=-1).bfloat16(),
+             "k": torch.nn.functional.normalize(torch.randn(B, T, lkh, d, device=dev, generator=gen), dim=-1).bfloat16(),
+             "v": torch.randn(B, T, lvh, d, device=dev, generator=gen).bfloat16(),
+             "beta": torch.sigmoid(torch.randn(B, T, lvh, device=dev, generator=gen)).bfloat16(),
+             "g": -torch.nn.functional.softplus(torch.randn(B, T, lvh, device=dev, generator=gen)) * 0.1,
+             "state": (torch.randn(B, lvh, d, d, device=dev, generator=gen) * 0.02).bfloat16()}
+        ws = torch.empty(gdn.api.chunked_forward_workspace_bytes(B, T, lvh), dtype=torch.uint8, device=dev)
+        run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"], _workspace=ws)
+        work, unit = B * T, "tokens/s"
     else:
         B = args.batch or 128
         p = synthetic.decode_inputs(B, 1, kh, vh, d, seed=0)
@@ -245,9 +259,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=2 T=131072 head-sharded leg")
-    ap.add_argument("--only", default=None, choices=["prefill", "decode"],
+    ap.add_argument("--only", default=None, choices=["prefill", "decode", "long"],
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
+    ap.add_argument("--heads", type=int, default=None, help="with --only long: v-heads of this GPU's share (default 4)")
     args = ap.parse_args()
     if args.only is None:
         args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

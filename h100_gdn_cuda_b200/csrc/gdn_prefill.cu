@@ -346,7 +346,9 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.si_sh = p.si_sh;
             cp.vh = s.num_v_heads;
             cp.num_segments = plan.num_segments;
-            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / 16), 128, 0, st>>>(cp);
+            cp.status = d->status;
+            if (int rc = set_smem(gdn_seg_combine_kernel, SegCombineSmem::kBytes)) return rc;
+            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / 16), 128, SegCombineSmem::kBytes, st>>>(cp);
             GDN_CUDA(cudaGetLastError());
             p.mode = 2;
             gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);

@@ -4,8 +4,13 @@
 // produced by the mode-1 launch of gdn_fused_seq_kernel.  The work is tiny (one 128 x 128 x 128
 // product per chain and segment) and strictly sequential in p; it stays in fp32 on CUDA cores.
 // One CTA of 128 threads per (chain, block of 16 state rows); thread = column of the state.
+// M_p (64 KB) comes into shared memory by one bulk copy, the copy of M_{p+1} running while M_p is
+// being used (element-wise global loads of M made this kernel latency-bound: 235 us instead of
+// about 40 at 8 chains x 16 segments).
 #pragma once
 #include <cuda_bf16.h>
+
+#include "sm100_ptx.cuh"
 
 namespace gdn {
 
@@ -15,38 +20,76 @@ struct SegCombineParams {
     const __nv_bfloat16* state_in;  // or NULL
     long long si_ss, si_sh;
     int vh, num_segments;
+    int* status;
+};
+
+struct SegCombineSmem {
+    static constexpr int D = 128, R = 16;
+    static constexpr int kOffM = 0;                      // two buffers of D x D fp32
+    static constexpr int kOffS = 2 * D * D * 4;          // R x D fp32
+    static constexpr int kOffBar = kOffS + R * D * 4;    // 2 mbarriers, abort flag
+    static constexpr int kBytes = kOffBar + 32 + 128;
 };
 
 __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombineParams p) {
-    constexpr int D = 128, R = 16;
-    __shared__ float sS[R][D];
+    using namespace ptx;
+    using L = SegCombineSmem;
+    constexpr int D = L::D, R = L::R;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    float* sM = reinterpret_cast<float*>(smem + L::kOffM);
+    float(*sS)[D] = reinterpret_cast<float(*)[D]>(smem + L::kOffS);
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
+    int* abort_flag = reinterpret_cast<int*>(bar + 2);
+
     const long long chain = blockIdx.x;
     const int r0 = blockIdx.y * R, col = threadIdx.x;
     const int seq = static_cast<int>(chain / p.vh), head = static_cast<int>(chain % p.vh);
+    const int nseg = p.num_segments;
+    auto m_of = [&](int s) { return p.seg_mn + ((chain * nseg + s) * 2 + 1) * (D * D); };
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
+        mbar_fence_init();
+        if (nseg > 1) {
+            mbar_arrive_expect_tx(&bar[0], D * D * 4);
+            bulk_load(sM, m_of(0), D * D * 4, &bar[0]);
+        }
+    }
     float acc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r)
         acc[r] = p.state_in ? __bfloat162float(p.state_in[seq * p.si_ss + head * p.si_sh + static_cast<long long>(r0 + r) * D + col]) : 0.f;
-    for (int s = 0; s < p.num_segments; ++s) {
-        float* dst = p.seg_start + (chain * p.num_segments + s) * (D * D);
+    __syncthreads();
+    for (int s = 0; s < nseg; ++s) {
+        float* dst = p.seg_start + (chain * nseg + s) * (D * D);
 #pragma unroll
         for (int r = 0; r < R; ++r) dst[(r0 + r) * D + col] = acc[r];
-        if (s + 1 == p.num_segments) break;
-        __syncthreads();  // previous iteration's readers of sS are done
+        if (s + 1 == nseg) break;
+        const int b = s & 1;
+        // the other buffer was last read in iteration s - 1, which every thread has left (barrier below)
+        if (threadIdx.x == 0 && s + 2 < nseg) {
+            mbar_arrive_expect_tx(&bar[b ^ 1], D * D * 4);
+            bulk_load(sM + (b ^ 1) * D * D, m_of(s + 1), D * D * 4, &bar[b ^ 1]);
+        }
 #pragma unroll
         for (int r = 0; r < R; ++r) sS[r][col] = acc[r];
-        __syncthreads();
-        const float* N = p.seg_mn + (chain * p.num_segments + s) * 2 * (D * D);
-        const float* M = N + D * D;
+        const float* N = p.seg_mn + (chain * nseg + s) * 2 * (D * D);
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = N[(r0 + r) * D + col];
-#pragma unroll 4
+        __syncthreads();  // sS complete
+        mbar_wait(&bar[b], static_cast<uint32_t>((s >> 1) & 1), abort_flag);
+        const float* M = sM + b * D * D;
+#pragma unroll 8
         for (int k = 0; k < D; ++k) {
             const float m = M[k * D + col];
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r] = fmaf(sS[r][k], m, acc[r]);
         }
+        __syncthreads();  // sS and this M buffer are free again
     }
+    if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 6);
 }
 
 }  // namespace gdn
