@@ -511,12 +511,16 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // goes first and on its own barrier; P, K, Q are not needed before the second MMA group
                 mbar_arrive_expect_tx_w(&bar_full[s], 2 * L::kTile);
                 bulk_load_w(st + L::kOffU, blk, 2 * L::kTile, &bar_full[s]);
-                mbar_arrive_expect_tx_w(&bar_full2[s], L::kStage - 2 * L::kTile);
+                if (emit_o) {
+                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kStage - 2 * L::kTile);
 #pragma unroll
-                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full2[s], a * 64, khead, tok, batch);
+                    for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full2[s], a * 64, khead, tok, batch);
+                } else {
+                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile);  // no output: K is all the second group needs
+                }
 #pragma unroll
                 for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full2[s], a * 64, khead, tok, batch);
-                bulk_load_w(st + L::kOffP, blk + 2 * L::kTile, kChunk * kChunk * 2, &bar_full2[s]);
+                if (emit_o) bulk_load_w(st + L::kOffP, blk + 2 * L::kTile, kChunk * kChunk * 2, &bar_full2[s]);
                 if (c == 40 && lane == 0) GDN_STAMP_ANY(22);
             }
         }
