@@ -81,11 +81,14 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
         __syncthreads();  // sS complete
         mbar_wait(&bar[b], static_cast<uint32_t>((s >> 1) & 1), abort_flag);
         const float* M = sM + b * D * D;
-#pragma unroll 8
-        for (int k = 0; k < D; ++k) {
-            const float m = M[k * D + col];
+#pragma unroll 2
+        for (int k = 0; k < D; k += 4) {
+            const float m0 = M[k * D + col], m1 = M[(k + 1) * D + col], m2 = M[(k + 2) * D + col], m3 = M[(k + 3) * D + col];
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] = fmaf(sS[r][k], m, acc[r]);
+            for (int r = 0; r < R; ++r) {
+                const float4 s4 = *reinterpret_cast<const float4*>(&sS[r][k]);  // one address for all lanes: a broadcast
+                acc[r] = fmaf(s4.w, m3, fmaf(s4.z, m2, fmaf(s4.y, m1, fmaf(s4.x, m0, acc[r]))));
+            }
         }
         __syncthreads();  // sS and this M buffer are free again
     }
