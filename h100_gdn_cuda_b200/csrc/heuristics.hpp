@@ -35,7 +35,7 @@ inline PrefillConfig prefill_config() { return PrefillConfig{4, 512}; }
 
 // Segmented state propagation for few long padded sequences.  The state kernel is a serial chain
 // per (sequence, v-head); with fewer chains than SMs most of the GPU idles.  The chain obeys
-// S' = S M_c + N_c per chunk, so the sequence is cut into P segments: one launch finds every
+// S' = S M_c + N_c per chunk, so the sequence is cut into P (at most 32) segments: one launch finds every
 // segment's composite (M, N) (two CTAs per chain and segment), a small kernel chains them into the
 // segments' start states, and a second launch of the state kernel produces the output of all
 // segments at once.  Three passes instead of one, P segments wide.
@@ -56,7 +56,7 @@ inline SegmentPlan prefill_segments(long long chains, int chunks_per_seq, bool p
     auto waves = [&](long long ctas) { return (ctas + kSms - 1) / kSms; };
     constexpr int kFixed = 3, kMinSegment = 32;
     double best = 0.8 * static_cast<double>(waves(chains) * (chunks_per_seq + kFixed));
-    for (int P = 2; P <= 16 && chunks_per_seq / P >= kMinSegment; ++P) {
+    for (int P = 2; P <= 32 && chunks_per_seq / P >= kMinSegment; ++P) {
         const long long w1 = waves(2 * chains * P), w3 = waves(chains * P);
         if (w3 > 1 || w1 > 2) break;
         const int len = (chunks_per_seq + P - 1) / P;

@@ -77,9 +77,9 @@ def test_workspace_bytes(lib):
     assert api.chunked_forward_workspace_bytes(1, 65, 2) == 2 * 2 * unit + 256        # ragged tail: whole chunks
     # packed mode counts chunks, not tokens
     assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True) == 6 * 4 * unit + 256
-    # B=2, T=131072, 4 v-heads: 8 chains -> 16 segments
+    # B=2, T=131072, 4 v-heads: 8 chains -> 18 segments
     long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4)
-    assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 16 * 3 * 128 * 128 * 4 + 256
+    assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 18 * 3 * 128 * 128 * 4 + 256
     # 128 chains: never segmented
     assert api.chunked_forward_workspace_bytes(4, 131072, 32) == 4 * 2048 * 32 * unit + 256
 
@@ -106,7 +106,7 @@ def test_segment_plan_heuristic():
         exe = os.path.join(d, "h")
         subprocess.check_call(["g++", "-std=c++17", "-I", os.path.join(ROOT, "h100_gdn_cuda_b200", "csrc"), c, "-o", exe])
         rows = [tuple(int(x) for x in l.split()) for l in subprocess.check_output([exe]).decode().splitlines()]
-    assert rows[0] == (16, 128)          # 8 chains: two CTA waves of short segments beat one of long ones
+    assert rows[0] == (18, 114)          # 8 chains: two CTA waves of short segments beat one of long ones
     assert rows[1][0] == 9               # 16 chains: 9 segments fill 144 SMs in the second pass
     assert rows[2][0] >= 2               # 32 chains: still worth it
     assert rows[3] == (1, 2048)          # 64 chains: three passes cost more than they save
