@@ -348,7 +348,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.num_segments = plan.num_segments;
             cp.status = d->status;
             if (int rc = set_smem(gdn_seg_combine_kernel, SegCombineSmem::kBytes)) return rc;
-            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / 16), 128, SegCombineSmem::kBytes, st>>>(cp);
+            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R), 128, SegCombineSmem::kBytes, st>>>(cp);
             GDN_CUDA(cudaGetLastError());
             p.mode = 2;
             gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);

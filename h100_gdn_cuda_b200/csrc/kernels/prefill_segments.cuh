@@ -3,7 +3,7 @@
 // with M_p, N_p the composite transition of segment p (fp32, dv x dk and dk x dk with dv = dk = 128)
 // produced by the mode-1 launch of gdn_fused_seq_kernel.  The work is tiny (one 128 x 128 x 128
 // product per chain and segment) and strictly sequential in p; it stays in fp32 on CUDA cores.
-// One CTA of 128 threads per (chain, block of 16 state rows); thread = column of the state.
+// One CTA of 128 threads per (chain, block of 8 state rows); thread = column of the state.
 // M_p (64 KB) comes into shared memory by one bulk copy, the copy of M_{p+1} running while M_p is
 // being used (element-wise global loads of M made this kernel latency-bound: 235 us instead of
 // about 40 at 8 chains x 16 segments).
@@ -24,7 +24,7 @@ struct SegCombineParams {
 };
 
 struct SegCombineSmem {
-    static constexpr int D = 128, R = 16;
+    static constexpr int D = 128, R = 8;
     static constexpr int kOffM = 0;                      // two buffers of D x D fp32
     static constexpr int kOffS = 2 * D * D * 4;          // R x D fp32
     static constexpr int kOffBar = kOffS + R * D * 4;    // 2 mbarriers, abort flag
@@ -57,10 +57,16 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
             bulk_load(sM, m_of(0), D * D * 4, &bar[0]);
         }
     }
-    float acc[R];
+    float acc[R], nxt[R];  // nxt: the N rows of the coming segment, fetched one iteration ahead
 #pragma unroll
     for (int r = 0; r < R; ++r)
         acc[r] = p.state_in ? __bfloat162float(p.state_in[seq * p.si_ss + head * p.si_sh + static_cast<long long>(r0 + r) * D + col]) : 0.f;
+    auto load_n = [&](int s) {
+        const float* N = p.seg_mn + (chain * nseg + s) * 2 * (D * D);
+#pragma unroll
+        for (int r = 0; r < R; ++r) nxt[r] = (s + 1 < nseg) ? N[(r0 + r) * D + col] : 0.f;
+    };
+    load_n(0);
     __syncthreads();
     for (int s = 0; s < nseg; ++s) {
         float* dst = p.seg_start + (chain * nseg + s) * (D * D);
@@ -75,9 +81,9 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) sS[r][col] = acc[r];
-        const float* N = p.seg_mn + (chain * nseg + s) * 2 * (D * D);
 #pragma unroll
-        for (int r = 0; r < R; ++r) acc[r] = N[(r0 + r) * D + col];
+        for (int r = 0; r < R; ++r) acc[r] = nxt[r];
+        load_n(s + 1);
         __syncthreads();  // sS complete
         mbar_wait(&bar[b], static_cast<uint32_t>((s >> 1) & 1), abort_flag);
         const float* M = sM + b * D * D;
