@@ -258,6 +258,8 @@ size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
         const long long chains = static_cast<long long>(s->batch) * s->num_v_heads;
         const SegmentPlan plan = prefill_segments(chains, (s->seq_len + kChunk - 1) / kChunk, false);
         if (plan.num_segments > 1) bytes += static_cast<size_t>(chains) * plan.num_segments * 3 * kD * kD * sizeof(float) + 256;
+    } else if (s->batch > 1 && s->batch <= kMaxOrderedSeqs) {
+        bytes += (static_cast<size_t>(s->batch) * sizeof(int) + 255) / 256 * 256;  // sequences by length
     }
     return bytes;
 }
@@ -322,7 +324,16 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
         const long long chains = static_cast<long long>(s.batch) * s.num_v_heads;
         const SegmentPlan plan = prefill_segments(chains, (s.seq_len + kChunk - 1) / kChunk, packed);
-        if (plan.num_segments <= 1) {
+        if (packed && s.batch > 1 && s.batch <= kMaxOrderedSeqs && chains > d->sms) {
+            // more chains than SMs and unequal lengths: dispatch the longest sequences first
+            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kUnitBlockBytes;
+            int* order = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256);
+            gdn_seq_order_kernel<<<(s.batch + 127) / 128, 128, 0, st>>>(s.cu_seqlens, s.batch, order);
+            GDN_CUDA(cudaGetLastError());
+            p.seq_order = order;
+            gdn_fused_seq_kernel<<<dim3(s.num_v_heads, s.batch), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            GDN_CUDA(cudaGetLastError());
+        } else if (plan.num_segments <= 1) {
             gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
             GDN_CUDA(cudaGetLastError());
         } else {

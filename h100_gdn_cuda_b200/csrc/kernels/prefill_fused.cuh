@@ -49,6 +49,11 @@ struct FusedParams {
     int mode, seg_chunks, num_segments;
     float* seg_mn;
     const float* seg_start;
+    // Packed mode with more CTAs than SMs: sequences sorted by length, longest first (written by
+    // gdn_seq_order_kernel).  Then blockIdx.x = head and blockIdx.y = rank of the sequence, so the
+    // longest chains are dispatched first and the short ones fill the tail.  NULL: blockIdx.x =
+    // sequence, blockIdx.y = head.
+    const int* seq_order;
 };
 
 struct FusedSmem {
@@ -138,7 +143,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seq = blockIdx.x, head = blockIdx.y;
+    const int seq = p.seq_order ? p.seq_order[blockIdx.y] : static_cast<int>(blockIdx.x);
+    const int head = p.seq_order ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.y);
     const int khead = head / (p.vh / p.kh);
 
     int batch, gchunk0;
@@ -594,6 +600,23 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
     if (tid == 0 && *abort_flag && p.status) atomicExch(p.status, 4);
+}
+
+// order[r] = the sequence with the r-th largest token count (ties: lower index first), for up to
+// kMaxOrderedSeqs sequences.  One thread per sequence counts the sequences that go before its own.
+constexpr int kMaxOrderedSeqs = 2048;
+
+__global__ void __launch_bounds__(128) gdn_seq_order_kernel(const int* __restrict__ cu_seqlens, int num_seqs,
+                                                            int* __restrict__ order) {
+    __shared__ int len[kMaxOrderedSeqs];
+    for (int j = threadIdx.x; j < num_seqs; j += blockDim.x) len[j] = cu_seqlens[j + 1] - cu_seqlens[j];
+    __syncthreads();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_seqs) return;
+    const int mine = len[i];
+    int rank = 0;
+    for (int j = 0; j < num_seqs; ++j) rank += (len[j] > mine) || (len[j] == mine && j < i);
+    order[rank] = i;
 }
 
 }  // namespace gdn

@@ -75,8 +75,9 @@ def test_workspace_bytes(lib):
     unit = 2 * 64 * 128 * 2 + 64 * 64 * 2
     assert api.chunked_forward_workspace_bytes(4, 4096, 32) == 4 * 64 * 32 * unit + 256
     assert api.chunked_forward_workspace_bytes(1, 65, 2) == 2 * 2 * unit + 256        # ragged tail: whole chunks
-    # packed mode counts chunks, not tokens
-    assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True) == 6 * 4 * unit + 256
+    # packed mode counts chunks, not tokens; 256 bytes more hold the sequences ordered by length
+    assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True) == 6 * 4 * unit + 256 + 256
+    assert api.chunked_forward_workspace_bytes(1, 0, 4, total_tokens=200, total_chunks=4, packed=True) == 4 * 4 * unit + 256
     # B=2, T=131072, 4 v-heads: 8 chains -> 18 segments
     long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4)
     assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 18 * 3 * 128 * 128 * 4 + 256

@@ -190,6 +190,29 @@ def test_varlen_equals_padded_per_sequence(gdn):
         off += n
 
 
+def test_varlen_more_chains_than_sms(gdn):
+    # 40 sequences x 4 v-heads = 160 chains: the state kernel takes the sequences longest first
+    # (ties and single-token sequences included); every sequence must still land in its own slot
+    lens = [1 + (37 * i) % 150 for i in range(36)] + [64, 64, 150, 1]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=40, mild_gate=True)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"])
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final states")
+    off = 0
+    for i, n in enumerate(lens):
+        if i % 7 == 0:
+            sl = slice(off, off + n)
+            oi, si = gdn.chunked_forward(pd["q"][None, sl], pd["k"][None, sl], pd["v"][None, sl], pd["beta"][None, sl],
+                                         pd["g"][None, sl], None, pd["state"][i:i + 1])
+            assert torch.equal(oi[0], o[sl]) and torch.equal(si[0], s[i])
+        off += n
+
+
 def test_prefill_state_handoff(gdn):
     # prefill(T1) -> state -> prefill(T2) == prefill(T1+T2); then hand the state to decode
     p = synthetic.prefill_inputs(1, 384, 2, 4, 128, seed=12, mild_gate=True)
