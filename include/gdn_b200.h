@@ -212,7 +212,9 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * contents need not be initialised and are garbage afterwards.  It holds one 40 KiB block per
  * 64-token chunk and v-head (U, W and the intra-chunk attention block) and, when few long padded
  * sequences are propagated in segments, three fp32 states (192 KiB) per (sequence, v-head) and
- * segment. */
+ * segment; packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the sequences ordered
+ * by length: the state kernel takes the longest first when there are more (sequence, v-head)
+ * pairs than SMs). */
 typedef struct {
     GdnShape shape;
     GdnTokenTensor q, k, v, out;
@@ -241,7 +243,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  * ignored; inputs and outputs are passed as usual.
  *
  *   - Limit: gdn_chunked_forward_workspace_bytes(&args->shape) must not exceed
- *     GDN_STATIC_SCRATCH_BYTES (80 MiB + 256 bytes).  The scratch holds U and W (512 bytes per
+ *     GDN_STATIC_SCRATCH_BYTES (80 MiB + 8 KiB + 256 bytes).  The scratch holds U and W (512 bytes per
  *     token and v-head) and the intra-chunk attention blocks (8 KiB per 64-token chunk and
  *     v-head), so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
  *     tokens of 32 v-heads (less where long sequences of few heads add their segment states).
@@ -253,7 +255,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  *     left there.  Nothing in it has to start at zero (every element that is read has been
  *     written earlier in the same call), but two calls whose kernels overlap on the GPU -
  *     different streams, or different host threads - race on it: serialise them. */
-#define GDN_STATIC_SCRATCH_BYTES ((80u << 20) + 256u)
+#define GDN_STATIC_SCRATCH_BYTES ((80u << 20) + 8192u + 256u)
 int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* args, gdn_stream_t stream);
 
 #ifdef __cplusplus
