@@ -18,6 +18,7 @@ The printed JSON line carries:
              events, against the HBM roof that bounds both of them
   decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, fused gating) and its
              HBM roofline fraction
+  packed     packed (varlen) prefill of 16 sequences with log-normal lengths, 32768 tokens per GPU
   long_context  the B=2, T=131072 layer with the value heads sharded over the N ranks (strong scaling)
   cpu_baseline  the fp32 CPU token recurrence (the oracle) on a bounded sample, rank 0, N=1
 
@@ -259,6 +260,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=2 T=131072 head-sharded leg")
+    ap.add_argument("--no-packed", action="store_true", help="skip the packed (varlen) prefill leg")
     ap.add_argument("--only", default=None, choices=["prefill", "decode", "long"],
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
@@ -433,6 +435,41 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     ms_dec_kernel = e0.elapsed_time(e1) / dsteps
+    # ---------------- packed prefill: 16 sequences of log-normal lengths, 32768 tokens per rank
+    pk = None
+    if not args.no_packed:
+        lens = synthetic.lognormal_lengths(16, 32768, 64, 8192, seed=rank)
+        pp = synthetic.varlen_inputs(lens, kh, vh, d, seed=200 + rank)
+        pd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in pp.items()}
+        pws = torch.empty(gdn.api.chunked_forward_workspace_bytes(len(lens), 0, vh, total_tokens=sum(lens),
+                                                                  total_chunks=pp["total_chunks"], packed=True),
+                          dtype=torch.uint8, device=dev)
+        pev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for e in pev:
+            e.record()
+
+        def step_packed(events=None):
+            return gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"], pd["cu_seqlens"],
+                                       pd["chunk_indices"], pd["cu_chunks"], pp["total_chunks"], _workspace=pws,
+                                       _stage_events=events)
+        for _ in range(3):
+            step_packed()
+        barrier()
+        psteps = 10
+        e0.record()
+        for _ in range(psteps):
+            step_packed()
+        e1.record()
+        barrier()
+        ms_pk = max_over_ranks(e0.elapsed_time(e1) / psteps)
+        step_packed(pev)
+        torch.cuda.synchronize()
+        pk = {"metric": "prefill_tokens_per_s", "value": world * sum(lens) / (ms_pk * 1e-3), "unit": "tokens/s",
+              "config": "packed: 16 sequences of log-normal lengths (%d ... %d tokens), %d tokens per GPU, kh=16 vh=32 d=128"
+                        % (min(lens), max(lens), sum(lens)),
+              "ms_per_step": ms_pk, "gdn_uw_kernel_ms": pev[0].elapsed_time(pev[1]),
+              "gdn_fused_seq_kernel_ms": pev[1].elapsed_time(pev[2])}
+        del pd, pws
     # ---------------- long context: B=2, T=131072, the 32 value heads sharded over the ranks
     # (each rank takes vh / world v-heads with their q/k heads; no collective).  Strong scaling:
     # every rank works on the same two sequences, the layer's time is the slowest rank's.
@@ -461,7 +498,7 @@ def main():
               "config": "B=2 T=131072 kh=16 vh=32 d=128, value heads sharded over %d GPU(s): %d v-heads per GPU" % (world, lvh),
               "ms_per_step": ms_lc}
         del lq, lk, lv, lbeta, lg, ls0, lws
-    # the sampler ran across every timed region above (prefill resident, end to end, decode, long context)
+    # the sampler ran across every timed region above (prefill resident, end to end, decode, packed, long context)
     clocks = sampler.stop() if rank == 0 else None
     dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
 
@@ -519,6 +556,7 @@ def main():
                                 "frac_of_nominal_8TBs": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / 8000.0,
                                 "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes,
                                 "traffic": dB * NCU_DECODE_TRAFFIC_PER_TOKEN}},
+        "packed": pk,
         "long_context": lc,
         "clocks": clocks,
     }
