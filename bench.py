@@ -230,6 +230,14 @@ def run_only(args, gdn, synthetic, dev, peaks):
         ws = torch.empty(gdn.api.chunked_forward_workspace_bytes(B, T, lvh), dtype=torch.uint8, device=dev)
         run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"], _workspace=ws)
         work, unit = B * T, "tokens/s"
+    elif args.only == "packed":
+        # 16 sequences of log-normal lengths in one packed batch of 32768 tokens
+        lens = synthetic.lognormal_lengths(16, 32768, 64, 8192, seed=0)
+        p = synthetic.varlen_inputs(lens, kh, vh, d, seed=200)
+        t = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
+        run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"], t["cu_seqlens"],
+                                            t["chunk_indices"], t["cu_chunks"], p["total_chunks"])
+        B, work, unit = len(lens), sum(lens), "tokens/s"
     else:
         B = args.batch or 128
         p = synthetic.decode_inputs(B, 1, kh, vh, d, seed=0)
@@ -261,7 +269,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=2 T=131072 head-sharded leg")
     ap.add_argument("--no-packed", action="store_true", help="skip the packed (varlen) prefill leg")
-    ap.add_argument("--only", default=None, choices=["prefill", "decode", "long"],
+    ap.add_argument("--only", default=None, choices=["prefill", "decode", "long", "packed"],
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
     ap.add_argument("--heads", type=int, default=None, help="with --only long: v-heads of this GPU's share (default 4)")
