@@ -190,10 +190,26 @@ def test_varlen_equals_padded_per_sequence(gdn):
         off += n
 
 
+def test_chunked_forward_varlen_with_empty_sequences(gdn):
+    # sequences without tokens own no chunk; their final state is their initial state
+    lens = [70, 0, 5, 0]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=3, mild_gate=True)
+    assert p["total_chunks"] == 3
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"])
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final states")
+    assert torch.equal(s[1], pd["state"][1]) and torch.equal(s[3], pd["state"][3])
+
+
 def test_varlen_more_chains_than_sms(gdn):
     # 40 sequences x 4 v-heads = 160 chains: the state kernel takes the sequences longest first
-    # (ties and single-token sequences included); every sequence must still land in its own slot
-    lens = [1 + (37 * i) % 150 for i in range(36)] + [64, 64, 150, 1]
+    # (ties, single-token and empty sequences included); every sequence must still land in its own slot
+    lens = [1 + (37 * i) % 150 for i in range(35)] + [0, 64, 64, 150, 1]
     p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=40, mild_gate=True)
     o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
                                    cu_seqlens=p["cu_seqlens"])
@@ -205,7 +221,7 @@ def test_varlen_more_chains_than_sms(gdn):
     close(s, s_ref, "final states")
     off = 0
     for i, n in enumerate(lens):
-        if i % 7 == 0:
+        if i % 7 == 0 and n > 0:
             sl = slice(off, off + n)
             oi, si = gdn.chunked_forward(pd["q"][None, sl], pd["k"][None, sl], pd["v"][None, sl], pd["beta"][None, sl],
                                          pd["g"][None, sl], None, pd["state"][i:i + 1])

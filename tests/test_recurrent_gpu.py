@@ -136,6 +136,20 @@ def test_recurrent_varlen_and_inplace(gdn):
     assert torch.equal(s3, s) and torch.equal(o3, o)
 
 
+def test_recurrent_varlen_with_empty_sequences(gdn):
+    # a sequence without tokens produces no output rows and hands its state through unchanged
+    lens = [3, 0, 1, 0]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=12)
+    pd = dev(p)
+    o, s = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], pd["beta"], pd["g"],
+                                 cu_seqlens=pd["cu_seqlens"])
+    o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), p["beta"].float(), p["g"],
+                                   p["state"].float(), cu_seqlens=p["cu_seqlens"])
+    close(o, o_ref, "o")
+    close(s, s_ref, "state")
+    assert torch.equal(s[1], pd["state"][1]) and torch.equal(s[3], pd["state"][3])
+
+
 def test_recurrent_head_sliced_views(gdn):
     # value-head sharding passes non-contiguous head slices: results must equal the full call
     p = synthetic.decode_inputs(4, 2, 4, 8, 128, seed=13)
