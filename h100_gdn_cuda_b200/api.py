@@ -254,6 +254,9 @@ def _check_head_dim(d: int):
     _require(0 < d <= _PREFILL_D, "chunked kernels support head dims up to %d (got %d)" % (_PREFILL_D, d))
 
 
+_PREFILL_D_MAX = 256  # chunked_forward takes head dims up to here (above 128: the token-recurrent kernel)
+
+
 def chunked_forward_workspace_bytes(batch: int, seq_len: int, num_v_heads: int, total_tokens: int = 0,
                                     total_chunks: int = 0, packed: bool = False) -> int:
     """Bytes of scratch `chunked_forward` needs for a problem of this size (head dim 128)."""
@@ -278,10 +281,12 @@ def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None
     varlen, batch, seq_len, total = _prefill_dims(query, value, cu_seqlens)
     d = query.shape[-1]
     _require(key.shape[-1] == d and value.shape[-1] == d, "chunked kernels need dk == dv")
-    _check_head_dim(d)
+    _require(0 < d <= _PREFILL_D_MAX, "chunked_forward supports head dims up to %d (got %d)" % (_PREFILL_D_MAX, d))
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    D = _PREFILL_D
+    # up to 128: the tensor-core kernels (zero-padded to 128); 129..256: the library runs the
+    # token recurrence on 192 or 256 columns instead (no scratch)
+    D = _PREFILL_D if d <= _PREFILL_D else _aligned_dim(d)
     q, k, v = _pad_last(query, D), _pad_last(key, D), _pad_last(value, D)
     s_in = _pad_state(initial_state, D)
     if s_in is not None:

@@ -247,8 +247,43 @@ int gdn_compute_o(const GdnComputeOArgs* a, gdn_stream_t stream) {
     return GDN_OK;
 }
 
+// Head dims above the 128 the tensor-core kernels are built for (192 and 256, which the
+// reference's chunked kernels accept: sm90_bf16_gdn_compute_u_w.cuh:169) take the token-recurrent
+// kernel: the same layer semantics with the state kept in fp32 from the first token to the last,
+// no scratch, one launch.  Slower per token than the chunked kernels, but exact and on the GPU.
+static bool wide_heads(const GdnShape& s) { return s.head_dim_k > kD || s.head_dim_v > kD; }
+
+static int chunked_forward_wide(const GdnChunkedArgs* a, gdn_stream_t stream) {
+    const GdnShape& s = a->shape;
+    GDN_REQUIRE(s.head_dim_k == s.head_dim_v && s.head_dim_k % 64 == 0 && s.head_dim_k <= 256,
+                "gdn_chunked_forward: head dims above 128 must be dk = dv = 192 or 256 (got %d, %d); pad with zeros",
+                s.head_dim_k, s.head_dim_v);
+    GDN_REQUIRE(a->final_state.ptr != nullptr, "gdn_chunked_forward: head dims above 128 need a final_state buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* const* ev = a->stage_events;
+    if (ev) {
+        GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[0]), st));
+        GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
+    }
+    GdnRecurrentArgs r{};
+    r.shape = s;
+    r.q = a->q;
+    r.k = a->k;
+    r.v = a->v;
+    r.out = a->out;
+    r.beta = a->beta;
+    r.gate = a->gate;
+    r.state_in = a->initial_state;
+    r.state_out = a->final_state;
+    r.scale = a->scale;
+    if (int rc = gdn_recurrent_forward(&r, stream)) return rc;
+    if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
+    return GDN_OK;
+}
+
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
+    if (wide_heads(*s)) return 0;
     const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
     // one block of U, W (64 x 128 bf16 each) and P (64 x 64 bf16) per (chunk, v-head); for a
@@ -268,6 +303,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     GDN_REQUIRE(a != nullptr, "gdn_chunked_forward: args is NULL");
     const GdnShape& s = a->shape;
     if (int rc = check_shape(s, true)) return rc;
+    if (wide_heads(s)) return chunked_forward_wide(a, stream);
     if (int rc = require_d128(s, "gdn_chunked_forward")) return rc;
     if (int rc = check_token_tensor(a->q, "q", kD)) return rc;
     if (int rc = check_token_tensor(a->k, "k", kD)) return rc;

@@ -108,13 +108,16 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     const bool packed = cu_seqlens.has_value();
     const int64_t d = query.size(-1);
     require(key.size(-1) == d && value.size(-1) == d, "chunked kernels need dk == dv");
-    require(d > 0 && d <= kPrefillDim, "chunked kernels support head dims up to 128");
-    at::Tensor q = pad_last(query, kPrefillDim), k = pad_last(key, kPrefillDim), v = pad_last(value, kPrefillDim);
+    require(d > 0 && d <= 256, "chunked_forward supports head dims up to 256");
+    // up to 128: the tensor-core kernels on head dim 128 (zero-padded); 129..256: the library runs
+    // the token recurrence on 192 or 256 columns instead
+    const int64_t D = d <= kPrefillDim ? kPrefillDim : (d + 63) / 64 * 64;
+    at::Tensor q = pad_last(query, D), k = pad_last(key, D), v = pad_last(value, D);
     std::optional<at::Tensor> s_in;
     if (initial_state.has_value()) {
         cuda_bf16(*initial_state, "initial_state");
-        at::Tensor t = pad_state(*initial_state, kPrefillDim, kPrefillDim);
-        if (!(t.stride(-1) == 1 && t.stride(-2) == kPrefillDim)) t = t.contiguous();
+        at::Tensor t = pad_state(*initial_state, D, D);
+        if (!(t.stride(-1) == 1 && t.stride(-2) == D)) t = t.contiguous();
         s_in = t;
     }
     int tc = 0;
@@ -126,7 +129,7 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     GdnChunkedArgs a{};
     a.shape = make_shape(q, v, cu_seqlens, chunk_indices, cu_chunks, tc);
     at::Tensor out = at::empty_like(v);
-    at::Tensor fin = at::empty({a.shape.batch, v.size(-2), kPrefillDim, kPrefillDim}, v.options());
+    at::Tensor fin = at::empty({a.shape.batch, v.size(-2), D, D}, v.options());
     const int64_t tokens = packed ? q.size(0) : q.size(1);
     a.q = tok(q, packed);
     a.k = tok(k, packed);
@@ -143,7 +146,7 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     a.workspace_bytes = ws_bytes;
     a.stage_events = nullptr;
     check(gdn_chunked_forward(&a, stream), "chunked_forward");
-    if (d != kPrefillDim) {
+    if (d != D) {
         out = out.narrow(-1, 0, d);
         fin = fin.narrow(-1, 0, d).narrow(-2, 0, d);
     }

@@ -214,7 +214,10 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * sequences are propagated in segments, three fp32 states (192 KiB) per (sequence, v-head) and
  * segment; packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the sequences ordered
  * by length: the state kernel takes the longest first when there are more (sequence, v-head)
- * pairs than SMs). */
+ * pairs than SMs).
+ * Head dims: dk = dv = 128 for the tensor-core kernels (callers zero-pad smaller head dims);
+ * dk = dv = 192 or 256 are accepted as well and run on the kernel of gdn_recurrent_forward
+ * (no workspace: gdn_chunked_forward_workspace_bytes returns 0; final_state.ptr must be given). */
 typedef struct {
     GdnShape shape;
     GdnTokenTensor q, k, v, out;

@@ -265,9 +265,35 @@ def test_chunked_errors(gdn):
     p = dev(synthetic.prefill_inputs(1, 64, 1, 1, 128, seed=1))
     with pytest.raises(RuntimeError):
         gdn.chunked_forward(p["q"].float(), p["k"], p["v"], p["beta"], p["g"])
-    big = torch.zeros(1, 64, 1, 256, dtype=torch.bfloat16, device="cuda")
+    big = torch.zeros(1, 64, 1, 320, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         gdn.chunked_forward(big, big, big, p["beta"], p["g"])
+
+
+@pytest.mark.parametrize("B,T,kh,vh,d", [(2, 200, 2, 4, 192), (1, 130, 1, 2, 256), (2, 77, 2, 2, 200)])
+def test_chunked_forward_wide_heads(gdn, B, T, kh, vh, d):
+    # head dims in (128, 256] (the reference's chunked kernels go up to 256): same call, same semantics
+    p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=T + d, mild_gate=True)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float())
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"])
+    check_status(gdn)
+    assert o.shape == p["v"].shape and s.shape == p["state"].shape
+    close(o, o_ref, "O")
+    close(s, s_ref, "final state")
+
+
+def test_chunked_forward_wide_heads_varlen(gdn):
+    lens = [65, 1, 130, 0, 64]
+    p = synthetic.varlen_inputs(lens, 2, 4, 256, seed=9, mild_gate=True)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"])
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final states")
 
 
 @pytest.mark.parametrize("varlen", [False, True])

@@ -43,6 +43,12 @@ def test_chunked_forward_same_bits(mods):
     o1, s1 = py.chunked_forward(*a)
     o2, s2 = ext.chunked_forward(*a)
     assert o2.shape == v["v"].shape and torch.equal(o1, o2) and torch.equal(s1, s2)
+    # head dim above 128: both layers hand the call to the token-recurrent kernel
+    w = dev(synthetic.prefill_inputs(1, 100, 1, 2, 200, seed=6, mild_gate=True))
+    o1, s1 = py.chunked_forward(w["q"], w["k"], w["v"], w["beta"], w["g"], None, w["state"])
+    o2, s2 = ext.chunked_forward(w["q"], w["k"], w["v"], w["beta"], w["g"], None, w["state"])
+    assert o2.shape == w["v"].shape and s2.shape == w["state"].shape
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
 
 
 def test_recurrent_and_helpers_same_bits(mods):
@@ -93,6 +99,6 @@ def test_errors_raise(mods):
     p = dev(synthetic.prefill_inputs(1, 64, 1, 1, 128, seed=1))
     with pytest.raises(RuntimeError):
         ext.chunked_forward(p["q"].float(), p["k"], p["v"], p["beta"], p["g"])
-    big = torch.zeros(1, 64, 1, 256, dtype=torch.bfloat16, device="cuda")
+    big = torch.zeros(1, 64, 1, 320, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         ext.chunked_forward(big, big, big, p["beta"], p["g"])
