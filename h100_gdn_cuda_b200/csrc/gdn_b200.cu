@@ -46,21 +46,28 @@ const std::string& cuda_home() { return g_cuda_home; }
 using namespace gdn;
 
 // ------------------------------------------------------------------ recurrent
-template <int DK>
-static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st) {
-    constexpr int smem = recurrent_smem_bytes<DK>();
+template <int DK, bool kRing>
+static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st) {
+    constexpr int smem = recurrent_smem_bytes<DK, kRing>();
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK, kRing>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set[dev] = true;
     }
-    const int per_sm = recurrent_ctas_per_sm<DK>();
+    const int per_sm = recurrent_ctas_per_sm<DK, kRing>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
-    gdn_recurrent_kernel<DK><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
+    gdn_recurrent_kernel<DK, kRing><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
+}
+
+// `ring`: long runs of tokens (more than kRecTokRingMin per sequence on average) take the instance
+// with the multi-token ring; decode and speculative verify keep the lean one.
+template <int DK>
+static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st, bool ring) {
+    return ring ? launch_recurrent_t<DK, true>(p, sms, st) : launch_recurrent_t<DK, false>(p, sms, st);
 }
 
 // Head dimensions without a prebuilt kernel (or every call when GDN_JIT_RECURRENT=1) go through
@@ -246,15 +253,20 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.scale = a->scale;
     p.is_qk_norm = a->is_qk_norm; p.store_step = a->store_step_state;
     p.num_tiles = static_cast<long long>(s.batch) * s.num_v_heads * (s.head_dim_v / kRecTileRows);
+    // more than one token per sequence: tiles become work units of their own (the per-unit sharing
+    // of the q/k normalisation only pays for single-token decode)
+    p.split_tiles = s.cu_seqlens ? (s.total_tokens > s.batch) : (s.seq_len > 1);
     GDN_REQUIRE(p.num_tiles < (1ll << 31), "gdn_recurrent_forward: too many state tiles");
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);
+    const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(kRecTokRingMin) * s.batch)
+                                   : (s.seq_len > kRecTokRingMin);
     switch (s.head_dim_k) {
-        case 64: return launch_recurrent<64>(p, d->sms, st);
-        case 128: return launch_recurrent<128>(p, d->sms, st);
-        case 192: return launch_recurrent<192>(p, d->sms, st);
-        case 256: return launch_recurrent<256>(p, d->sms, st);
+        case 64: return launch_recurrent<64>(p, d->sms, st, ring);
+        case 128: return launch_recurrent<128>(p, d->sms, st, ring);
+        case 192: return launch_recurrent<192>(p, d->sms, st, ring);
+        case 256: return launch_recurrent<256>(p, d->sms, st, ring);
     }
     return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);  // 320 .. 512: compiled on first use
 }

@@ -21,7 +21,8 @@ inline RecurrentConfig recurrent_config(int dk, long long num_tiles, int sms) {
     c.stages = 4;
     c.ctas_per_sm = dk <= 128 ? 4 : 2;
     const int stage = (32 * dk * 2 + 4 * dk + 64 + 127) / 128 * 128;
-    c.smem_bytes = c.stages * stage + 128;
+    const int tok_slot = 8 * (4 * dk + 64);  // k, q, v slice of 8 tokens (the multi-token ring, two slots)
+    c.smem_bytes = c.stages * stage + 128 + 2 * tok_slot;
     c.grid = std::min<long long>(num_tiles, static_cast<long long>(sms) * c.ctas_per_sm);
     return c;
 }

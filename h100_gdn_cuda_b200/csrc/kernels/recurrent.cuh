@@ -17,6 +17,11 @@
 // The eight row sums are reduced over 16 lanes with a transposing butterfly (8 shuffles
 // instead of 32).  For single-token decode q/k normalisation and k.q are computed once per
 // unit, not per tile.  New states leave through coalesced 8-byte stores from registers.
+// Runs of more than one token (short prefill, speculative verify, head dims the chunked kernels do
+// not cover) make every tile a work unit of its own, so that a few long sequences still spread
+// over all CTAs; sequences longer than kRecTokRingMin tokens get k, q and v of 8 tokens at a time
+// through a second, two-slot ring of bulk copies (one token fetched ahead of the one in work
+// left the whole load latency, about a microsecond, exposed on every token).
 #pragma once
 #include "sm100_ptx.cuh"
 
@@ -44,6 +49,7 @@ struct RecurrentParams {
     int batch, seq_len, kh, vh, dv;
     float scale;
     int is_qk_norm, store_step;
+    int split_tiles;  // 1: every 32-row tile is a work unit (multi-token runs); 0: a unit = all tiles of a (sequence, v-head)
     long long num_tiles;
     int* status;
 };
@@ -51,6 +57,8 @@ struct RecurrentParams {
 constexpr int kRecTileRows = 32;
 constexpr int kRecStages = 4;
 constexpr int kRecThreads = 128;
+constexpr int kRecTokBlock = 8;     // tokens per slot of the multi-token ring
+constexpr int kRecTokRingMin = 16;  // sequences longer than this use it
 
 // One ring stage: the 32 x DK state tile, then k and q of the unit's first token
 // (DK bf16 each) and the 32 entries of v that belong to the tile's rows.
@@ -63,9 +71,18 @@ struct RecStage {
     static constexpr int kBytes = (kOffV + kRecTileRows * 2 + 127) / 128 * 128;
 };
 
+// One slot of the multi-token ring: k, q (DK bf16 each) and the tile's 32 entries of v for 8 tokens.
 template <int DK>
+struct RecTokSlot {
+    static constexpr int kOffK = 0;
+    static constexpr int kOffQ = kRecTokBlock * DK * 2;
+    static constexpr int kOffV = 2 * kRecTokBlock * DK * 2;
+    static constexpr int kBytes = kOffV + kRecTokBlock * kRecTileRows * 2;
+};
+
+template <int DK, bool kRing = true>
 constexpr int recurrent_smem_bytes() {
-    return kRecStages * RecStage<DK>::kBytes + 128;
+    return kRecStages * RecStage<DK>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
 }
 
 namespace rec {
@@ -100,14 +117,19 @@ __device__ __forceinline__ float hsum(f2 v) {
 
 // Body of the kernel as a device function: the ahead-of-time entry points below and the
 // entry point the run-time compiler generates (csrc/gdn_jit.cu) both instantiate it.
-template <int DK>
+// kRing: with the multi-token ring (long runs of tokens); without it the kernel is the lean decode
+// kernel (its registers are at the limit of four CTAs per SM at DK = 128).
+template <int DK, bool kRing = true>
 __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     using namespace ptx;
     using namespace rec;
     using Stage = RecStage<DK>;
     constexpr int NQ = DK / 32;  // packed pairs per row per lane (lane owns 4 columns of every 64)
     extern __shared__ __align__(128) uint8_t smem[];
+    using TokSlot = RecTokSlot<DK>;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kRecStages * Stage::kBytes);
+    uint64_t* tokfull = full + kRecStages;  // [2]
+    uint8_t* tokbase = smem + kRecStages * Stage::kBytes + 128;
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x;
@@ -116,24 +138,30 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     const int rblocks = p.dv / kRecTileRows;
     const bool has_in = p.state_in != nullptr;
     const int rep = p.vh / p.kh;
-    const int num_units = static_cast<int>(p.num_tiles / rblocks);
+    const int tpu = (kRing && p.split_tiles) ? 1 : rblocks;  // tiles per work unit
+    const int upg = rblocks / tpu;                // work units per (sequence, v-head)
+    const int num_units = static_cast<int>(p.num_tiles / tpu);
     const int stride = static_cast<int>(gridDim.x);
 
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kRecStages; ++s) mbar_init(&full[s], 1);
+        mbar_init(&tokfull[0], 1);
+        mbar_init(&tokfull[1], 1);
         mbar_fence_init();
     }
     __syncthreads();
 
     struct Unit {
-        int seq, head, khead, ntok;
+        int seq, head, khead, ntok, rb0;
         long long tok0, bidx;
     };
     auto decode = [&](int unit) {
         Unit t;
-        t.head = unit % p.vh;
-        t.seq = unit / p.vh;
+        const int sh = unit / upg;
+        t.rb0 = (unit - sh * upg) * tpu;
+        t.head = sh % p.vh;
+        t.seq = sh / p.vh;
         t.khead = t.head / rep;
         if (p.cu_seqlens) {
             t.tok0 = p.cu_seqlens[t.seq];
@@ -184,9 +212,9 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     if (tid == 0 && prod_unit < num_units) prod_u = decode(prod_unit);
     auto produce_one = [&]() {
         if (prod_unit >= num_units) return;
-        issue(prod_u, prod_rb, prod_it % kRecStages);
+        issue(prod_u, prod_u.rb0 + prod_rb, prod_it % kRecStages);
         ++prod_it;
-        if (++prod_rb == rblocks) {
+        if (++prod_rb == tpu) {
             prod_rb = 0;
             prod_unit += stride;
             if (prod_unit < num_units) prod_u = decode(prod_unit);
@@ -203,6 +231,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     }
 
     int it = 0;
+    int tb_it = 0;  // blocks that have gone through the multi-token ring (slot and parity bookkeeping)
     for (int unit = blockIdx.x; unit < num_units; unit += stride) {
         const Unit T = decode(unit);
         float beta_next = 0.f, g_next = 0.f;
@@ -214,7 +243,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         f2 k2[NQ], q2[NQ];
         float kq = 0.f;
 
-        for (int rb = 0; rb < rblocks; ++rb, ++it) {
+        for (int r = 0; r < tpu; ++r, ++it) {
+            const int rb = T.rb0 + r;
             const int stage = it % kRecStages;
             const uint32_t parity = static_cast<uint32_t>((it / kRecStages) & 1);
             if (tid == 0) produce_one();  // refills the stage consumed in the previous iteration
@@ -241,7 +271,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 #pragma unroll
                     for (int c = 0; c < NQ; ++c) S[j][c] = 0ull;
             }
-            const bool fresh_qk = (rb == 0) || (T.ntok > 1);
+            const bool fresh_qk = (r == 0) || (T.ntok > 1);
             uint2 kw[NQ / 2], qw[NQ / 2];
             if (T.ntok > 0) {
                 if (fresh_qk) {
@@ -258,7 +288,6 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             __syncthreads();  // every thread has read this stage: it may be refilled
 
             // ---- token loop (inputs of token t+1 are fetched from global while token t is computed)
-            float beta_t = beta_first, g_t = g_first;
             auto load_token = [&](int t, uint2* kk, uint2* qq, float* vv, float& bt, float& gt) {
                 const long long tok = T.tok0 + t;
                 const __nv_bfloat16* kp = p.k + T.bidx * p.k_sb + tok * p.k_st + T.khead * p.k_sh;
@@ -274,19 +303,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 load_scalars(T, t, bt, gt);
             };
 
-            for (int t = 0; t < T.ntok; ++t) {
-                uint2 kn[NQ / 2], qn[NQ / 2];
-                float vn[4], beta_n = 0.f, g_n = 0.f;
-                if (t + 1 < T.ntok) load_token(t + 1, kn, qn, vn, beta_n, g_n);
-
-                if (t > 0 || fresh_qk) {
+            auto prep_kq = [&](const uint2* kw_, const uint2* qw_) {
                     // unpack, optional L2 normalisation, k.q
 #pragma unroll
                     for (int pc = 0; pc < NQ / 2; ++pc) {
-                        k2[2 * pc] = bf2_to_f2(kw[pc].x);
-                        k2[2 * pc + 1] = bf2_to_f2(kw[pc].y);
-                        q2[2 * pc] = bf2_to_f2(qw[pc].x);
-                        q2[2 * pc + 1] = bf2_to_f2(qw[pc].y);
+                        k2[2 * pc] = bf2_to_f2(kw_[pc].x);
+                        k2[2 * pc + 1] = bf2_to_f2(kw_[pc].y);
+                        q2[2 * pc] = bf2_to_f2(qw_[pc].x);
+                        q2[2 * pc + 1] = bf2_to_f2(qw_[pc].y);
                     }
                     f2 akk = 0ull, aqq = 0ull, akq = 0ull;
 #pragma unroll
@@ -313,7 +337,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         }
                         kq = skq * inv_k * inv_q;
                     }
-                }
+                            };
+            auto token_step = [&](int t, const float* vr_, float beta_t, float g_t) {
                 // ---- S.k and S.q for the thread's 4 rows
                 f2 ak[4], aq[4];
 #pragma unroll
@@ -371,7 +396,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float dkj = __shfl_sync(0xffffffffu, v1, base + 2 * j);
-                    const float r = vr[j] - eg * dkj;
+                    const float r = vr_[j] - eg * dkj;
                     const float br = beta_t * r;
                     if (l16 == 8 + 2 * j) o_mine = p.scale * fmaf(eg, v1, br * kq);
                     const f2 br2 = pk(br, br);
@@ -402,6 +427,80 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         }
                     }
                 }
+            };
+            if (kRing && T.ntok > kRecTokRingMin) {
+                // k, q, v of 8 tokens per slot, two slots: block b + 2 is requested when block b is done
+                constexpr int TB = kRecTokBlock;
+                const int nblk = (T.ntok + TB - 1) / TB;
+                auto issue_block = [&](int blk) {  // one thread
+                    const int slot = (tb_it + blk) & 1;
+                    uint8_t* dst = tokbase + slot * TokSlot::kBytes;
+                    const int nt = min(TB, T.ntok - blk * TB);
+                    mbar_arrive_expect_tx(&tokfull[slot], static_cast<uint32_t>(nt) * (4 * DK + kRecTileRows * 2));
+                    for (int i = 0; i < nt; ++i) {
+                        const long long tok = T.tok0 + blk * TB + i;
+                        bulk_load(dst + TokSlot::kOffK + i * DK * 2, p.k + T.bidx * p.k_sb + tok * p.k_st + T.khead * p.k_sh,
+                                  DK * 2, &tokfull[slot]);
+                        bulk_load(dst + TokSlot::kOffQ + i * DK * 2, p.q + T.bidx * p.q_sb + tok * p.q_st + T.khead * p.q_sh,
+                                  DK * 2, &tokfull[slot]);
+                        bulk_load(dst + TokSlot::kOffV + i * kRecTileRows * 2,
+                                  p.v + T.bidx * p.v_sb + tok * p.v_st + T.head * p.v_sh + rb * kRecTileRows,
+                                  kRecTileRows * 2, &tokfull[slot]);
+                    }
+                };
+                if (tid == 0) {
+                    issue_block(0);
+                    if (nblk > 1) issue_block(1);
+                }
+                // beta and gate: lane l holds those of token 32 * group + l, the next group one ahead
+                float bsc = 0.f, gsc = 0.f, bsn = 0.f, gsn = 0.f;
+                if (lane < T.ntok) load_scalars(T, lane, bsc, gsc);
+                for (int blk = 0; blk < nblk; ++blk) {
+                    const int slot = (tb_it + blk) & 1;
+                    const uint32_t par = static_cast<uint32_t>(((tb_it + blk) >> 1) & 1);
+                    if ((blk & 3) == 0) {
+                        if (blk > 0) {
+                            bsc = bsn;
+                            gsc = gsn;
+                        }
+                        const int tn = (blk + 4) * TB + lane;
+                        bsn = 0.f;
+                        gsn = 0.f;
+                        if (tn < T.ntok) load_scalars(T, tn, bsn, gsn);
+                    }
+                    mbar_wait(&tokfull[slot], par, &abort_flag);
+                    const uint8_t* ts = tokbase + slot * TokSlot::kBytes;
+                    const int nt = min(TB, T.ntok - blk * TB);
+                    for (int i = 0; i < nt; ++i) {
+                        const int t = blk * TB + i;
+                        uint2 kt[NQ / 2], qt[NQ / 2];
+                        float vt[4];
+#pragma unroll
+                        for (int pc = 0; pc < NQ / 2; ++pc) {
+                            kt[pc] = *reinterpret_cast<const uint2*>(ts + TokSlot::kOffK + i * DK * 2 + (pc * 64 + l16 * 4) * 2);
+                            qt[pc] = *reinterpret_cast<const uint2*>(ts + TokSlot::kOffQ + i * DK * 2 + (pc * 64 + l16 * 4) * 2);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            vt[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(
+                                ts + TokSlot::kOffV + i * kRecTileRows * 2)[warp * 8 + 2 * j + half]);
+                        const float beta_t = __shfl_sync(0xffffffffu, bsc, t & 31);
+                        const float g_t = __shfl_sync(0xffffffffu, gsc, t & 31);
+                        prep_kq(kt, qt);
+                        token_step(t, vt, beta_t, g_t);
+                    }
+                    __syncthreads();  // the slot has been read by every thread
+                    if (tid == 0 && blk + 2 < nblk) issue_block(blk + 2);
+                }
+                tb_it += nblk;
+            } else {
+            float beta_t = beta_first, g_t = g_first;
+            for (int t = 0; t < T.ntok; ++t) {
+                uint2 kn[NQ / 2], qn[NQ / 2];
+                float vn[4], beta_n = 0.f, g_n = 0.f;
+                if (t + 1 < T.ntok) load_token(t + 1, kn, qn, vn, beta_n, g_n);
+                if (t > 0 || fresh_qk) prep_kq(kw, qw);
+                token_step(t, vr, beta_t, g_t);
 #pragma unroll
                 for (int pc = 0; pc < NQ / 2; ++pc) {
                     kw[pc] = kn[pc];
@@ -413,6 +512,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 g_t = g_n;
             }
 
+            }
             if (!p.store_step) {
                 __nv_bfloat16* sp = p.state_out + static_cast<long long>(T.seq) * p.so_ss + T.head * p.so_sh +
                                     static_cast<long long>(rb) * kRecTileRows * DK;
@@ -438,14 +538,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     if (tid == 0 && abort_flag && p.status) atomicExch(p.status, 1);
 }
 
-template <int DK>
+template <int DK, bool kRing = false>
 constexpr int recurrent_ctas_per_sm() {
-    return DK <= 128 ? 4 : 2;
+    return DK <= 128 ? (kRing ? 3 : 4) : 2;
 }
 
-template <int DK>
-__global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK>()) gdn_recurrent_kernel(const RecurrentParams p) {
-    gdn_recurrent_body<DK>(p);
+template <int DK, bool kRing = false>
+__global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK, kRing>()) gdn_recurrent_kernel(const RecurrentParams p) {
+    gdn_recurrent_body<DK, kRing>(p);
 }
 
 }  // namespace gdn
