@@ -119,6 +119,44 @@ def test_spec_verify_step_states_and_accepted(gdn):
         assert O.rel_fro(s_run.float().cpu(), steps_ref[:, t]) < 1e-2
 
 
+@pytest.mark.parametrize("d", [64, 128, 256])
+def test_long_runs_step_states_and_accepted(gdn, d):
+    # more than 16 tokens per sequence: the instance that streams k, q, v through its token ring;
+    # 41 tokens = five full blocks of 8 and a ragged one, caps that end inside and between blocks
+    B, T, kh, vh = 3, 41, 2, 4
+    p = synthetic.decode_inputs(B, T, kh, vh, d, seed=31 + d)
+    beta_ref, g_ref = O.gating_ref(p["A_log"], p["dt_bias"], p["a"], p["b"])
+    beta, g = beta_ref.bfloat16(), g_ref.float()
+    pd = dev(p)
+    common = (p["q"].float(), p["k"].float(), p["v"].float(), beta.float(), g, p["state"].float())
+    o, steps = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], beta.cuda(), g.cuda(),
+                                     inference_mode=gdn.SpecVerify, is_qk_norm=True)
+    o_ref, steps_ref = O.recurrent_ref(*common, is_qk_norm=True, store_step_state=True)
+    assert steps.shape == (B, T, vh, d, d)
+    close(o, o_ref, "o")
+    close(steps, steps_ref, "step states")
+    nat = torch.tensor([41, 24, 17], dtype=torch.int32)
+    o, s = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], beta.cuda(), g.cuda(),
+                                 num_accepted_tokens=nat.cuda(), inference_mode=1, is_qk_norm=True)
+    o_ref, s_ref = O.recurrent_ref(*common, is_qk_norm=True, num_accepted_tokens=nat)
+    mask = torch.arange(T)[None, :] < nat[:, None]
+    close(o.float().cpu()[mask], o_ref[mask], "o (accepted tokens)")
+    close(s, s_ref, "state after the accepted prefix")
+
+
+def test_recurrent_varlen_short_and_long_sequences(gdn):
+    # one launch with sequences on both sides of the 16-token threshold (and an empty one)
+    lens = [40, 3, 0, 17, 100, 1, 16, 33]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=14, mild_gate=True)
+    pd = dev(p)
+    o, s = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], pd["beta"], pd["g"],
+                                 cu_seqlens=pd["cu_seqlens"])
+    o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), p["beta"].float(), p["g"],
+                                   p["state"].float(), cu_seqlens=p["cu_seqlens"])
+    close(o, o_ref, "o")
+    close(s, s_ref, "state")
+
+
 def test_recurrent_varlen_and_inplace(gdn):
     lens = [1, 5, 2, 9]
     p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=2)
