@@ -72,17 +72,17 @@ static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st, 
 
 // Head dimensions without a prebuilt kernel (or every call when GDN_JIT_RECURRENT=1) go through
 // the run-time compiler: a three-line translation unit instantiates the kernel body for DK.
-static int launch_recurrent_jit(const RecurrentParams& p, int dk, int sms, cudaStream_t st) {
-    const RecurrentConfig cfg = recurrent_config(dk, p.num_tiles, sms);
+static int launch_recurrent_jit(const RecurrentParams& p, int dk, int sms, cudaStream_t st, bool ring) {
+    const RecurrentConfig cfg = recurrent_config(dk, p.num_tiles, sms, ring);
     char src[512];
     snprintf(src, sizeof(src),
              "#include \"kernels/recurrent.cuh\"\n"
              "extern \"C\" __global__ void __launch_bounds__(%d, %d) gdn_recurrent_jit(const gdn::RecurrentParams p) {\n"
-             "    gdn::gdn_recurrent_body<%d>(p);\n}\n",
-             kRecThreads, cfg.ctas_per_sm, dk);
+             "    gdn::gdn_recurrent_body<%d, %s>(p);\n}\n",
+             kRecThreads, cfg.ctas_per_sm, dk, ring ? "true" : "false");
     jit::LoadedKernel k;
     std::string err;
-    if (int rc = jit::get_kernel("recurrent_dk" + std::to_string(dk), src, "gdn_recurrent_jit", &k, &err))
+    if (int rc = jit::get_kernel("recurrent_dk" + std::to_string(dk) + (ring ? "_ring" : ""), src, "gdn_recurrent_jit", &k, &err))
         return fail(rc, "%s", err.c_str());
     GDN_CUDA(cudaFuncSetAttribute(reinterpret_cast<const void*>(k.kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   cfg.smem_bytes));
@@ -259,16 +259,17 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     GDN_REQUIRE(p.num_tiles < (1ll << 31), "gdn_recurrent_forward: too many state tiles");
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);
+    
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(kRecTokRingMin) * s.batch)
                                    : (s.seq_len > kRecTokRingMin);
+    if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
     switch (s.head_dim_k) {
         case 64: return launch_recurrent<64>(p, d->sms, st, ring);
         case 128: return launch_recurrent<128>(p, d->sms, st, ring);
         case 192: return launch_recurrent<192>(p, d->sms, st, ring);
         case 256: return launch_recurrent<256>(p, d->sms, st, ring);
     }
-    return launch_recurrent_jit(p, s.head_dim_k, d->sms, st);  // 320 .. 512: compiled on first use
+    return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);  // 320 .. 512: compiled on first use
 }
 
 }  // extern "C"

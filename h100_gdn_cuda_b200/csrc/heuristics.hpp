@@ -16,13 +16,15 @@ struct RecurrentConfig {
     long long grid;    // persistent CTAs
 };
 
-inline RecurrentConfig recurrent_config(int dk, long long num_tiles, int sms) {
+// `ring`: the multi-token instance (two tile stages, the token ring, every tile a work unit);
+// otherwise the decode instance (four tile stages).
+inline RecurrentConfig recurrent_config(int dk, long long num_tiles, int sms, bool ring = false) {
     RecurrentConfig c;
-    c.stages = 4;
-    c.ctas_per_sm = dk <= 128 ? 4 : 2;
+    c.stages = ring ? 2 : 4;
+    c.ctas_per_sm = ring ? (dk <= 64 ? 4 : (dk <= 256 ? 3 : 2)) : (dk <= 128 ? 4 : 2);
     const int stage = (32 * dk * 2 + 4 * dk + 64 + 127) / 128 * 128;
-    const int tok_slot = 8 * (4 * dk + 64);  // k, q, v slice of 8 tokens (the multi-token ring, two slots)
-    c.smem_bytes = c.stages * stage + 128 + 2 * tok_slot;
+    const int tok_slot = 8 * (4 * dk + 64);  // k, q, v slice of 8 tokens (two slots)
+    c.smem_bytes = c.stages * stage + 128 + (ring ? 2 * tok_slot : 0);
     c.grid = std::min<long long>(num_tiles, static_cast<long long>(sms) * c.ctas_per_sm);
     return c;
 }

@@ -55,7 +55,8 @@ struct RecurrentParams {
 };
 
 constexpr int kRecTileRows = 32;
-constexpr int kRecStages = 4;
+constexpr int kRecStages = 4;      // state tiles in flight per CTA (decode)
+constexpr int kRecStagesRing = 2;  // in the multi-token instance a tile lasts for many tokens: two are enough
 constexpr int kRecThreads = 128;
 constexpr int kRecTokBlock = 8;     // tokens per slot of the multi-token ring
 constexpr int kRecTokRingMin = 16;  // sequences longer than this use it
@@ -82,7 +83,7 @@ struct RecTokSlot {
 
 template <int DK, bool kRing = true>
 constexpr int recurrent_smem_bytes() {
-    return kRecStages * RecStage<DK>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
+    return (kRing ? kRecStagesRing : kRecStages) * RecStage<DK>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
 }
 
 namespace rec {
@@ -127,9 +128,10 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     constexpr int NQ = DK / 32;  // packed pairs per row per lane (lane owns 4 columns of every 64)
     extern __shared__ __align__(128) uint8_t smem[];
     using TokSlot = RecTokSlot<DK>;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kRecStages * Stage::kBytes);
-    uint64_t* tokfull = full + kRecStages;  // [2]
-    uint8_t* tokbase = smem + kRecStages * Stage::kBytes + 128;
+    constexpr int kStages = kRing ? kRecStagesRing : kRecStages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * Stage::kBytes);
+    uint64_t* tokfull = full + kStages;  // [2]
+    uint8_t* tokbase = smem + kStages * Stage::kBytes + 128;
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x;
@@ -145,7 +147,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kRecStages; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
         mbar_init(&tokfull[0], 1);
         mbar_init(&tokfull[1], 1);
         mbar_fence_init();
@@ -206,13 +208,13 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         }
     };
 
-    // The producer walks (unit, rb) pairs kRecStages-1 iterations ahead of the consumers.
+    // The producer walks (unit, rb) pairs kStages-1 iterations ahead of the consumers.
     int prod_unit = blockIdx.x, prod_rb = 0, prod_it = 0;
     Unit prod_u{};
     if (tid == 0 && prod_unit < num_units) prod_u = decode(prod_unit);
     auto produce_one = [&]() {
         if (prod_unit >= num_units) return;
-        issue(prod_u, prod_u.rb0 + prod_rb, prod_it % kRecStages);
+        issue(prod_u, prod_u.rb0 + prod_rb, prod_it % kStages);
         ++prod_it;
         if (++prod_rb == tpu) {
             prod_rb = 0;
@@ -221,7 +223,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         }
     };
     if (tid == 0) {
-        for (int s = 0; s < kRecStages - 1; ++s) produce_one();
+        for (int s = 0; s < kStages - 1; ++s) produce_one();
     }
 
     float beta_first = 0.f, g_first = 0.f;  // scalars of the first token of the current unit
@@ -245,8 +247,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 
         for (int r = 0; r < tpu; ++r, ++it) {
             const int rb = T.rb0 + r;
-            const int stage = it % kRecStages;
-            const uint32_t parity = static_cast<uint32_t>((it / kRecStages) & 1);
+            const int stage = it % kStages;
+            const uint32_t parity = static_cast<uint32_t>((it / kStages) & 1);
             if (tid == 0) produce_one();  // refills the stage consumed in the previous iteration
 
             // ---- staged data -> registers
@@ -428,7 +430,9 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                     }
                 }
             };
-            if (kRing && T.ntok > kRecTokRingMin) {
+            if constexpr (kRing) {
+                // (every sequence of the launch goes through the ring, the short ones with their first block's
+                // latency exposed: the host picks this instance when the sequences average more than kRecTokRingMin tokens)
                 // k, q, v of 8 tokens per slot, two slots: block b + 2 is requested when block b is done
                 constexpr int TB = kRecTokBlock;
                 const int nblk = (T.ntok + TB - 1) / TB;
@@ -540,7 +544,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 
 template <int DK, bool kRing = false>
 constexpr int recurrent_ctas_per_sm() {
-    return DK <= 128 ? (kRing ? 3 : 4) : 2;
+    return kRing ? (DK <= 64 ? 4 : 3) : (DK <= 128 ? 4 : 2);
 }
 
 template <int DK, bool kRing = false>
