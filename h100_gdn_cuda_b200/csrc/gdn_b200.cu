@@ -260,8 +260,9 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     
-    const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(kRecTokRingMin) * s.batch)
-                                   : (s.seq_len > kRecTokRingMin);
+    const int ring_min = jit::env_int("GDN_REC_RING_MIN", kRecTokRingMin);  // tuning aid
+    const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
+                                   : (s.seq_len > ring_min);
     if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
     switch (s.head_dim_k) {
         case 64: return launch_recurrent<64>(p, d->sms, st, ring);
