@@ -21,9 +21,9 @@ struct RecurrentConfig {
 inline RecurrentConfig recurrent_config(int dk, long long num_tiles, int sms, bool ring = false) {
     RecurrentConfig c;
     c.stages = ring ? 2 : 4;
-    c.ctas_per_sm = ring ? (dk <= 64 ? 4 : (dk <= 256 ? 3 : 2)) : (dk <= 128 ? 4 : 2);
-    const int stage = (32 * dk * 2 + 4 * dk + 64 + 127) / 128 * 128;
-    const int tok_slot = 8 * (4 * dk + 64);  // k, q, v slice of 8 tokens (two slots)
+    c.ctas_per_sm = ring ? (dk <= 64 ? 4 : (dk <= 256 ? 3 : 1)) : (dk <= 128 ? 4 : 2);
+    const int tok_slot = 8 * (4 * dk + 64);  // k, q, v slice of 8 tokens (two ring slots; one more in every stage)
+    const int stage = (32 * dk * 2 + (ring ? tok_slot : 4 * dk + 64) + 127) / 128 * 128;
     c.smem_bytes = c.stages * stage + 128 + (ring ? 2 * tok_slot : 0);
     c.grid = std::min<long long>(num_tiles, static_cast<long long>(sms) * c.ctas_per_sm);
     return c;

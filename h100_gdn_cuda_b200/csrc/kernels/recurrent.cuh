@@ -61,15 +61,17 @@ constexpr int kRecThreads = 128;
 constexpr int kRecTokBlock = 8;     // tokens per slot of the multi-token ring
 constexpr int kRecTokRingMin = 16;  // sequences longer than this use it
 
-// One ring stage: the 32 x DK state tile, then k and q of the unit's first token
-// (DK bf16 each) and the 32 entries of v that belong to the tile's rows.
-template <int DK>
+// One ring stage: the 32 x DK state tile, then k and q (DK bf16 each) and the 32 entries of v that
+// belong to the tile's rows, for the unit's first token (decode instance) or its first
+// kRecTokBlock tokens (multi-token instance; same layout as a slot of the token ring).
+template <int DK, bool kRing = false>
 struct RecStage {
+    static constexpr int kTok = kRing ? kRecTokBlock : 1;
     static constexpr int kTileBytes = kRecTileRows * DK * 2;
     static constexpr int kOffK = kTileBytes;
-    static constexpr int kOffQ = kOffK + DK * 2;
-    static constexpr int kOffV = kOffQ + DK * 2;
-    static constexpr int kBytes = (kOffV + kRecTileRows * 2 + 127) / 128 * 128;
+    static constexpr int kOffQ = kOffK + kTok * DK * 2;
+    static constexpr int kOffV = kOffQ + kTok * DK * 2;
+    static constexpr int kBytes = (kOffV + kTok * kRecTileRows * 2 + 127) / 128 * 128;
 };
 
 // One slot of the multi-token ring: k, q (DK bf16 each) and the tile's 32 entries of v for 8 tokens.
@@ -83,7 +85,7 @@ struct RecTokSlot {
 
 template <int DK, bool kRing = true>
 constexpr int recurrent_smem_bytes() {
-    return (kRing ? kRecStagesRing : kRecStages) * RecStage<DK>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
+    return (kRing ? kRecStagesRing : kRecStages) * RecStage<DK, kRing>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
 }
 
 namespace rec {
@@ -124,7 +126,7 @@ template <int DK, bool kRing = true>
 __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     using namespace ptx;
     using namespace rec;
-    using Stage = RecStage<DK>;
+    using Stage = RecStage<DK, kRing>;
     constexpr int NQ = DK / 32;  // packed pairs per row per lane (lane owns 4 columns of every 64)
     extern __shared__ __align__(128) uint8_t smem[];
     using TokSlot = RecTokSlot<DK>;
@@ -180,18 +182,20 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     // Producer (one thread): everything tile `rb` of `unit` needs for its first token.
     auto issue = [&](const Unit& t, int rb, int stage) {
         uint8_t* dst = smem + stage * Stage::kBytes;
-        const uint32_t bytes = (has_in ? Stage::kTileBytes : 0) + (t.ntok > 0 ? 4 * DK + kRecTileRows * 2 : 0);
+        const int nt0 = min(t.ntok, Stage::kTok);  // tokens whose k, q, v travel with the tile
+        const uint32_t bytes = (has_in ? Stage::kTileBytes : 0) + static_cast<uint32_t>(nt0) * (4 * DK + kRecTileRows * 2);
         mbar_arrive_expect_tx(&full[stage], bytes);
         if (has_in) {
             const __nv_bfloat16* src = p.state_in + t.seq * p.si_ss + t.head * p.si_sh +
                                        static_cast<long long>(rb) * kRecTileRows * DK;
             bulk_load(dst, src, Stage::kTileBytes, &full[stage]);
         }
-        if (t.ntok > 0) {
-            bulk_load(dst + Stage::kOffK, p.k + t.bidx * p.k_sb + t.tok0 * p.k_st + t.khead * p.k_sh, DK * 2, &full[stage]);
-            bulk_load(dst + Stage::kOffQ, p.q + t.bidx * p.q_sb + t.tok0 * p.q_st + t.khead * p.q_sh, DK * 2, &full[stage]);
-            bulk_load(dst + Stage::kOffV, p.v + t.bidx * p.v_sb + t.tok0 * p.v_st + t.head * p.v_sh + rb * kRecTileRows,
-                      kRecTileRows * 2, &full[stage]);
+        for (int i = 0; i < nt0; ++i) {
+            const long long tok = t.tok0 + i;
+            bulk_load(dst + Stage::kOffK + i * DK * 2, p.k + t.bidx * p.k_sb + tok * p.k_st + t.khead * p.k_sh, DK * 2, &full[stage]);
+            bulk_load(dst + Stage::kOffQ + i * DK * 2, p.q + t.bidx * p.q_sb + tok * p.q_st + t.khead * p.q_sh, DK * 2, &full[stage]);
+            bulk_load(dst + Stage::kOffV + i * kRecTileRows * 2,
+                      p.v + t.bidx * p.v_sb + tok * p.v_st + t.head * p.v_sh + rb * kRecTileRows, kRecTileRows * 2, &full[stage]);
         }
     };
     auto load_scalars = [&](const Unit& t, int tk, float& bt, float& gt) {
@@ -229,7 +233,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     float beta_first = 0.f, g_first = 0.f;  // scalars of the first token of the current unit
     if (static_cast<int>(blockIdx.x) < num_units) {
         const Unit t0 = decode(blockIdx.x);
-        if (t0.ntok > 0) load_scalars(t0, 0, beta_first, g_first);
+        const int tk = kRing ? lane : 0;  // multi-token instance: lane l holds the scalars of token l
+        if (tk < t0.ntok) load_scalars(t0, tk, beta_first, g_first);
     }
 
     int it = 0;
@@ -239,7 +244,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         float beta_next = 0.f, g_next = 0.f;
         if (unit + stride < num_units) {
             const Unit tn = decode(unit + stride);
-            if (tn.ntok > 0) load_scalars(tn, 0, beta_next, g_next);
+            const int tk = kRing ? lane : 0;
+            if (tk < tn.ntok) load_scalars(tn, tk, beta_next, g_next);
         }
         // per-unit values of the first token (kept across the unit's tiles when ntok == 1)
         f2 k2[NQ], q2[NQ];
@@ -431,13 +437,16 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 }
             };
             if constexpr (kRing) {
+                static_assert(Stage::kOffQ - Stage::kOffK == TokSlot::kOffQ && Stage::kOffV - Stage::kOffK == TokSlot::kOffV,
+                              "the stage's token block must be laid out like a ring slot");
                 // (every sequence of the launch goes through the ring, the short ones with their first block's
                 // latency exposed: the host picks this instance when the sequences average more than kRecTokRingMin tokens)
-                // k, q, v of 8 tokens per slot, two slots: block b + 2 is requested when block b is done
+// k, q, v of 8 tokens per block.  Block 0 came with the tile's stage; blocks 1.. go through
+                // the two slots of the token ring, block b + 2 being requested when block b is done.
                 constexpr int TB = kRecTokBlock;
                 const int nblk = (T.ntok + TB - 1) / TB;
-                auto issue_block = [&](int blk) {  // one thread
-                    const int slot = (tb_it + blk) & 1;
+                auto issue_block = [&](int blk) {  // one thread; blk >= 1
+                    const int slot = (tb_it + blk - 1) & 1;
                     uint8_t* dst = tokbase + slot * TokSlot::kBytes;
                     const int nt = min(TB, T.ntok - blk * TB);
                     mbar_arrive_expect_tx(&tokfull[slot], static_cast<uint32_t>(nt) * (4 * DK + kRecTileRows * 2));
@@ -453,15 +462,13 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                     }
                 };
                 if (tid == 0) {
-                    issue_block(0);
                     if (nblk > 1) issue_block(1);
+                    if (nblk > 2) issue_block(2);
                 }
-                // beta and gate: lane l holds those of token 32 * group + l, the next group one ahead
-                float bsc = 0.f, gsc = 0.f, bsn = 0.f, gsn = 0.f;
-                if (lane < T.ntok) load_scalars(T, lane, bsc, gsc);
+                // beta and gate: lane l holds those of token 32 * group + l (group 0 was fetched during
+                // the previous unit), the next group is fetched one group ahead
+                float bsc = beta_first, gsc = g_first, bsn = 0.f, gsn = 0.f;
                 for (int blk = 0; blk < nblk; ++blk) {
-                    const int slot = (tb_it + blk) & 1;
-                    const uint32_t par = static_cast<uint32_t>(((tb_it + blk) >> 1) & 1);
                     if ((blk & 3) == 0) {
                         if (blk > 0) {
                             bsc = bsn;
@@ -472,8 +479,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         gsn = 0.f;
                         if (tn < T.ntok) load_scalars(T, tn, bsn, gsn);
                     }
-                    mbar_wait(&tokfull[slot], par, &abort_flag);
-                    const uint8_t* ts = tokbase + slot * TokSlot::kBytes;
+                    const uint8_t* ts;
+                    if (blk == 0) {
+                        ts = st + Stage::kTileBytes;  // same layout as a ring slot
+                    } else {
+                        const int slot = (tb_it + blk - 1) & 1;
+                        mbar_wait(&tokfull[slot], static_cast<uint32_t>(((tb_it + blk - 1) >> 1) & 1), &abort_flag);
+                        ts = tokbase + slot * TokSlot::kBytes;
+                    }
                     const int nt = min(TB, T.ntok - blk * TB);
                     for (int i = 0; i < nt; ++i) {
                         const int t = blk * TB + i;
@@ -493,10 +506,10 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         prep_kq(kt, qt);
                         token_step(t, vt, beta_t, g_t);
                     }
-                    __syncthreads();  // the slot has been read by every thread
-                    if (tid == 0 && blk + 2 < nblk) issue_block(blk + 2);
+                    __syncthreads();  // the block (stage or slot) has been read by every thread
+                    if (tid == 0 && blk >= 1 && blk + 2 < nblk) issue_block(blk + 2);
                 }
-                tb_it += nblk;
+                if (nblk > 1) tb_it += nblk - 1;
             } else {
             float beta_t = beta_first, g_t = g_first;
             for (int t = 0; t < T.ntok; ++t) {
