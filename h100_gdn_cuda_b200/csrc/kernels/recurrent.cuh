@@ -17,11 +17,13 @@
 // The eight row sums are reduced over 16 lanes with a transposing butterfly (8 shuffles
 // instead of 32).  For single-token decode q/k normalisation and k.q are computed once per
 // unit, not per tile.  New states leave through coalesced 8-byte stores from registers.
-// Runs of more than one token (short prefill, speculative verify, head dims the chunked kernels do
-// not cover) make every tile a work unit of its own, so that a few long sequences still spread
-// over all CTAs; sequences longer than kRecTokRingMin tokens get k, q and v of 8 tokens at a time
-// through a second, two-slot ring of bulk copies (one token fetched ahead of the one in work
-// left the whole load latency, about a microsecond, exposed on every token).
+// Long runs of tokens (short prefill, head dims the chunked kernels do not cover) take a second
+// instance of the kernel (kRing), chosen by the host when the sequences average more than
+// kRecTokRingMin tokens: every tile is a work unit of its own, so that a few long sequences
+// still spread over all CTAs, and k, q, v arrive 8 tokens at a time by bulk copies: the first
+// block with the tile's stage, the others through a two-slot ring.  (With one token fetched ahead
+// of the one in work, as the decode instance does for its few tokens, every token paid the whole
+// load latency, about a microsecond.)
 #pragma once
 #include "sm100_ptx.cuh"
 
