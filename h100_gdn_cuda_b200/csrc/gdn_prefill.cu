@@ -7,6 +7,7 @@
 #include "kernels/prefill_seq.cuh"
 #include "kernels/prefill_segments.cuh"
 #include "kernels/prefill_uw.cuh"
+#include "kernels/prefill_zp.cuh"
 #include "tma_host.hpp"
 
 using namespace gdn;
@@ -129,6 +130,32 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
         if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
         gdn_uw_kernel<kD, false><<<grid, 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
     }
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+// Chunk-parallel stage of the whole-layer path: Z and PT of every (chunk, v-head) into `blocks`.
+int launch_zp(const GdnShape& s, const GdnTokenTensor& q, const GdnTokenTensor& k, const GdnTokenScalar& beta,
+              const GdnTokenScalar& gate, void* blocks, float p_scale, DeviceInfo* d, cudaStream_t st) {
+    const int nc = num_chunks(s);
+    if (nc == 0) return GDN_OK;
+    CUtensorMap tmK, tmQ;
+    if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
+    if (int rc = make_token_map(&tmQ, q, s, s.num_k_heads, "q")) return rc;
+    ZPParams p{};
+    p.map = chunk_map(s);
+    p.beta = scalar_view(beta);
+    p.gate = scalar_view(gate);
+    p.blocks = static_cast<uint8_t*>(blocks);
+    p.p_scale = p_scale;
+    p.kh = s.num_k_heads;
+    p.vh = s.num_v_heads;
+    p.num_chunks = nc;
+    p.status = d->status;
+    constexpr int smem = ZPSmem::kBytes;
+    if (int rc = set_smem(gdn_zp_kernel, smem)) return rc;
+    const int grid = zp_grid(static_cast<long long>(nc) * s.num_k_heads, d->sms);
+    gdn_zp_kernel<<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
@@ -286,9 +313,9 @@ size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (wide_heads(*s)) return 0;
     const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
-    // one block of U, W (64 x 128 bf16 each) and P (64 x 64 bf16) per (chunk, v-head); for a
+    // one block of Z (64 x 128 bf16) and PT (64 x 64 bf16) per (chunk, v-head); for a
     // segmented run (few long padded sequences) three fp32 states per chain and segment on top
-    size_t bytes = chunks * static_cast<size_t>(s->num_v_heads) * kUnitBlockBytes + 256;
+    size_t bytes = chunks * static_cast<size_t>(s->num_v_heads) * kZPBlockBytes + 256;
     if (!s->cu_seqlens) {
         const long long chains = static_cast<long long>(s->batch) * s->num_v_heads;
         const SegmentPlan plan = prefill_segments(chains, (s->seq_len + kChunk - 1) / kChunk, false);
@@ -331,15 +358,14 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         }
         return GDN_OK;
     }
-    const GdnTokenTensor none{};
-    if (int rc = launch_uw(s, a->k, a->v, none, none, a->beta, a->gate, true, d, st, &a->q, a->workspace, a->scale))
-        return rc;
+    if (int rc = launch_zp(s, a->q, a->k, a->beta, a->gate, a->workspace, a->scale, d, st)) return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
     {
-        CUtensorMap tmQ, tmK, tmO;
+        CUtensorMap tmQ, tmK, tmV, tmO;
         if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
         if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
+        if (int rc = make_token_map(&tmV, a->v, s, s.num_v_heads, "v")) return rc;
         if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "out")) return rc;
         FusedParams p{};
         p.map = chunk_map(s);
@@ -362,19 +388,19 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         const SegmentPlan plan = prefill_segments(chains, (s.seq_len + kChunk - 1) / kChunk, packed);
         if (packed && s.batch > 1 && s.batch <= kMaxOrderedSeqs && chains > d->sms) {
             // more chains than SMs and unequal lengths: dispatch the longest sequences first
-            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kUnitBlockBytes;
+            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kZPBlockBytes;
             int* order = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256);
             gdn_seq_order_kernel<<<(s.batch + 127) / 128, 128, 0, st>>>(s.cu_seqlens, s.batch, order);
             GDN_CUDA(cudaGetLastError());
             p.seq_order = order;
-            gdn_fused_seq_kernel<<<dim3(s.num_v_heads, s.batch), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(s.num_v_heads, s.batch), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
         } else if (plan.num_segments <= 1) {
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
         } else {
             // composite transitions of all segments, their start states, then all segments at once
-            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kUnitBlockBytes;
+            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kZPBlockBytes;
             uint8_t* extra = static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256;
             float* seg_mn = reinterpret_cast<float*>(extra);
             float* seg_start = seg_mn + static_cast<size_t>(chains) * plan.num_segments * 2 * kD * kD;
@@ -383,7 +409,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             p.seg_mn = seg_mn;
             p.seg_start = seg_start;
             p.mode = 1;
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, 2 * plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, 2 * plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
             SegCombineParams cp{};
             cp.seg_mn = seg_mn;
@@ -398,21 +424,13 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R), 128, SegCombineSmem::kBytes, st>>>(cp);
             GDN_CUDA(cudaGetLastError());
             p.mode = 2;
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
         }
     }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
     return GDN_OK;
 }
-
-#ifdef GDN_PHASE_TIMING
-int gdn_debug_phase_stamps(long long* out64) {
-    GDN_CUDA(cudaDeviceSynchronize());
-    GDN_CUDA(cudaMemcpyFromSymbol(out64, g_phase_stamps, sizeof(long long) * 64));
-    return GDN_OK;
-}
-#endif
 
 // ------------------------------------------------------------------ prefill on built-in scratch
 // Scratch for callers that cannot allocate device memory (see include/gdn_b200.h).  The array
@@ -429,7 +447,7 @@ int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* a, gdn_stream_t str
     if (need > GDN_STATIC_SCRATCH_BYTES)
         return fail(GDN_ERR_WORKSPACE,
                     "gdn_chunked_forward_static_scratch: this problem needs %zu bytes of scratch but the built-in "
-                    "array holds %u (about 640 bytes per token and v-head); use gdn_chunked_forward with a "
+                    "array holds %u (384 bytes per token and v-head); use gdn_chunked_forward with a "
                     "caller-provided workspace",
                     need, GDN_STATIC_SCRATCH_BYTES);
     int dev = 0;

@@ -78,4 +78,10 @@ inline int uw_grid(long long units, int sms) {
     return static_cast<int>(std::min<long long>(units, static_cast<long long>(sms) * prefill_config().uw_ctas_per_sm));
 }
 
+// Grid of the persistent chunk-parallel kernel of the whole-layer path (units = chunks x k-heads,
+// two CTAs of 256 threads per SM).
+inline int zp_grid(long long units, int sms) {
+    return static_cast<int>(std::min<long long>(units, static_cast<long long>(sms) * 2));
+}
+
 }  // namespace gdn

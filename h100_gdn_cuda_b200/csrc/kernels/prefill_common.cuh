@@ -50,6 +50,11 @@ __device__ __forceinline__ long long gdn_clock_ordered() {
 // U (16 KB), W (16 KB), P (8 KB).  One untiled bulk copy moves a whole block in either direction.
 constexpr int kUnitBlockBytes = 2 * kChunk * 128 * 2 + kChunk * kChunk * 2;
 
+// Scratch of the whole-layer path since the WY/UT transform was folded into the recurrence (see
+// prefill_zp.cuh): per (global chunk, v-head) unit Z (64 x 128 bf16 as two 64 x 64 swizzled atoms, the
+// shared-memory image of an MN-major B operand) and then PT (64 x 64, one atom).
+constexpr int kZPBlockBytes = kChunk * 128 * 2 + kChunk * kChunk * 2;
+
 // per-token scalar tensor (beta or gate) as the kernels see it
 struct ScalarView {
     const void* ptr;

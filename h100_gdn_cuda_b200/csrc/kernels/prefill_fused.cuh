@@ -1,24 +1,27 @@
 // State propagation + output of chunked Gated DeltaNet prefill, warp-specialised.
-// One CTA of 448 threads walks the chunks of one (sequence, v-head):
-//     U_new = U - W S^T
-//     O     = scale * ( e^{g} .* (Q S^T) + P U_new ),   P = tril(Q K^T .* e^{g_i - g_j}) (precomputed)
-//     S    <- e^{g_L} S + U_new^T (K .* e^{g_L - g})
+// One CTA of 512 threads walks the chunks of one (sequence, v-head).  With T = (I + A)^-1 diag(beta) of
+// the WY/UT transform folded into two precomputed matrices per chunk (prefill_zp.cuh),
+//     Z = T^T diag(e^{g_L - g}) K   and   PT = scale tril(Q K^T .* e^{g_i - g_j}) T,
+// the chunk step is
+//     R  = V - e^{g} .* (K S^T)            (U_new = T R is never formed)
+//     O  = scale * e^{g} .* (Q S^T) + PT R
+//     S <- e^{g_L} S + R^T Z
 // This is the path gdn_chunked_forward uses; it stands in for the reference's
 // sm90_bf16_chunked_seq_state_update and sm90_bf16_gdn_chunked_compute_O
 // (kernels/sm90_bf16_chunked_seq_state_update2.cuh, sm90_bf16_gdn_chunked_compute_O.cuh:23-530)
 // and never writes per-chunk states.
 //
 // The only serial dependence between chunks runs through the state:
-//     S_bf(c) -> [MMA] D1 = U^T I - S_bf W^T -> [pass] Un_a, Un_b -> [MMA] dS = Un_b K -> [pass] S, S_bf(c+1)
+//     S_bf(c) -> [MMA] D1 = S_bf K^T -> [pass] R = V^T - e^g D1 -> [MMA] dS = R Z -> [pass] S, S_bf(c+1)
 // Roles keep everything else off that chain:
 //   warps 0-7   state warps: own the fp32 state in registers (row = TMEM lane, 64 columns each),
 //               run the two passes of the chain
 //   warps 8-11  output warps: O epilogue (scale, transpose through shared memory, coalesced stores)
-//   warp 12     producer: chunk-local gate cumsum; per chunk one bulk copy of its U, W, P block of
-//               the scratch and tensor copies of Q and K, into a two-stage ring
+//   warp 12     producer: chunk-local gate cumsum; per chunk one bulk copy of its Z, PT block of
+//               the scratch and tensor copies of Q, K and V, into a two-stage ring
 //   warp 13     one thread issues every tcgen05.mma and commits completion onto mbarriers
-// All operands are transposed so that the 128 state rows are the MMA M dimension; S_bf, Un_a,
-// Un_b are bf16 A operands in tensor memory; Q, K, W, U, P tiles are used as TMA delivered them.
+// All operands are transposed so that the 128 state rows are the MMA M dimension; S_bf and R are
+// bf16 A operands in tensor memory; Q, K, Z, PT tiles are used as the copies delivered them.
 #pragma once
 #include <cuda.h>
 
@@ -37,12 +40,12 @@ struct FusedParams {
     int kh, vh;
     float scale;
     int* status;
-    const uint8_t* blocks;  // U, W, P of every (global chunk, v-head): kUnitBlockBytes each
+    const uint8_t* blocks;  // Z, PT of every (global chunk, v-head): kZPBlockBytes each
     // Segmented runs (padded mode, few long sequences; see gdn_chunked_forward).  The state obeys
     // S' = S M_c + N_c per chunk, so a segment of chunks has a composite (M, N) as well.
     //   mode 0: one CTA walks the whole sequence (blockIdx.z = 0).
     //   mode 1: blockIdx.z = 2 * segment + kind; no output.  kind 0 starts from S = 0 and ends with
-    //           N of the segment; kind 1 starts from S = I with U taken as 0 and ends with M.
+    //           N of the segment; kind 1 starts from S = I with V taken as 0 and ends with M.
     //           Both are written in fp32 to seg_mn[((chain * num_segments + segment) * 2 + kind)].
     //   mode 2: blockIdx.z = segment; starts from seg_start[chain * num_segments + segment] (fp32),
     //           writes the output of its chunks; the last segment writes the final state.
@@ -59,11 +62,11 @@ struct FusedParams {
 struct FusedSmem {
     static constexpr int D = 128;
     static constexpr int kTile = kChunk * D * 2;  // 16 KB
-    // U, W, P in the order of a unit block of the scratch, so that one bulk copy fills all three
-    static constexpr int kOffQ = 0, kOffK = kTile, kOffU = 2 * kTile, kOffW = 3 * kTile, kOffP = 4 * kTile;
-    static constexpr int kStage = 2 * kTile + kUnitBlockBytes;  // Q, K, U, W, P
+    // Z, PT in the order of a unit block of the scratch, so that one bulk copy fills both
+    static constexpr int kOffQ = 0, kOffK = kTile, kOffV = 2 * kTile, kOffZ = 3 * kTile, kOffPT = 4 * kTile;
+    static constexpr int kStage = 3 * kTile + kZPBlockBytes;  // Q, K, V, Z, PT
     static constexpr int kOffO = 2 * kStage;         // two output staging tiles
-    static constexpr int kOffGate = kOffO + 2 * kTile;  // 3 x { e^g[64], e^{gL-g}[64], e^{gL} }
+    static constexpr int kOffGate = kOffO + 2 * kTile;  // 3 x { scale e^g[64], -e^g[64], e^{gL} }
     static constexpr int kGateStride = (2 * 64 + 4) * 4;
     static constexpr int kOffBar = kOffGate + 3 * kGateStride;
     static constexpr int kBytes = kOffBar + 128 + 1024;
@@ -72,13 +75,12 @@ struct FusedSmem {
 namespace fused {
 constexpr int kThreads = 512;  // 16 warps = 4 warpgroups (the last holds the producer, the issuer and 2 idle warps)
 constexpr uint32_t kTmSbf = 0;    // bf16 state, 64 columns
-constexpr uint32_t kTmUnA = 64;   // bf16 U_new^T, 32 columns
-constexpr uint32_t kTmUnB = 96;   // bf16 U_new^T .* decay, 32 columns
-constexpr uint32_t kTmD1 = 128;   // fp32 U_new^T, 64 columns
+constexpr uint32_t kTmR = 64;     // bf16 R = V^T - e^g .* (S K^T), 32 columns
+constexpr uint32_t kTmD1 = 128;   // fp32 S K^T, 64 columns
 constexpr uint32_t kTmO1a = 192;  // fp32 S Q^T, even chunks
 constexpr uint32_t kTmDS = 256;   // fp32 state increment, 128 columns
 constexpr uint32_t kTmO1b = 384;  // fp32 S Q^T, odd chunks
-constexpr uint32_t kTmO2 = 448;   // fp32 U_new^T P^T
+constexpr uint32_t kTmO2 = 448;   // fp32 R PT^T
 
 // Register re-allocation between warpgroups (every warp of the warpgroup executes it).
 template <int N>
@@ -121,7 +123,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 
 __global__ void __launch_bounds__(fused::kThreads, 1)
     gdn_fused_seq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                         const __grid_constant__ CUtensorMap tmO, const FusedParams p) {
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                         const FusedParams p) {
     using namespace ptx;
     using namespace fused;
     using L = FusedSmem;
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     uint64_t* bar_ds = bars + 7;
     uint64_t* bar_o = bars + 8;
     uint64_t* bar_ofree = bars + 9;
-    uint64_t* bar_full2 = bars + 10;  // [2]: P, K, Q of a stage (bar_full: U, W and the gate vectors)
+    uint64_t* bar_full2 = bars + 10;  // [2]: Z, PT, Q of a stage (bar_full: K, V and the gate vectors)
     uint64_t* bar_go = bars + 12;     // state warps are past their chunk-boundary work: the epilogue may run
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
@@ -264,17 +267,17 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const int n = chunk_n(c);
             const float* gb = gate_buf(c);
             mbar_wait(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);  // gate values visible
-            // ---- U_new^T = U^T - S W^T -> two bf16 operand copies (rows past the end zeroed)
-            // This thread's 32 values of U^T come straight from the TMA tile (element (token, row)
+            // ---- R = V^T - e^g .* (S K^T) -> bf16 operand copy in tensor memory
+            // This thread's 32 values of V^T come straight from the TMA tile (element (token, row)
             // of the swizzled layout), packed two tokens per register while the MMA is running.
-            const uint8_t* sU = smem + (c & 1) * L::kStage + L::kOffU;
-            uint32_t upk[16];
+            const uint8_t* sV = smem + (c & 1) * L::kStage + L::kOffV;
+            uint32_t vpk[16];
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
                 const int i0 = 32 * hf + 2 * e;
-                const uint32_t lo = *reinterpret_cast<const uint16_t*>(sU + i0 * 128 + uoff8[i0 & 7]);
-                const uint32_t hi = *reinterpret_cast<const uint16_t*>(sU + (i0 + 1) * 128 + uoff8[(i0 + 1) & 7]);
-                upk[e] = zero_u ? 0u : (lo | (hi << 16));
+                const uint32_t lo = *reinterpret_cast<const uint16_t*>(sV + i0 * 128 + uoff8[i0 & 7]);
+                const uint32_t hi = *reinterpret_cast<const uint16_t*>(sV + (i0 + 1) * 128 + uoff8[(i0 + 1) & 7]);
+                vpk[e] = zero_u ? 0u : (lo | (hi << 16));
             }
             const int nloc = n - 32 * hf;  // tokens of this half that exist
             // The state warps now idle until D1 arrives: the window in which the output warps (which
@@ -283,60 +286,42 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             if (lane == 0) mbar_arrive(bar_go);
             mbar_wait(bar_d1, par, abort_flag);
             tc_fence_after_sync();
-            if (c == 40 && tid == 0) GDN_STAMP_ANY(40);
             {
                 uint32_t r[32];
-                tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);  // -(S W^T)
-                float dec[32];
+                tmem_ld32(tmem + kTmD1 + tm_lane + 32 * hf, r);  // S K^T
+                float neg[32];                                    // -e^{g} of this half's tokens
 #pragma unroll
                 for (int e4 = 0; e4 < 8; ++e4) {
                     const float4 t = *reinterpret_cast<const float4*>(gb + 64 + 32 * hf + 4 * e4);
-                    dec[4 * e4] = t.x; dec[4 * e4 + 1] = t.y; dec[4 * e4 + 2] = t.z; dec[4 * e4 + 3] = t.w;
+                    neg[4 * e4] = t.x; neg[4 * e4 + 1] = t.y; neg[4 * e4 + 2] = t.z; neg[4 * e4 + 3] = t.w;
                 }
                 tmem_wait_ld();
-                uint32_t wa[16], wb[16];
-                if (nloc >= 32) {  // every token of this half exists (all chunks but a ragged last one)
+                uint32_t wa[16];
 #pragma unroll
-                    // the plain copy is on its way to tensor memory while the scaled one is computed
-                    f2 u2[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        u2[e] = add2(pk(bf16_lo(upk[e]), bf16_hi(upk[e])),
-                                     pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])));
-                        float u0, u1;
-                        unpk(u2[e], u0, u1);
-                        wa[e] = pack_bf16(u0, u1);
+                for (int e = 0; e < 16; ++e) {
+                    float r0, r1;
+                    unpk(fma2(pk(neg[2 * e], neg[2 * e + 1]), pk(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])),
+                              pk(bf16_lo(vpk[e]), bf16_hi(vpk[e]))),
+                         r0, r1);
+                    // rows past the end of a sequence meet zero rows of Z and zero columns of PT; they are
+                    // cleared all the same so that no stray Inf/NaN of a neighbouring sequence can enter
+                    if (nloc < 32) {
+                        if (2 * e >= nloc) r0 = 0.f;
+                        if (2 * e + 1 >= nloc) r1 = 0.f;
                     }
-                    tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        float d0, d1;
-                        unpk(mul2(u2[e], pk(dec[2 * e], dec[2 * e + 1])), d0, d1);
-                        wb[e] = pack_bf16(d0, d1);
-                    }
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float u0 = 2 * e < nloc ? bf16_lo(upk[e]) + __uint_as_float(r[2 * e]) : 0.f;
-                        const float u1 = 2 * e + 1 < nloc ? bf16_hi(upk[e]) + __uint_as_float(r[2 * e + 1]) : 0.f;
-                        wa[e] = pack_bf16(u0, u1);
-                        wb[e] = pack_bf16(u0 * dec[2 * e], u1 * dec[2 * e + 1]);
-                    }
+                    wa[e] = pack_bf16(r0, r1);
                 }
-                if (nloc < 32) tmem_st16(tmem + kTmUnA + tm_lane + 16 * hf, wa);
-                tmem_st16(tmem + kTmUnB + tm_lane + 16 * hf, wb);
+                tmem_st16(tmem + kTmR + tm_lane + 16 * hf, wa);
             }
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_un);
-            if (c == 40 && tid == 0) GDN_STAMP_ANY(41);
             // ---- S <- e^{g_L} S + dS
             const float eg_last = gb[128];
             const f2 eg2 = pk(eg_last, eg_last);
             mbar_wait(bar_ds, par, abort_flag);
             tc_fence_after_sync();
-            if (c == 40 && tid == 0) GDN_STAMP_ANY(42);
             {
                 // both halves of this thread's 64 increments are requested at once; the new bf16
                 // state of a half is on its way to tensor memory while the other half is computed
@@ -362,10 +347,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_sbf);
             }
-            if (c == 40 && tid == 0) GDN_STAMP_ANY(43);
         }
         if (lane == 0) mbar_arrive(bar_go);  // releases the last chunk's epilogue
-        if (p.mode == 1) {
+        // nothing is written once a wait of this CTA has given up (the results would be garbage)
+        const bool healthy = *abort_flag == 0;
+        if (!healthy) {
+        } else if (p.mode == 1) {
             float4* d4 = reinterpret_cast<float4*>(p.seg_mn + ((chain * p.num_segments + segment) * 2 + seg_kind) * (D * D) +
                                                    static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll
@@ -404,11 +391,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a) + tm_lane;
             const uint32_t tO2 = tmem + kTmO2 + tm_lane;
             mbar_wait_relaxed<200>(&bar_full[c & 1], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
-            if (c == 40 && otid == 0) GDN_STAMP_ANY(49);
             mbar_wait_relaxed<100>(bar_o, par, abort_flag);
             mbar_wait_relaxed<50>(bar_go, static_cast<uint32_t>((c + 1) & 1), abort_flag);
             tc_fence_after_sync();
-            if (c == 40 && otid == 0) GDN_STAMP_ANY(50);
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 uint32_t r1[16], r2[16];
@@ -423,7 +408,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     gv[4 * e4] = t.x; gv[4 * e4 + 1] = t.y; gv[4 * e4 + 2] = t.z; gv[4 * e4 + 3] = t.w;
                 }
                 tmem_wait_ld();
-                if (c == 40 && otid == 0) GDN_STAMP_ANY(53 + 2 * b);
                 if (b == 3) {
                     tc_fence_before_sync();
                     __syncwarp();
@@ -435,15 +419,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     const float o = fmaf(gv[e], __uint_as_float(r1[e]), __uint_as_float(r2[e]));
                     *reinterpret_cast<__nv_bfloat16*>(sO + i * 128 + off8[i & 7]) = __float2bfloat16(o);
                 }
-                if (c == 40 && otid == 0) GDN_STAMP_ANY(54 + 2 * b);
             }
-            if (c == 40 && otid == 0) GDN_STAMP_ANY(51);
             const long long tok0 = seq_tok0 + static_cast<long long>(c) * kChunk;
             const bool ragged = packed && n < kChunk;  // a full-box store would spill into the next sequence
             fence_proxy_async_smem();
             if (otid == 0) bulk_wait_read<0>();  // earlier stores have finished reading their staging tiles
             named_bar_sync(1, 128);
-            if (!ragged) {
+            if (*abort_flag != 0) {
+                // a wait has given up: the tile is garbage and stays on chip
+            } else if (!ragged) {
                 if (otid == 0) {
                     tma_store_4d(&tmO, sO, 0, head, static_cast<int>(tok0), batch);
                     tma_store_4d(&tmO, sO + 8192, 64, head, static_cast<int>(tok0), batch);
@@ -452,7 +436,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             } else {
                 store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid);
             }
-            if (c == 40 && otid == 0) GDN_STAMP_ANY(52);
         }
         if (otid == 0) bulk_wait_read<0>();
     } else {
@@ -495,12 +478,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             // tokens past the end carry the last valid value (their raw gate was taken as 0)
             const float g_last = __shfl_sync(0xffffffffu, (n - 1 < 32) ? g0 : g1, (n - 1) & 31);
             const float e0 = p.scale * __expf(g0), e1 = p.scale * __expf(g1);  // epilogue factor for S q
-            const float d0 = __expf(g_last - g0), d1 = __expf(g_last - g1);
+            const float d0 = -__expf(g0), d1 = -__expf(g1);  // factor of S k in R = v - e^g (S k)
             const float el = __expf(g_last);
-            if (c == 40 && lane == 0) GDN_STAMP_ANY(20);
             mbar_wait_relaxed<200>(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
-            if (c == 40 && lane == 0) GDN_STAMP_ANY(21);
-            if (c == 40 && lane == 0) GDN_STAMP_ANY(23);
             float* gb = gate_buf(c);
             gb[lane] = e0;
             gb[lane + 32] = e1;
@@ -512,59 +492,54 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // warp-uniform issue: one elected lane arms the barrier and launches the loads
                 uint8_t* st = smem + s * L::kStage;
                 const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
-                const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kUnitBlockBytes;
-                // what the serial chain needs first (W for the first MMA, U for the pass that follows)
-                // goes first and on its own barrier; P, K, Q are not needed before the second MMA group
+                const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kZPBlockBytes;
+                // what the serial chain needs first (K for the first MMA, V for the pass that follows)
+                // goes first and on its own barrier; Z, PT, Q are not needed before the second MMA group
                 mbar_arrive_expect_tx_w(&bar_full[s], 2 * L::kTile);
-                bulk_load_w(st + L::kOffU, blk, 2 * L::kTile, &bar_full[s]);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffV + a * 8192, &tmV, &bar_full[s], a * 64, head, tok, batch);
                 if (emit_o) {
-                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kStage - 2 * L::kTile);
+                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile + kZPBlockBytes);
+                    bulk_load_w(st + L::kOffZ, blk, kZPBlockBytes, &bar_full2[s]);
 #pragma unroll
                     for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full2[s], a * 64, khead, tok, batch);
                 } else {
-                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile);  // no output: K is all the second group needs
+                    mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile);  // no output: Z is all the second group needs
+                    bulk_load_w(st + L::kOffZ, blk, L::kTile, &bar_full2[s]);
                 }
-#pragma unroll
-                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full2[s], a * 64, khead, tok, batch);
-                if (emit_o) bulk_load_w(st + L::kOffP, blk + 2 * L::kTile, kChunk * kChunk * 2, &bar_full2[s]);
-                if (c == 40 && lane == 0) GDN_STAMP_ANY(22);
             }
         }
     } else if (warp == 13) {
         // =============================================================== MMA issuer
         // The whole warp runs this loop with warp-uniform values; one elected lane issues.
         {
-            constexpr uint32_t id_sw = make_idesc_bf16(128, 64, false, false, true);
             constexpr uint32_t id_sq = make_idesc_bf16(128, 64, false, false);
             constexpr uint32_t id_ds = make_idesc_bf16(128, 128, false, true);
             // one base descriptor per tile and stage; K-steps are constant offsets from them
-            uint64_t dW[2], dQ[2], dK[2], dP[2];
+            uint64_t dK[2], dQ[2], dZ[2], dP[2];
 #pragma unroll
             for (int s = 0; s < 2; ++s) {
                 const uint32_t st = smem_u32(smem + s * L::kStage);
-                dW[s] = make_smem_desc_sw128(st + L::kOffW, 0, 1024);     // K-major B
+                dK[s] = make_smem_desc_sw128(st + L::kOffK, 0, 1024);     // K-major B
                 dQ[s] = make_smem_desc_sw128(st + L::kOffQ, 0, 1024);     // K-major B
-                dK[s] = make_smem_desc_sw128(st + L::kOffK, 8192, 1024);  // MN-major B
-                dP[s] = make_smem_desc_sw128(st + L::kOffP, 0, 1024);     // K-major B
+                dZ[s] = make_smem_desc_sw128(st + L::kOffZ, 8192, 1024);  // MN-major B
+                dP[s] = make_smem_desc_sw128(st + L::kOffPT, 0, 1024);    // K-major B
             }
             const uint32_t tS = tmem + kTmSbf, tD1 = tmem + kTmD1, tDS = tmem + kTmDS, tO2 = tmem + kTmO2;
-            const uint32_t tUa = tmem + kTmUnA, tUb = tmem + kTmUnB;
+            const uint32_t tR = tmem + kTmR;
             for (int c = 0; c < nchunks; ++c) {
                 const int s = c & 1;
                 const uint32_t par = static_cast<uint32_t>(c & 1);
-                const uint64_t w = dW[s], q = dQ[s], k = dK[s], pp = dP[s];
-                if (c == 40) GDN_STAMP_ANY(29);
+                const uint64_t k = dK[s], q = dQ[s], z = dZ[s], pp = dP[s];
                 mbar_wait(&bar_full[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
-                if (c == 40) GDN_STAMP_ANY(30);
-                if (c == 40) GDN_STAMP_ANY(31);
                 mbar_wait(bar_sbf, par, abort_flag);
                 tc_fence_after_sync();
-                if (c == 40) GDN_STAMP_ANY(32);
-                // D1 = -(S_bf W^T)
-                mma_ts_k128_w<false>(tD1, tS, w, id_sw);
+                // D1 = S_bf K^T
+                mma_ts_k128_w<false>(tD1, tS, k, id_sq);
                 mma_commit_w(bar_d1);
-                if (c == 40) GDN_STAMP_ANY(33);
                 // O1 = S_bf Q^T
                 mbar_wait(&bar_full2[s], static_cast<uint32_t>((c >> 1) & 1), abort_flag);
                 tc_fence_after_sync();
@@ -572,26 +547,21 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     const uint32_t tO1 = tmem + ((c & 1) ? kTmO1b : kTmO1a);
                     mma_ts_k128_w<false>(tO1, tS, q, id_sq);
                 }
-                if (c == 40) GDN_STAMP_ANY(34);
                 mbar_wait(bar_un, par, abort_flag);
                 tc_fence_after_sync();
-                if (c == 40) GDN_STAMP_ANY(35);
-                // dS = Un_b K
-                mma_ts_k64_w<false, 128>(tDS, tUb, k, id_ds);
+                // dS = R Z
+                mma_ts_k64_w<false, 128>(tDS, tR, z, id_ds);
                 mma_commit_w(bar_ds);
-                if (c == 40) GDN_STAMP_ANY(36);
-                // O2 = Un_a P^T (its accumulator must have been drained by the previous epilogue)
+                // O2 = R PT^T (its accumulator must have been drained by the previous epilogue)
                 if (emit_o) {
                     if (c > 0) {
                         mbar_wait(bar_ofree, static_cast<uint32_t>((c - 1) & 1), abort_flag);
                         tc_fence_after_sync();
                     }
-                    mma_ts_k64_w<false, 2>(tO2, tUa, pp, id_sq);
+                    mma_ts_k64_w<false, 2>(tO2, tR, pp, id_sq);
                     mma_commit_w(bar_o);
                 }
                 mma_commit_w(&bar_empty[s]);
-                if (c == 40) GDN_STAMP_ANY(37);
-                if (c == 41) GDN_STAMP_ANY(38);
             }
         }
     }

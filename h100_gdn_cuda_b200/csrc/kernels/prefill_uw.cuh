@@ -104,7 +104,21 @@ __device__ __forceinline__ void mma_block(float* d, const float* am, int lda, in
     b[1] = to_tf32(bm[(k0b + t + 4) * ldb + n0 + g]);
     mma_tf32(d, a, b);
 }
-// store -d (16x8) at [r0][n0]
+// d(rows 0-7 of the 16x8 tile) += A(8x8 at [r0][k0] of `am`) * B(8x8 at [k0b][n0] of `bm`): the upper half of
+// the warp MMA; lane (g, t) ends up with d[0], d[1] = rows g, columns 2t, 2t+1 of the product.
+__device__ __forceinline__ void mma_block8(float* d, const float* am, int lda, int r0, int k0, const float* bm,
+                                           int ldb, int k0b, int n0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t a[4], b[2];
+    a[0] = to_tf32(am[(r0 + g) * lda + k0 + t]);
+    a[1] = 0u;
+    a[2] = to_tf32(am[(r0 + g) * lda + k0 + t + 4]);
+    a[3] = 0u;
+    b[0] = to_tf32(bm[(k0b + t) * ldb + n0 + g]);
+    b[1] = to_tf32(bm[(k0b + t + 4) * ldb + n0 + g]);
+    mma_tf32(d, a, b);
+}
+// store sign * d (16x8) at [r0][n0]
 __device__ __forceinline__ void store_block(const float* d, float sign, float* m, int ld, int r0, int n0, int lane) {
     const int g = lane >> 2, t = lane & 3;
     *reinterpret_cast<float2*>(&m[(r0 + g) * ld + n0 + 2 * t]) = make_float2(sign * d[0], sign * d[1]);

@@ -209,8 +209,9 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * fp32 or bf16 gate, token-major beta; writes `out` (like v) and final_state.  The per-chunk
  * state tensor of the reference is never materialised.  `workspace` is caller-provided device
  * memory of at least gdn_chunked_forward_workspace_bytes(&shape) bytes, 256-byte aligned; its
- * contents need not be initialised and are garbage afterwards.  It holds one 40 KiB block per
- * 64-token chunk and v-head (U, W and the intra-chunk attention block) and, when few long padded
+ * contents need not be initialised and are garbage afterwards.  It holds one 24 KiB block per
+ * 64-token chunk and v-head (the WY/UT transform folded into a 64 x 128 and a 64 x 64 bf16
+ * matrix that the state kernel consumes) and, when few long padded
  * sequences are propagated in segments, three fp32 states (192 KiB) per (sequence, v-head) and
  * segment; packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the sequences ordered
  * by length: the state kernel takes the longest first when there are more (sequence, v-head)
@@ -246,19 +247,23 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  * ignored; inputs and outputs are passed as usual.
  *
  *   - Limit: gdn_chunked_forward_workspace_bytes(&args->shape) must not exceed
- *     GDN_STATIC_SCRATCH_BYTES (80 MiB + 8 KiB + 256 bytes).  The scratch holds U and W (512 bytes per
- *     token and v-head) and the intra-chunk attention blocks (8 KiB per 64-token chunk and
- *     v-head), so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
+ *     GDN_STATIC_SCRATCH_BYTES (48 MiB + 8 KiB + 256 bytes).  The scratch holds 24 KiB per 64-token
+ *     chunk and v-head (384 bytes per token and v-head),
+ *     so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
  *     tokens of 32 v-heads (less where long sequences of few heads add their segment states).
  *     Larger problems are refused with GDN_ERR_WORKSPACE and a message.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address; make that first
- *     call outside any stream capture.
+ *     call outside any stream capture.  With CUDA's lazy module loading that first call (or the
+ *     first gdn_chunked_forward on the device, which loads the same module) is also the moment
+ *     the array's memory is claimed on that device: a host that is about to hand all HBM to its
+ *     own pool should make one small warm-up call on each device before it does so, or the
+ *     first real call can fail for lack of memory.
  *   - All calls on a device share the one array and it keeps whatever the previous call
  *     left there.  Nothing in it has to start at zero (every element that is read has been
  *     written earlier in the same call), but two calls whose kernels overlap on the GPU -
  *     different streams, or different host threads - race on it: serialise them. */
-#define GDN_STATIC_SCRATCH_BYTES ((80u << 20) + 8192u + 256u)
+#define GDN_STATIC_SCRATCH_BYTES ((48u << 20) + 8192u + 256u)
 int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* args, gdn_stream_t stream);
 
 #ifdef __cplusplus

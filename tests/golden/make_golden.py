@@ -55,5 +55,51 @@ def main():
         print(name, "o", tuple(o.shape), "absmax", float(o.abs().max()))
 
 
+def branch_cases():
+    """Fixtures for the branches of the oracle that the plain recurrence above does not reach:
+    q/k L2 normalisation, per-token (step) states and the accepted-token cap.  The package's
+    normalisation kernel needs a GPU, so q and k are normalised here in float64 with the formula
+    the reference kernel uses (x * rsqrt(sum x^2 + 1e-6), sm90_bf16_gdn_recurrent.cuh:299,350)
+    and the package's naive recurrence runs on the normalised tensors; the fixture stores the RAW
+    q and k, so the oracle has to do the normalisation itself.  Step states come from calling the
+    naive recurrence one token at a time, each call starting from the state the previous returned."""
+    import fla
+    from fla.ops.gated_delta_rule.naive import naive_recurrent_gated_delta_rule as naive
+
+    def norm64(x):
+        x = x.double()
+        return (x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)).float()
+
+    # --- qk-norm, GQA, initial state, raw (un-normalised) bf16-rounded q and k
+    p = synthetic.prefill_inputs(2, 40, 2, 4, 64, seed=11, with_state=True, dtype=torch.bfloat16, normalize=False)
+    q, k = norm64(p["q"].float()).repeat_interleave(2, dim=2), norm64(p["k"].float()).repeat_interleave(2, dim=2)
+    s0 = p["state"].float().transpose(-1, -2).contiguous()
+    o, s = naive(q, k, p["v"].float(), p["beta"].float(), p["g"], initial_state=s0, output_final_state=True)
+    np.savez_compressed(os.path.join(HERE, "branch_qknorm_B2_T40_kh2_vh4_d64.npz"),
+                        q=p["q"].float().numpy(), k=p["k"].float().numpy(), v=p["v"].float().numpy(),
+                        beta=p["beta"].float().numpy(), g=p["g"].numpy(), state=p["state"].float().numpy(),
+                        o=o.numpy(), final_state=s.transpose(-1, -2).contiguous().numpy(),
+                        fla_version=np.array(fla.__version__))
+    print("branch_qknorm", tuple(o.shape), float(o.abs().max()))
+
+    # --- step states (speculative verify): B=3, T=6, token by token
+    p = synthetic.prefill_inputs(3, 6, 2, 2, 64, seed=12, with_state=True, dtype=torch.bfloat16)
+    st = p["state"].float().transpose(-1, -2).contiguous()
+    outs, steps = [], []
+    for t in range(6):
+        sl = slice(t, t + 1)
+        o, st = naive(p["q"].float()[:, sl], p["k"].float()[:, sl], p["v"].float()[:, sl], p["beta"].float()[:, sl],
+                      p["g"][:, sl], initial_state=st, output_final_state=True)
+        outs.append(o)
+        steps.append(st.transpose(-1, -2).contiguous())
+    np.savez_compressed(os.path.join(HERE, "branch_steps_B3_T6_h2_d64.npz"),
+                        q=p["q"].float().numpy(), k=p["k"].float().numpy(), v=p["v"].float().numpy(),
+                        beta=p["beta"].float().numpy(), g=p["g"].numpy(), state=p["state"].float().numpy(),
+                        o=torch.cat(outs, dim=1).numpy(), step_states=torch.stack(steps, dim=1).numpy(),
+                        fla_version=np.array(fla.__version__))
+    print("branch_steps", tuple(torch.stack(steps, dim=1).shape))
+
+
 if __name__ == "__main__":
     main()
+    branch_cases()

@@ -69,10 +69,10 @@ def test_struct_sizes_match_c(lib):
 
 
 def test_workspace_bytes(lib):
-    """Scratch of chunked_forward: 40 KB per (64-token chunk, v-head); for few long padded sequences
+    """Scratch of chunked_forward: 24 KB per (64-token chunk, v-head); for few long padded sequences
     three fp32 states per chain and segment on top (the segmented state propagation)."""
     from h100_gdn_cuda_b200 import api
-    unit = 2 * 64 * 128 * 2 + 64 * 64 * 2
+    unit = 64 * 128 * 2 + 64 * 64 * 2
     assert api.chunked_forward_workspace_bytes(4, 4096, 32) == 4 * 64 * 32 * unit + 256
     assert api.chunked_forward_workspace_bytes(1, 65, 2) == 2 * 2 * unit + 256        # ragged tail: whole chunks
     # packed mode counts chunks, not tokens; 256 bytes more hold the sequences ordered by length

@@ -13,7 +13,10 @@ from h100_gdn_cuda_b200 import synthetic
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "*.npz"))))
+PLAIN = sorted(f for f in glob.glob(os.path.join(GOLDEN, "*.npz")) if not os.path.basename(f).startswith("branch_"))
+
+
+@pytest.mark.parametrize("path", PLAIN)
 def test_oracle_matches_golden(path):
     z = np.load(path)
     t = {k: torch.from_numpy(z[k]) for k in z.files if k != "fla_version"}
@@ -24,7 +27,39 @@ def test_oracle_matches_golden(path):
 
 
 def test_golden_present():
-    assert len(glob.glob(os.path.join(GOLDEN, "*.npz"))) >= 3
+    assert len(PLAIN) >= 3
+
+
+def _load(name):
+    z = np.load(os.path.join(GOLDEN, name))
+    return {k: torch.from_numpy(z[k]) for k in z.files if k != "fla_version"}
+
+
+def test_oracle_qk_norm_matches_golden():
+    """The fixture holds RAW q, k and the outputs of the third-party recurrence on q, k normalised
+    by the generating script: the oracle's own normalisation branch has to reproduce them."""
+    t = _load("branch_qknorm_B2_T40_kh2_vh4_d64.npz")
+    o, s = O.recurrent_ref(t["q"], t["k"], t["v"], t["beta"], t["g"], t["state"], is_qk_norm=True)
+    assert (o - t["o"]).abs().max().item() < 2e-6
+    assert (s - t["final_state"]).abs().max().item() < 2e-6
+    # and without the flag the answer is a different one (the fixture does exercise the branch)
+    o_raw, _ = O.recurrent_ref(t["q"], t["k"], t["v"], t["beta"], t["g"], t["state"])
+    assert (o_raw - t["o"]).abs().max().item() > 1e-2
+
+
+def test_oracle_step_states_and_accept_cap_match_golden():
+    """Per-token states (the third-party recurrence called one token at a time) and the accepted-token
+    cap: the state after the accepted prefix is the step state of its last token."""
+    t = _load("branch_steps_B3_T6_h2_d64.npz")
+    o, steps = O.recurrent_ref(t["q"], t["k"], t["v"], t["beta"], t["g"], t["state"], store_step_state=True)
+    assert (o - t["o"]).abs().max().item() < 2e-6
+    assert (steps - t["step_states"]).abs().max().item() < 2e-6
+    acc = [2, 6, 1]
+    o_c, s_c = O.recurrent_ref(t["q"], t["k"], t["v"], t["beta"], t["g"], t["state"], num_accepted_tokens=acc)
+    for b, a in enumerate(acc):
+        assert (s_c[b] - t["step_states"][b, a - 1]).abs().max().item() < 2e-6
+        assert (o_c[b, :a] - t["o"][b, :a]).abs().max().item() < 2e-6
+        assert o_c[b, a:].abs().max().item() == 0 if a < 6 else True
 
 
 def test_known_answer_single_step():
