@@ -39,7 +39,8 @@ class RecurrentArgs(C.Structure):
     _fields_ = [("shape", Shape), ("q", TokenTensor), ("k", TokenTensor), ("v", TokenTensor),
                 ("out", TokenTensor), ("beta", TokenScalar), ("gate", TokenScalar),
                 ("state_in", State), ("state_out", State), ("num_accepted_tokens", C.c_void_p),
-                ("scale", C.c_float), ("is_qk_norm", C.c_int32), ("store_step_state", C.c_int32)]
+                ("scale", C.c_float), ("is_qk_norm", C.c_int32), ("store_step_state", C.c_int32),
+                ("gating_a", TokenScalar), ("gating_b", TokenScalar), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p)]
 
 
 class ComputeUWArgs(C.Structure):
@@ -64,7 +65,7 @@ class ChunkedArgs(C.Structure):
                 ("out", TokenTensor), ("beta", TokenScalar), ("gate", TokenScalar),
                 ("initial_state", State), ("final_state", State), ("scale", C.c_float),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("stage_events", C.POINTER(C.c_void_p))]
+                ("stage_events", C.POINTER(C.c_void_p)), ("is_qk_norm", C.c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/gdn_b200.h declares
@@ -73,6 +74,7 @@ SYMBOLS = {
     "gdn_last_error": (C.c_char_p, []),
     "gdn_version": (C.c_int, []),
     "gdn_device_status": (C.c_int, [C.c_int, C.POINTER(C.c_int)]),
+    "gdn_selftest_bounded_wait": (C.c_int, [C.c_int64, C.c_void_p]),
     "gdn_jit_compile": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_int)]),
     "gdn_fused_gating": (C.c_int, [C.c_void_p] * 6 + [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "gdn_chunk_local_cumsum": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int32,

@@ -176,15 +176,28 @@ def transpose_to_mn_major(input: torch.Tensor, alignment: int = 16) -> torch.Ten
 
 def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=None, cu_seqlens=None,
                       num_accepted_tokens=None, inference_mode: int = 0, is_qk_norm: bool = False,
-                      scale: Optional[float] = None, *, inplace_state: bool = False, _max_head_dim: int = 256):
+                      scale: Optional[float] = None, *, inplace_state: bool = False, gating=None,
+                      _max_head_dim: int = 256):
     """Token recurrence for decode / speculative verify / short prefill; python_api.cpp:107-122
     and csrc/apis/gdn_forward.cpp:134-206.
 
     Returns (output, new_state).  new_state is (B, vh, dv, dk), or one state per token
     ((B,T,vh,dv,dk) / (N,vh,dv,dk)) when inference_mode == SpecVerify.  `gate` may be bf16
-    or fp32 (or None for no decay).  With `inplace_state=True` (an extension) the new state
-    overwrites `initial_state`, which is returned."""
-    _require(beta is not None, "beta is required")
+    or fp32 (or None for no decay).  Extensions (keyword-only): with `inplace_state=True` the new
+    state overwrites `initial_state`, which is returned (its (dv, dk) blocks must be contiguous);
+    with `gating=(A_log, dt_bias, a, b)` the kernel computes beta = sigmoid(b) and
+    gate = -exp(A_log) * softplus(a + dt_bias) itself from the layer's raw projections (what
+    fused_gdn_gating would produce, without the extra launch or the bf16 rounding of its
+    outputs) and `beta` / `gate` must be None."""
+    if gating is not None:
+        _require(beta is None and gate is None, "pass either gating=(A_log, dt_bias, a, b) or beta/gate, not both")
+        g_A, g_dt, g_a, g_b = gating
+        _require(g_a.dtype == g_b.dtype == g_A.dtype == g_dt.dtype, "A_log, dt_bias, a, b must share a dtype")
+        _require(g_a.shape == g_b.shape and g_A.numel() >= g_a.shape[-1] and g_dt.numel() >= g_a.shape[-1],
+                 "gating: a and b are (B,T,vh) / (N,vh); A_log and dt_bias hold one entry per v-head")
+        g_A, g_dt = g_A.contiguous(), g_dt.contiguous()
+    else:
+        _require(beta is not None, "beta is required")
     for t, n in ((query, "query"), (key, "key"), (value, "value")):
         _cuda_bf16(t, n)
     varlen = cu_seqlens is not None
@@ -204,7 +217,10 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
         if s_in.shape[-1] != d_al or s_in.shape[-2] != dv_al:
             _require(not inplace_state, "in-place state needs head dims that are multiples of 64")
             s_in = torch.nn.functional.pad(s_in, (0, d_al - s_in.shape[-1], 0, dv_al - s_in.shape[-2]))
-        s_in = s_in if s_in.stride(-1) == 1 and s_in.stride(-2) == d_al else s_in.contiguous()
+        if not (s_in.stride(-1) == 1 and s_in.stride(-2) == d_al):
+            # a copy would silently break the in-place promise: the caller's tensor would never change
+            _require(not inplace_state, "inplace_state needs contiguous (dv, dk) blocks in initial_state")
+            s_in = s_in.contiguous()
     kh, vh = q.shape[-2], v.shape[-2]
     if varlen:
         batch, seq_len, total = cu_seqlens.numel() - 1, 0, q.shape[0]
@@ -227,6 +243,9 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
         _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen), _token_tensor(out, varlen),
         _token_scalar(beta, varlen), _token_scalar(gate, varlen), _state_desc(s_in), so_desc,
         _i32(num_accepted_tokens, "num_accepted_tokens"), float(scale), int(bool(is_qk_norm)), int(store_steps))
+    if gating is not None:
+        args.gating_a, args.gating_b = _token_scalar(g_a, varlen), _token_scalar(g_b, varlen)
+        args.A_log, args.dt_bias = g_A.data_ptr(), g_dt.data_ptr()
     cabi.check(cabi.load().gdn_recurrent_forward(C.byref(args), _stream()), "recurrent_forward")
     if dv_al != dv_in:
         out = out[..., :dv_in]
@@ -258,23 +277,28 @@ _PREFILL_D_MAX = 256  # chunked_forward takes head dims up to here (above 128: t
 
 
 def chunked_forward_workspace_bytes(batch: int, seq_len: int, num_v_heads: int, total_tokens: int = 0,
-                                    total_chunks: int = 0, packed: bool = False) -> int:
-    """Bytes of scratch `chunked_forward` needs for a problem of this size (head dim 128)."""
-    shape = cabi.Shape(batch, seq_len, total_tokens if packed else batch * seq_len, 1, num_v_heads, _PREFILL_D,
+                                    total_chunks: int = 0, packed: bool = False,
+                                    num_k_heads: Optional[int] = None) -> int:
+    """Bytes of scratch `chunked_forward` needs for a problem of this size (head dim 128).  Without
+    `num_k_heads` the figure is the upper bound num_k_heads = num_v_heads."""
+    kh = num_v_heads if num_k_heads is None else num_k_heads
+    shape = cabi.Shape(batch, seq_len, total_tokens if packed else batch * seq_len, kh, num_v_heads, _PREFILL_D,
                        _PREFILL_D, 1 if packed else None, None, None, total_chunks)
     return int(cabi.load().gdn_chunked_forward_workspace_bytes(C.byref(shape)))
 
 
 def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None, initial_state=None,
                     cu_seqlens=None, chunk_indices=None, cu_chunks=None, total_chunks: Optional[int] = None,
-                    *, _stage_events=None, _workspace=None):
+                    *, is_qk_norm: bool = False, _stage_events=None, _workspace=None):
     """Chunked (64-token) Gated DeltaNet prefill; python_api.cpp:47-60, csrc/apis/gdn_forward.cpp:18-132.
 
     query/key (B,T,kh,d) or (N,kh,d); value (B,T,vh,d) or (N,vh,d); beta bf16 and gate fp32
     (raw per-token log-decay, before any cumsum) shaped (B,T,vh) / (N,vh); initial_state
     (B|S, vh, d, d) bf16 or None.  Packed mode needs int32 cu_seqlens, chunk_indices and
     cu_chunks.  Returns (output shaped like value, final_state (B|S, vh, d, d)), both bf16.
-    The default scale is d ** -0.5 with d the caller's (unpadded) head dimension."""
+    The default scale is d ** -0.5 with d the caller's (unpadded) head dimension.
+    `is_qk_norm=True` (keyword-only extension; the reference lists it as future work) L2-normalises
+    q and k per head inside the kernels, as recurrent_forward does."""
     for t, n in ((query, "query"), (key, "key"), (value, "value")):
         _cuda_bf16(t, n)
     _require(gate is None or gate.dtype in (torch.float32, torch.bfloat16), "gate must be fp32 (or bf16)")
@@ -312,7 +336,7 @@ def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None
     args = cabi.ChunkedArgs(shape, _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen),
                             _token_tensor(out, varlen), _token_scalar(beta, varlen), _token_scalar(gate, varlen),
                             _state_desc(s_in), _state_desc(final), float(scale), ws.data_ptr(), ws_bytes,
-                            ev)
+                            ev, int(bool(is_qk_norm)))
     cabi.check(lib.gdn_chunked_forward(C.byref(args), _stream()), "chunked_forward")
     if d != D:
         out, final = out[..., :d], final[..., :d, :d]
@@ -330,7 +354,16 @@ def bf16_gdn_compute_u_w(k, v, u, w, beta, gate=None, compiled_dims: str = "t", 
         _cuda_bf16(t, n)
     varlen, batch, seq_len, total = _prefill_dims(k, v, cu_seqlens)
     d = k.shape[-1]
-    _require(d == _PREFILL_D and v.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    _require(0 < d <= _PREFILL_D and v.shape[-1] == d, "low-level chunked kernels need dk = dv <= %d" % _PREFILL_D)
+    if d != _PREFILL_D:
+        # the kernels are built for head dim 128: run on zero-padded copies (exact) and copy the results back
+        up, wp = torch.empty(*u.shape[:-1], _PREFILL_D, dtype=u.dtype, device=u.device), \
+            torch.empty(*w.shape[:-1], _PREFILL_D, dtype=w.dtype, device=w.device)
+        bf16_gdn_compute_u_w(_pad_last(k, _PREFILL_D), _pad_last(v, _PREFILL_D), up, wp, beta, gate, compiled_dims,
+                             cu_seqlens, chunk_indices)
+        u.copy_(up[..., :d])
+        w.copy_(wp[..., :d])
+        return
     beta, gate = _crop_tokens(beta, total if varlen else seq_len), _crop_tokens(gate, total if varlen else seq_len)
     tc = 0 if chunk_indices is None else chunk_indices.numel() // 2
     shape = _shape(batch, seq_len, total, k.shape[-2], v.shape[-2], d, d, cu_seqlens, chunk_indices, None, tc)
@@ -357,8 +390,21 @@ def bf16_chunked_seq_state_update(k, u, w, initial_state, state, final_state, ga
         _cuda_bf16(t, n)
     varlen, batch, seq_len, total = _prefill_dims(k, u, cu_seqlens)
     d = k.shape[-1]
-    _require(d == _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    _require(0 < d <= _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv <= %d" % _PREFILL_D)
     _require(state.is_contiguous(), "state must be contiguous")
+    if d != _PREFILL_D:
+        # as the reference's wrapper does (csrc/apis/gdn_forward.cpp:252-302): zero-padded copies, results copied back
+        D = _PREFILL_D
+        up = _pad_last(u, D)
+        sp = torch.empty(*state.shape[:-2], D, D, dtype=state.dtype, device=state.device)
+        fp = None if final_state is None else torch.empty(*final_state.shape[:-2], D, D, dtype=state.dtype, device=state.device)
+        bf16_chunked_seq_state_update(_pad_last(k, D), up, _pad_last(w, D), _pad_state(initial_state, D), sp, fp, gate,
+                                      compiled_dims, cu_seqlens, cu_chunks, total_chunks, chunk_size)
+        u.copy_(up[..., :d])
+        state.copy_(sp[..., :d, :d])
+        if final_state is not None:
+            final_state.copy_(fp[..., :d, :d])
+        return
     gate = _crop_tokens(gate, total if varlen else seq_len)
     if varlen:
         _require(cu_chunks is not None, "packed mode needs cu_chunks")
@@ -381,10 +427,17 @@ def bf16_gdn_chunked_compute_O(q, state, k, u, o, gate=None, scale: Optional[flo
         _cuda_bf16(t, n)
     varlen, batch, seq_len, total = _prefill_dims(q, u, cu_seqlens)
     d = q.shape[-1]
-    _require(d == _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv = %d" % _PREFILL_D)
+    _require(0 < d <= _PREFILL_D and u.shape[-1] == d, "low-level chunked kernels need dk = dv <= %d" % _PREFILL_D)
     _require(state.is_contiguous(), "state must be contiguous")
     if scale is None:
         scale = 1.0 / math.sqrt(d)
+    if d != _PREFILL_D:
+        D = _PREFILL_D
+        op = torch.empty(*o.shape[:-1], D, dtype=o.dtype, device=o.device)
+        bf16_gdn_chunked_compute_O(_pad_last(q, D), _pad_state(state, D).contiguous(), _pad_last(k, D), _pad_last(u, D), op,
+                                   gate, scale, compiled_dims, cu_seqlens, chunk_indices, cu_chunks, chunk_size)
+        o.copy_(op[..., :d])
+        return
     gate = _crop_tokens(gate, total if varlen else seq_len)
     tc = 0
     if varlen:

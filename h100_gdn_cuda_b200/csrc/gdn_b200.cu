@@ -7,6 +7,8 @@
 #include "kernels/helpers.cuh"
 #include "kernels/recurrent.cuh"
 
+#include <atomic>
+
 namespace gdn {
 
 static __device__ int g_status_word;
@@ -14,6 +16,14 @@ static __device__ int g_status_word;
 static std::mutex g_dev_mutex;
 static DeviceInfo g_devices[64];
 static std::string g_library_root, g_cuda_home;
+// Environment switches of the recurrent path, read when the library is first used and again by
+// every gdn_init() (never on the launch path): GDN_REC_RING_MIN (tuning aid: token count above
+// which the multi-token instance is used), GDN_JIT_RECURRENT (test aid: force the run-time compiler).
+static std::atomic<int> g_ring_min{-1}, g_force_jit{-1};
+static void read_env_switches() {
+    g_ring_min.store(jit::env_int("GDN_REC_RING_MIN", kRecTokRingMin));
+    g_force_jit.store(jit::env_int("GDN_JIT_RECURRENT", 0));
+}
 
 int get_device_info(DeviceInfo** out) {
     int dev = 0;
@@ -44,6 +54,24 @@ const std::string& cuda_home() { return g_cuda_home; }
 }  // namespace gdn
 
 using namespace gdn;
+
+// ------------------------------------------------------------------ self-test of the bounded waits
+// One warp waits, with the given cycle limit, on an mbarrier that nothing ever arrives on.  The
+// wait gives up, the kernel records status 7 and returns: the same path a product kernel takes
+// when a copy or an MMA never completes, exercised without any fault.
+__global__ void gdn_selftest_wait_kernel(long long limit_cycles, int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(&bar, 1);
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = ptx::mbar_wait_limit(&bar, 0, &abort_flag, limit_cycles);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!ok || abort_flag) && status) atomicExch(status, 7);
+}
 
 // ------------------------------------------------------------------ recurrent
 template <int DK, bool kRing>
@@ -100,6 +128,7 @@ int gdn_init(const char* library_root, const char* cuda_home) {
     g_library_root = library_root ? library_root : "";
     g_cuda_home = cuda_home ? cuda_home : "";
     jit::set_roots(g_library_root, g_cuda_home);
+    read_env_switches();
     return GDN_OK;
 }
 
@@ -122,6 +151,16 @@ int gdn_device_status(int device, int* status_out) {
     }
     if (device != cur) cudaSetDevice(cur);
     return rc;
+}
+
+int gdn_selftest_bounded_wait(int64_t limit_cycles, gdn_stream_t stream) {
+    GDN_REQUIRE(limit_cycles > 0 && limit_cycles <= 1000000000ll,
+                "gdn_selftest_bounded_wait: limit must be between 1 and 1e9 cycles (got %lld)", (long long)limit_cycles);
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    gdn_selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, d->status);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
 }
 
 // ------------------------------------------------------------------ helpers
@@ -221,9 +260,16 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     if (int rc = check_token_tensor(a->k, "k", s.head_dim_k)) return rc;
     if (int rc = check_token_tensor(a->v, "v", s.head_dim_v)) return rc;
     if (int rc = check_token_tensor(a->out, "out", s.head_dim_v)) return rc;
-    GDN_REQUIRE(a->beta.ptr != nullptr, "gdn_recurrent_forward: beta is NULL");
-    GDN_REQUIRE(a->beta.dtype == GDN_BF16 || a->beta.dtype == GDN_F32, "beta dtype must be bf16 or f32");
-    GDN_REQUIRE(!a->gate.ptr || a->gate.dtype == GDN_BF16 || a->gate.dtype == GDN_F32, "gate dtype must be bf16 or f32");
+    const bool fused_gating = a->gating_a.ptr != nullptr;
+    if (fused_gating) {
+        GDN_REQUIRE(a->gating_b.ptr && a->A_log && a->dt_bias, "gdn_recurrent_forward: fused gating needs a, b, A_log and dt_bias");
+        GDN_REQUIRE((a->gating_a.dtype == GDN_BF16 || a->gating_a.dtype == GDN_F32) && a->gating_b.dtype == a->gating_a.dtype,
+                    "gdn_recurrent_forward: gating inputs must share one dtype, bf16 or f32");
+    } else {
+        GDN_REQUIRE(a->beta.ptr != nullptr, "gdn_recurrent_forward: beta is NULL");
+        GDN_REQUIRE(a->beta.dtype == GDN_BF16 || a->beta.dtype == GDN_F32, "beta dtype must be bf16 or f32");
+        GDN_REQUIRE(!a->gate.ptr || a->gate.dtype == GDN_BF16 || a->gate.dtype == GDN_F32, "gate dtype must be bf16 or f32");
+    }
     GDN_REQUIRE(a->state_out.ptr != nullptr, "gdn_recurrent_forward: state_out is NULL");
     GDN_REQUIRE(aligned16(a->state_out.ptr) && a->state_out.stride_seq % 8 == 0 && a->state_out.stride_head % 8 == 0,
                 "state_out must be 16-byte aligned with strides that are multiples of 8");
@@ -241,10 +287,17 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.k = (const __nv_bfloat16*)a->k.ptr; p.k_sb = a->k.stride_batch; p.k_st = a->k.stride_token; p.k_sh = a->k.stride_head;
     p.v = (const __nv_bfloat16*)a->v.ptr; p.v_sb = a->v.stride_batch; p.v_st = a->v.stride_token; p.v_sh = a->v.stride_head;
     p.out = (__nv_bfloat16*)a->out.ptr; p.o_sb = a->out.stride_batch; p.o_st = a->out.stride_token; p.o_sh = a->out.stride_head;
-    p.beta = a->beta.ptr; p.beta_f32 = a->beta.dtype == GDN_F32;
-    p.beta_sb = a->beta.stride_batch; p.beta_st = a->beta.stride_token; p.beta_sh = a->beta.stride_head;
-    p.gate = a->gate.ptr; p.gate_f32 = a->gate.dtype == GDN_F32;
-    p.gate_sb = a->gate.stride_batch; p.gate_st = a->gate.stride_token; p.gate_sh = a->gate.stride_head;
+    // with fused gating the kernel reads the raw projections b and a where it would read beta and the gate
+    const GdnTokenScalar& sb = fused_gating ? a->gating_b : a->beta;
+    const GdnTokenScalar& sg = fused_gating ? a->gating_a : a->gate;
+    p.beta = sb.ptr; p.beta_f32 = sb.dtype == GDN_F32;
+    p.beta_sb = sb.stride_batch; p.beta_st = sb.stride_token; p.beta_sh = sb.stride_head;
+    p.gate = sg.ptr; p.gate_f32 = sg.dtype == GDN_F32;
+    p.gate_sb = sg.stride_batch; p.gate_st = sg.stride_token; p.gate_sh = sg.stride_head;
+    p.fused_gating = fused_gating;
+    p.gating_param_f32 = fused_gating && a->gating_a.dtype == GDN_F32;
+    p.A_log = a->A_log;
+    p.dt_bias = a->dt_bias;
     p.state_in = (const __nv_bfloat16*)a->state_in.ptr; p.si_ss = a->state_in.stride_seq; p.si_sh = a->state_in.stride_head;
     p.state_out = (__nv_bfloat16*)a->state_out.ptr; p.so_ss = a->state_out.stride_seq; p.so_sh = a->state_out.stride_head;
     p.cu_seqlens = s.cu_seqlens;
@@ -260,10 +313,12 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     
-    const int ring_min = jit::env_int("GDN_REC_RING_MIN", kRecTokRingMin);  // tuning aid
+    if (g_ring_min.load(std::memory_order_relaxed) < 0) read_env_switches();
+    const int ring_min = g_ring_min.load(std::memory_order_relaxed);
+    const int force_jit = g_force_jit.load(std::memory_order_relaxed);
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
                                    : (s.seq_len > ring_min);
-    if (jit::env_int("GDN_JIT_RECURRENT", 0)) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
+    if (force_jit) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
     switch (s.head_dim_k) {
         case 64: return launch_recurrent<64>(p, d->sms, st, ring);
         case 128: return launch_recurrent<128>(p, d->sms, st, ring);

@@ -72,6 +72,13 @@ ChunkMap chunk_map(const GdnShape& s) {
 int num_chunks(const GdnShape& s) {
     return s.cu_seqlens ? s.total_chunks : s.batch * ((s.seq_len + kChunk - 1) / kChunk);
 }
+// States are read and written with 16-byte accesses.
+int check_state(const GdnState& t, const char* name) {
+    if (!t.ptr) return GDN_OK;
+    GDN_REQUIRE(aligned16(t.ptr) && t.stride_seq % 8 == 0 && t.stride_head % 8 == 0,
+                "%s must be 16-byte aligned with strides that are multiples of 8 elements", name);
+    return GDN_OK;
+}
 int check_scalar(const GdnTokenScalar& t, const char* name, bool required) {
     if (!t.ptr) {
         GDN_REQUIRE(!required, "%s is NULL", name);
@@ -89,25 +96,15 @@ int set_smem(K kernel, int bytes) {
 
 int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& v, const GdnTokenTensor& u,
               const GdnTokenTensor& w, const GdnTokenScalar& beta, const GdnTokenScalar& gate, bool gate_is_raw,
-              DeviceInfo* d, cudaStream_t st, const GdnTokenTensor* q = nullptr, void* blocks = nullptr,
-              float p_scale = 1.f) {
-    // With q (the whole-layer path) U, W and P go to `blocks` (one contiguous block per unit) and
-    // u / w are not used; without it (the low-level wrapper) U and W go to the caller's tensors.
+              DeviceInfo* d, cudaStream_t st) {
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
-    CUtensorMap tmK, tmV, tmQ, tmUo, tmWo;
+    CUtensorMap tmK, tmV, tmUo, tmWo;
     if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
     if (int rc = make_token_map(&tmV, v, s, s.num_v_heads, "v")) return rc;
-    if (q) {
-        if (int rc = make_token_map(&tmQ, *q, s, s.num_k_heads, "q")) return rc;
-        tmUo = tmK;
-        tmWo = tmK;
-    } else {
-        if (int rc = make_token_map(&tmUo, u, s, s.num_v_heads, "u")) return rc;
-        if (int rc = make_token_map(&tmWo, w, s, s.num_v_heads, "w")) return rc;
-        tmQ = tmK;
-    }
+    if (int rc = make_token_map(&tmUo, u, s, s.num_v_heads, "u")) return rc;
+    if (int rc = make_token_map(&tmWo, w, s, s.num_v_heads, "w")) return rc;
     UWParams p{};
     p.map = chunk_map(s);
     p.beta = scalar_view(beta);
@@ -119,24 +116,17 @@ int launch_uw(const GdnShape& s, const GdnTokenTensor& k, const GdnTokenTensor& 
     p.vh = s.num_v_heads;
     p.num_chunks = nc;
     p.status = d->status;
-    p.blocks = static_cast<uint8_t*>(blocks);
-    p.p_scale = p_scale;
     constexpr int smem = UWSmem<kD>::kBytes;
     const int grid = uw_grid(static_cast<long long>(nc) * s.num_v_heads, d->sms);
-    if (q) {
-        if (int rc = set_smem(gdn_uw_kernel<kD, true>, smem)) return rc;
-        gdn_uw_kernel<kD, true><<<grid, 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
-    } else {
-        if (int rc = set_smem(gdn_uw_kernel<kD, false>, smem)) return rc;
-        gdn_uw_kernel<kD, false><<<grid, 128, smem, st>>>(tmK, tmV, tmQ, tmUo, tmWo, p);
-    }
+    if (int rc = set_smem(gdn_uw_kernel<kD>, smem)) return rc;
+    gdn_uw_kernel<kD><<<grid, 128, smem, st>>>(tmK, tmV, tmUo, tmWo, p);
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
 
 // Chunk-parallel stage of the whole-layer path: Z and PT of every (chunk, v-head) into `blocks`.
 int launch_zp(const GdnShape& s, const GdnTokenTensor& q, const GdnTokenTensor& k, const GdnTokenScalar& beta,
-              const GdnTokenScalar& gate, void* blocks, float p_scale, DeviceInfo* d, cudaStream_t st) {
+              const GdnTokenScalar& gate, void* blocks, float* norms, float p_scale, DeviceInfo* d, cudaStream_t st) {
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     CUtensorMap tmK, tmQ;
@@ -148,14 +138,20 @@ int launch_zp(const GdnShape& s, const GdnTokenTensor& q, const GdnTokenTensor& 
     p.gate = scalar_view(gate);
     p.blocks = static_cast<uint8_t*>(blocks);
     p.p_scale = p_scale;
+    p.norms = norms;
     p.kh = s.num_k_heads;
     p.vh = s.num_v_heads;
     p.num_chunks = nc;
     p.status = d->status;
     constexpr int smem = ZPSmem::kBytes;
-    if (int rc = set_smem(gdn_zp_kernel, smem)) return rc;
     const int grid = zp_grid(static_cast<long long>(nc) * s.num_k_heads, d->sms);
-    gdn_zp_kernel<<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
+    if (norms) {
+        if (int rc = set_smem(gdn_zp_kernel<true>, smem)) return rc;
+        gdn_zp_kernel<true><<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
+    } else {
+        if (int rc = set_smem(gdn_zp_kernel<false>, smem)) return rc;
+        gdn_zp_kernel<false><<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
+    }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
@@ -199,6 +195,8 @@ int gdn_seq_state_update(const GdnSeqStateArgs* a, gdn_stream_t stream) {
     if (int rc = check_token_tensor(a->u, "u", kD)) return rc;
     if (int rc = check_token_tensor(a->w, "w", kD)) return rc;
     if (int rc = check_scalar(a->gate_cumsum, "gate", false)) return rc;
+    if (int rc = check_state(a->initial_state, "initial_state")) return rc;
+    if (int rc = check_state(a->final_state, "final_state")) return rc;
     GDN_REQUIRE(a->chunk_states != nullptr, "gdn_seq_state_update: chunk_states is NULL");
     GDN_REQUIRE(aligned16(a->chunk_states), "chunk_states must be 16-byte aligned");
     GDN_REQUIRE(!s.cu_seqlens || s.cu_chunks, "gdn_seq_state_update: packed mode needs cu_chunks");
@@ -303,10 +301,15 @@ static int chunked_forward_wide(const GdnChunkedArgs* a, gdn_stream_t stream) {
     r.state_in = a->initial_state;
     r.state_out = a->final_state;
     r.scale = a->scale;
+    r.is_qk_norm = a->is_qk_norm;
     if (int rc = gdn_recurrent_forward(&r, stream)) return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));
     return GDN_OK;
 }
+
+// Workspace layout of gdn_chunked_forward: [Z, PT blocks][q/k norm factors][segment states | sequence order]
+static size_t ws_blocks_bytes(size_t chunks, int vh) { return (chunks * static_cast<size_t>(vh) * kZPBlockBytes + 255) / 256 * 256; }
+static size_t ws_norms_bytes(size_t chunks, int kh) { return (chunks * static_cast<size_t>(kh) * 128 * sizeof(float) + 255) / 256 * 256; }
 
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
@@ -315,7 +318,7 @@ size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
     // one block of Z (64 x 128 bf16) and PT (64 x 64 bf16) per (chunk, v-head); for a
     // segmented run (few long padded sequences) three fp32 states per chain and segment on top
-    size_t bytes = chunks * static_cast<size_t>(s->num_v_heads) * kZPBlockBytes + 256;
+    size_t bytes = ws_blocks_bytes(chunks, s->num_v_heads) + ws_norms_bytes(chunks, s->num_k_heads) + 256;
     if (!s->cu_seqlens) {
         const long long chains = static_cast<long long>(s->batch) * s->num_v_heads;
         const SegmentPlan plan = prefill_segments(chains, (s->seq_len + kChunk - 1) / kChunk, false);
@@ -338,6 +341,8 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     if (int rc = check_token_tensor(a->out, "out", kD)) return rc;
     if (int rc = check_scalar(a->beta, "beta", true)) return rc;
     if (int rc = check_scalar(a->gate, "gate", false)) return rc;
+    if (int rc = check_state(a->initial_state, "initial_state")) return rc;
+    if (int rc = check_state(a->final_state, "final_state")) return rc;
     GDN_REQUIRE(s.num_v_heads <= 65535, "too many heads");
     const size_t need = gdn_chunked_forward_workspace_bytes(&s);
     if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
@@ -358,7 +363,11 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         }
         return GDN_OK;
     }
-    if (int rc = launch_zp(s, a->q, a->k, a->beta, a->gate, a->workspace, a->scale, d, st)) return rc;
+    uint8_t* const ws = static_cast<uint8_t*>(a->workspace);
+    const size_t nchunks = static_cast<size_t>(num_chunks(s));
+    float* const norms = a->is_qk_norm ? reinterpret_cast<float*>(ws + ws_blocks_bytes(nchunks, s.num_v_heads)) : nullptr;
+    uint8_t* const ws_extra = ws + ws_blocks_bytes(nchunks, s.num_v_heads) + ws_norms_bytes(nchunks, s.num_k_heads);
+    if (int rc = launch_zp(s, a->q, a->k, a->beta, a->gate, a->workspace, norms, a->scale, d, st)) return rc;
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
 
     {
@@ -382,14 +391,14 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         p.scale = a->scale;
         p.status = d->status;
         p.blocks = static_cast<const uint8_t*>(a->workspace);
+        p.norms = norms;
         constexpr int smem = FusedSmem::kBytes;
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
         const long long chains = static_cast<long long>(s.batch) * s.num_v_heads;
         const SegmentPlan plan = prefill_segments(chains, (s.seq_len + kChunk - 1) / kChunk, packed);
         if (packed && s.batch > 1 && s.batch <= kMaxOrderedSeqs && chains > d->sms) {
             // more chains than SMs and unequal lengths: dispatch the longest sequences first
-            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kZPBlockBytes;
-            int* order = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256);
+            int* order = reinterpret_cast<int*>(ws_extra);
             gdn_seq_order_kernel<<<(s.batch + 127) / 128, 128, 0, st>>>(s.cu_seqlens, s.batch, order);
             GDN_CUDA(cudaGetLastError());
             p.seq_order = order;
@@ -400,9 +409,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             GDN_CUDA(cudaGetLastError());
         } else {
             // composite transitions of all segments, their start states, then all segments at once
-            const size_t blocks_bytes = static_cast<size_t>(num_chunks(s)) * s.num_v_heads * kZPBlockBytes;
-            uint8_t* extra = static_cast<uint8_t*>(a->workspace) + ((blocks_bytes + 255) / 256) * 256;
-            float* seg_mn = reinterpret_cast<float*>(extra);
+            float* seg_mn = reinterpret_cast<float*>(ws_extra);
             float* seg_start = seg_mn + static_cast<size_t>(chains) * plan.num_segments * 2 * kD * kD;
             p.seg_chunks = plan.seg_chunks;
             p.num_segments = plan.num_segments;

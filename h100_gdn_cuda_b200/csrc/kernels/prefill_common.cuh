@@ -7,49 +7,6 @@ namespace gdn {
 
 constexpr int kChunk = 64;
 
-// Optional phase timing for kernel development: compiled in only with -DGDN_PHASE_TIMING.
-// CTA (0,0) writes clock64() stamps to a global buffer.
-#ifdef GDN_PHASE_TIMING
-__device__ long long g_phase_stamps[64];
-__device__ __forceinline__ long long gdn_clock_ordered() {
-    long long t;
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
-    return t;
-}
-#ifndef GDN_STAMP_BX
-#define GDN_STAMP_BX 0
-#define GDN_STAMP_BY 0
-#endif
-#define GDN_STAMP(i)                                                                  \
-    do {                                                                              \
-        if (blockIdx.x == GDN_STAMP_BX && blockIdx.y == GDN_STAMP_BY && threadIdx.x == 0)              \
-            g_phase_stamps[i] = gdn_clock_ordered();                                                  \
-    } while (0)
-#define GDN_STAMP_IF(cond, i)                                                   \
-    do {                                                                        \
-        if ((cond) && threadIdx.x == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
-    } while (0)
-#define GDN_STAMP_ANY(i)                                                   \
-    do {                                                                  \
-        if (blockIdx.x == 0 && blockIdx.y == 0) g_phase_stamps[i] = gdn_clock_ordered(); \
-    } while (0)
-#else
-#define GDN_STAMP(i) \
-    do {             \
-    } while (0)
-#define GDN_STAMP_IF(cond, i) \
-    do {                      \
-    } while (0)
-#define GDN_STAMP_ANY(i) \
-    do {                 \
-    } while (0)
-#endif
-
-// Scratch of gdn_chunked_forward: one contiguous block per (global chunk, v-head) unit, laid out
-// exactly as the shared-memory images the state kernel wants (128-byte-swizzled 64 x 64 atoms):
-// U (16 KB), W (16 KB), P (8 KB).  One untiled bulk copy moves a whole block in either direction.
-constexpr int kUnitBlockBytes = 2 * kChunk * 128 * 2 + kChunk * kChunk * 2;
-
 // Scratch of the whole-layer path since the WY/UT transform was folded into the recurrence (see
 // prefill_zp.cuh): per (global chunk, v-head) unit Z (64 x 128 bf16 as two 64 x 64 swizzled atoms, the
 // shared-memory image of an MN-major B operand) and then PT (64 x 64, one atom).

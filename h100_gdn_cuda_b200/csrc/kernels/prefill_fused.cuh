@@ -41,6 +41,9 @@ struct FusedParams {
     float scale;
     int* status;
     const uint8_t* blocks;  // Z, PT of every (global chunk, v-head): kZPBlockBytes each
+    // q/k L2 normalisation: NULL, or per (global chunk, k-head) 64 inverse key norms then 64 inverse query
+    // norms (written by gdn_zp_kernel); they enter through the two per-token factors of a chunk
+    const float* norms;
     // Segmented runs (padded mode, few long sequences; see gdn_chunked_forward).  The state obeys
     // S' = S M_c + N_c per chunk, so a segment of chunks has a composite (M, N) as well.
     //   mode 0: one CTA walks the whole sequence (blockIdx.z = 0).
@@ -464,6 +467,14 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             ra0 = rb0;
             ra1 = rb1;
             load_raw(c + 2, rb0, rb1);
+            float rk0 = 1.f, rk1 = 1.f, rq0 = 1.f, rq1 = 1.f;
+            if (p.norms) {  // requested here, used after the wait for a free stage
+                const float* nr = p.norms + (static_cast<size_t>(gchunk0 + c) * p.kh + khead) * 128;
+                rk0 = __ldg(nr + lane);
+                rk1 = __ldg(nr + 32 + lane);
+                rq0 = __ldg(nr + 64 + lane);
+                rq1 = __ldg(nr + 96 + lane);
+            }
             // chunk-local cumulative gate
 #pragma unroll
             for (int m = 1; m < 32; m <<= 1) {
@@ -482,10 +493,10 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             const float el = __expf(g_last);
             mbar_wait_relaxed<200>(&bar_empty[s], static_cast<uint32_t>(((c >> 1) + 1) & 1), abort_flag);
             float* gb = gate_buf(c);
-            gb[lane] = e0;
-            gb[lane + 32] = e1;
-            gb[64 + lane] = d0;
-            gb[64 + lane + 32] = d1;
+            gb[lane] = e0 * rq0;
+            gb[lane + 32] = e1 * rq1;
+            gb[64 + lane] = d0 * rk0;
+            gb[64 + lane + 32] = d1 * rk1;
             if (lane == 0) gb[128] = el;
             __syncwarp();
             {

@@ -210,7 +210,6 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         const long long rem = seq_tokens - static_cast<long long>(c) * kChunk;
         const int n = rem < kChunk ? static_cast<int>(rem) : kChunk;
 
-        if (c == 2) GDN_STAMP(20);
         if (tid == 0 && c + 1 < nchunks) issue_loads(c + 1);
         if (kEmitH) {
             store_state_global(p.chunk_states + (static_cast<long long>(gchunk0 + c) * p.vh + head) * D * D);
@@ -247,10 +246,8 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         const float eg_last = sEg[n - 1];
         __syncthreads();
 
-        if (c == 2) GDN_STAMP(21);
         // ---- first wave of MMAs
         mbar_wait(&bar_full[stage], static_cast<uint32_t>((c >> 1) & 1), &abort_flag);
-        if (c == 2) GDN_STAMP(22);
         if (tid == 0) {
             tc_fence_after_sync();
             if (kComputeO) {
@@ -289,7 +286,6 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         }
         __syncwarp();
 
-        if (c == 2) GDN_STAMP(23);
         // ---- P = tril(Q K^T .* e^{g_i - g_j}) -> bf16 K-major tile
         if (kComputeO) {
             mbar_wait(&bar_a, par, &abort_flag);
@@ -319,10 +315,8 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
             fence_proxy_async_smem();
         }
 
-        if (c == 2) GDN_STAMP(24);
         // ---- U_new^T: mask rows past the end, make the two bf16 operand copies
         mbar_wait(&bar_b, par, &abort_flag);
-        if (c == 2) GDN_STAMP(25);
         tc_fence_after_sync();
         {
             uint32_t r[32];
@@ -354,7 +348,6 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         tc_fence_before_sync();
         __syncthreads();
 
-        if (c == 2) GDN_STAMP(26);
         // ---- second wave of MMAs
         if (tid == 0) {
             tc_fence_after_sync();
@@ -377,10 +370,8 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         }
         __syncwarp();
 
-        if (c == 2) GDN_STAMP(27);
         // ---- S <- e^{g_L} S + dS ; refresh the bf16 operand copy
         mbar_wait(&bar_c, par, &abort_flag);
-        if (c == 2) GDN_STAMP(28);
         tc_fence_after_sync();
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
@@ -392,11 +383,9 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
         }
         store_state_operand();
 
-        if (c == 2) GDN_STAMP(29);
         // ---- O = scale (e^{g_i} O1 + O2), transposed through shared memory
         if (kComputeO) {
             mbar_wait(&bar_d, par, &abort_flag);
-        if (c == 2) GDN_STAMP(30);
             tc_fence_after_sync();
             uint32_t r1[32], r2[32];
             tmem_ld32(tmem + kTmO1 + tm_lane + 32 * hf, r1);
@@ -409,10 +398,8 @@ __global__ void __launch_bounds__(256, 1) gdn_seq_kernel(const __grid_constant__
                 *reinterpret_cast<__nv_bfloat16*>(sO + stage_off<D>(i, row >> 3) + (row & 7) * 2) = __float2bfloat16(o);
             }
             __syncthreads();
-        if (c == 2) GDN_STAMP(31);
             store_staged_tile<D, 256>(sO, p.out, batch, tok0, head, n, tid);
         }
-        if (c == 2) GDN_STAMP(32);
         tmem_wait_st();
         tc_fence_before_sync();
         __syncthreads();

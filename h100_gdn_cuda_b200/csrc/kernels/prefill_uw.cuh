@@ -5,24 +5,24 @@
 // sm90_bf16_compute_u_w (gdn_cuda/include/gdn_cuda/kernels/sm90_bf16_gdn_compute_u_w.cuh:153-667),
 // using the canonical W (gate folded in before the solve).
 //
+// This is the stage kernel behind the low-level wrapper gdn_compute_u_w; the whole-layer path
+// (gdn_chunked_forward) folds the transform into the recurrence instead (prefill_zp.cuh).
 // Persistent CTAs of 128 threads (four per SM) walk the (chunk, v-head) units.  tcgen05 tensor
 // cores do the big contractions with the TMA-loaded tiles used as they are:
-//   K K^T, Q K^T : M=64 N=32 K=D MMAs, one accumulator per issuing warp (columns 0-31 and 32-63 of
-//                each product); the two halves of a product are interleaved in the same
-//                tensor-memory columns (lanes +0 and +16 of every 32-lane quarter), so one 32-lane
-//                load hands every thread of a warp half a row;
+//   K K^T      : M=64 N=32 K=D MMAs, one accumulator per issuing warp (columns 0-31 and 32-63 of
+//                the product), interleaved in the same tensor-memory columns (lanes +0 and +16 of
+//                every 32-lane quarter), so one 32-lane load hands every thread of a warp half a row;
 //   U = T V    : M=64 N=D K=64, A = T (bf16, written by the CTA), B = the V tile read MN-major;
 //   W = T' K   : M=64 N=D K=64, A = T' = X diag(beta e^g), B = the K tile read MN-major;
 //                U and W are interleaved the same way (U in lanes +0, W in lanes +16).
-// One pass over the first accumulators forms A (fp32, shared memory) and, with kWithP, the
-// intra-chunk attention block P (bf16) with one ex2 per element.  The unit-lower-triangular
+// One pass over the first accumulators forms A (fp32, shared memory) with one ex2 per element.
+// The unit-lower-triangular
 // inverse: the 16x16 diagonal blocks in fp32 by forward substitution (one column per thread),
 // then two levels of recursive doubling (16 -> 32 -> 64) whose block products use warp-level
 // tensor-core MMAs on TF32 operands with fp32 accumulation, all in place.
-// Tensor memory: D columns.  Shared memory (52 KB): the K tile (later the U staging tile), a
-// second tile buffer (Q, then the staged P, then V, then the W staging tile) and A (later T, T').
-// With kWithP (the whole-layer path) U, W, P leave as one contiguous unit block by bulk copies;
-// without it U and W go to the caller's token-major tensors.
+// Tensor memory: D columns.  Shared memory (52 KB): the K tile (later the U staging tile), the V
+// tile (later the W staging tile) and A (later T, T').  U and W go to the caller's token-major
+// tensors through tiled TMA stores (row-predicated stores for a ragged packed tail).
 #pragma once
 #include <cuda.h>
 
@@ -36,8 +36,6 @@ struct UWParams {
     ScalarView gate;      // ptr == NULL: no decay
     int gate_is_raw;      // 1: per-token log-decay (cumsum taken here); 0: already chunk-local cumsum
     TokenView u, w;
-    uint8_t* blocks;       // kWithP: one kUnitBlockBytes block per (global chunk, v-head), see below
-    float p_scale;         // kWithP: factor folded into P (the output scale)
     int kh, vh;
     int num_chunks;
     int* status;
@@ -126,13 +124,9 @@ __device__ __forceinline__ void store_block(const float* d, float sign, float* m
 }
 }  // namespace uw
 
-// With kWithP the kernel also produces the intra-chunk attention block the output stage needs,
-//     P = tril(Q K^T .* exp(g_i - g_j))   (bf16, 64x64 per unit),
-// from a Q tile that is loaded into the buffer the V tile later occupies.
-template <int D, bool kWithP>
+template <int D>
 __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ CUtensorMap tmK,
                                                         const __grid_constant__ CUtensorMap tmV,
-                                                        const __grid_constant__ CUtensorMap tmQ,
                                                         const __grid_constant__ CUtensorMap tmUo,
                                                         const __grid_constant__ CUtensorMap tmWo,
                                                         const UWParams p) {
@@ -162,7 +156,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar_load, 1);
-        mbar_init(bar_mma, kWithP ? 4 : 2);
+        mbar_init(bar_mma, 2);
         mbar_init(bar_mma2, 2);
         mbar_fence_init();
     }
@@ -184,30 +178,20 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     const int khead = head / (p.vh / p.kh);
     const ChunkPos cp = locate_chunk(p.map, chunk);
     const int n = cp.n;
-#ifdef GDN_PHASE_TIMING
-    const bool stamp_on = blockIdx.x == GDN_STAMP_BX && it == GDN_STAMP_BY;
-#define GDN_STAMP_UW(i) GDN_STAMP_IF(stamp_on, i)
-#else
-#define GDN_STAMP_UW(i)
-#endif
     // beta and gate of this thread's token: requested first, used after the set-up below
     float b_mine = 0.f, g_mine = 0.f;
     if (tid < n) {
         b_mine = p.beta.load(cp.batch, cp.tok0 + tid, head);
         if (p.gate.ptr) g_mine = p.gate.load(cp.batch, cp.tok0 + tid, head);
     }
-    // one load phase per unit without P, two with it; two MMA phases per unit
-    const uint32_t load_par0 = kWithP ? 0u : (it & 1u);
+    // one load phase and two MMA phases per unit
+    const uint32_t load_par0 = it & 1u;
 
-    GDN_STAMP_UW(0);
     if (tid == 0) {
         mbar_arrive_expect_tx(bar_load, 2 * L::kTile);
         for (int a = 0; a < NA; ++a) {
             tma_load_4d(sK + a * 8192, &tmK, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
-            if (kWithP)
-                tma_load_4d(sV + a * 8192, &tmQ, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
-            else
-                tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
+            tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
         }
     }
     // beta and the chunk-local cumulative gate (rows past the end: beta = 0, g = g of the last row)
@@ -241,22 +225,18 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    GDN_STAMP_UW(1);
     // ---- A_raw = K K^T, columns 0-31 into lanes +0 and columns 32-63 into lanes +16
     mbar_wait(bar_load, load_par0, abort_flag);
-    GDN_STAMP_UW(2);
     // Every accumulator has its own issuing warp (warp-uniform issue, one elected lane): the issue
     // rate of one warp, not the tensor pipe, is what bounds these small MMAs.
     //   warp 0: K K^T columns 0-31 (lanes +0)    warp 1: K K^T columns 32-63 (lanes +16)
-    //   warp 2: Q K^T columns 0-31               warp 3: Q K^T columns 32-63
-    if (warp < (kWithP ? 4 : 2)) {
+    if (warp < 2) {
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, 32, false, false);
         const uint64_t dk0 = make_smem_desc_sw128(smem_u32(sK), 0, 1024);
-        const uint64_t dq0 = make_smem_desc_sw128(smem_u32(sV), 0, 1024);
-        const uint64_t da = (warp & 2) ? dq0 : dk0;                             // A: Q or K tile
+        const uint64_t da = dk0;                                                // A: the K tile
         const uint64_t db = (warp & 1) ? desc_advance(dk0, 32 * 128) : dk0;     // B: rows 32-63 or 0-31 of K
-        const uint32_t tacc = ((warp & 1) ? tHi : tLo) + ((warp & 2) ? 32u : 0u);
+        const uint32_t tacc = (warp & 1) ? tHi : tLo;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = kmajor_step(ks, 8192);
@@ -270,21 +250,18 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     __syncwarp();
     mbar_wait(bar_mma, it & 1u, abort_flag);
     tc_fence_after_sync();
-    GDN_STAMP_UW(3);
     {
         // row 16*warp + (lane & 15); lanes 0-15 hold columns 0-31, lanes 16-31 columns 32-63.
-        // The decay factor exp(g_i - g_j) is shared by A (strictly lower part) and P (lower part).
         const int i = 16 * warp + (lane & 15);
         const int cbase = (lane >> 4) * 32;
         const float bi = sBeta[i], gi = sG[i];
-        const f2 bi2 = pk(bi, bi), ps2 = pk(p.p_scale, p.p_scale);
-        uint32_t r[32], rq[32];
+        const f2 bi2 = pk(bi, bi);
+        uint32_t r[32];
         tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
-        if (kWithP) tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 32, rq);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-            float a[8], pq[8];
+            float a[8];
 #pragma unroll
             for (int e4 = 0; e4 < 2; ++e4) {
                 const float4 gc = *reinterpret_cast<const float4*>(sG + cbase + j + 4 * e4);
@@ -299,37 +276,16 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
                     const f2 dec2 = pk(d0, d1);
                     unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), bi2), dec2), a[4 * e4 + e],
                          a[4 * e4 + e + 1]);
-                    if (kWithP)
-                        unpk(mul2(mul2(pk(__uint_as_float(rq[k]), __uint_as_float(rq[k + 1])), ps2), dec2),
-                             pq[4 * e4 + e], pq[4 * e4 + e + 1]);
                 }
             }
             *reinterpret_cast<float4*>(&sA[i * LD + cbase + j]) = make_float4(a[0], a[1], a[2], a[3]);
             *reinterpret_cast<float4*>(&sA[i * LD + cbase + j + 4]) = make_float4(a[4], a[5], a[6], a[7]);
-            if (kWithP) {
-                // P tile staged over the (dead) Q tile in the 64x64 swizzled TMA layout
-                *reinterpret_cast<uint4*>(sV + tile_off(i, (cbase + j) >> 3)) =
-                    make_uint4(pack_bf16(pq[0], pq[1]), pack_bf16(pq[2], pq[3]), pack_bf16(pq[4], pq[5]),
-                               pack_bf16(pq[6], pq[7]));
-            }
         }
         if (i >= cbase && i < cbase + 32) sA[i * LD + i] = 0.f;  // A is strictly lower triangular
     }
-    uint32_t bar_load_parity = 0;
-    if (kWithP) fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
-    if (kWithP) {
-        // (fence + barrier above: staged P complete and visible to the TMA engine)
-        if (tid == 0) {
-            bulk_store(p.blocks + static_cast<size_t>(unit) * kUnitBlockBytes + 2 * L::kTile, sV,
-                       kChunk * kChunk * 2);
-            bulk_commit();
-        }
-        bar_load_parity = 1;  // the V tile follows into the same buffer once the store has read it
-    }
 
-    GDN_STAMP_UW(4);
     // ---- X = (I + A)^-1, in place.  Diagonal 16x16 blocks: one column per thread.
     {
         const int b = warp, j = lane & 15;
@@ -359,13 +315,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         }
     }
     __syncthreads();
-    if (kWithP && tid == 0) {
-        bulk_wait_read<0>();  // the P store has read the buffer: the V tile may land there
-        mbar_arrive_expect_tx(bar_load, L::kTile);
-        for (int a = 0; a < NA; ++a)
-            tma_load_4d(sV + a * 8192, &tmV, bar_load, a * 64, head, static_cast<int>(cp.tok0), cp.batch);
-    }
-    GDN_STAMP_UW(5);
     // level 1 (16 -> 32): X_10 = -X_11 A_10 X_00 and X_32 = -X_33 A_32 X_22; warp = (pair, 8-column half).
     // The intermediate A_10 X_00 is parked in the unused block above the diagonal.
     {
@@ -382,7 +331,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         store_block(e, -1.f, sA, LD, i0, j0 + n0, lane);
     }
     __syncthreads();
-    GDN_STAMP_UW(6);
     // level 2 (32 -> 64): X_[2:4,0:2] = -X_[2:4,2:4] A_[2:4,0:2] X_[0:2,0:2]; warp = 16x16 block of the result.
     // The intermediate goes to the unused upper-right quadrant; K-steps that would only meet the
     // (zero, here scratch) blocks above the diagonal are skipped.
@@ -414,7 +362,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    GDN_STAMP_UW(7);
     // ---- T = X diag(beta), T' = X diag(beta e^g) as bf16 K-major swizzled tiles written over X:
     //      every thread first pulls its 32 values of X into registers
     {
@@ -450,9 +397,7 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     fence_proxy_async_smem();
     __syncthreads();
 
-    GDN_STAMP_UW(8);
     // ---- U = T V (lanes +0), W = T' K (lanes +16)
-    if (kWithP) mbar_wait(bar_load, bar_load_parity, abort_flag);
     if (warp < 2) {  // warp 0 issues U, warp 1 issues W
         tc_fence_after_sync();
         constexpr uint32_t idesc = make_idesc_bf16(64, D, false, true);
@@ -468,7 +413,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     mbar_wait(bar_mma2, it & 1u, abort_flag);
     tc_fence_after_sync();
 
-    GDN_STAMP_UW(9);
     // ---- accumulators -> bf16 -> staged tiles (over the K and V tiles) -> coalesced stores
     uint8_t* stU = sK;
     uint8_t* stW = sV;
@@ -494,15 +438,8 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
-    GDN_STAMP_UW(10);
-    if (kWithP) {
-        // U and W staging tiles are adjacent: one copy (rows past the end of a sequence are zero)
-        static_assert(L::kOffV == L::kOffK + L::kTile, "U and W staging tiles must be adjacent");
-        if (tid == 0) {
-            bulk_store(p.blocks + static_cast<size_t>(unit) * kUnitBlockBytes, stU, 2 * L::kTile);
-            bulk_commit();
-            bulk_wait_read<0>();
-        }
+    if (*abort_flag != 0) {
+        // a wait has given up: nothing is written
     } else if (p.map.cu_seqlens != nullptr && n < kChunk) {
         // a full-box store would spill into the next packed sequence: row-predicated stores
         store_tile_rows<128>(stU, p.u, cp.batch, cp.tok0, head, n, tid);
@@ -515,7 +452,6 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
         bulk_commit();
         bulk_wait_read<0>();
     }
-    GDN_STAMP_UW(11);
     __syncthreads();  // staging tiles and vectors are free for the next unit
     }                 // unit loop
     if (warp == 0) tmem_dealloc(tmem, D);

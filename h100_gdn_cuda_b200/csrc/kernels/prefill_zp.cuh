@@ -34,6 +34,7 @@ struct ZPParams {
     ScalarView gate;  // raw per-token log-decay (the chunk-local cumsum is taken here); ptr == NULL: no decay
     uint8_t* blocks;  // kZPBlockBytes per (global chunk, v-head)
     float p_scale;    // output scale, folded into P
+    float* norms;     // kNorm: 128 floats per (global chunk, k-head): rsqrt(sum k^2 + eps)[64], the same for q [64]
     int kh, vh;
     int num_chunks;
     int* status;
@@ -49,7 +50,8 @@ struct ZPSmem {
     static constexpr int kOffP = 64 * kLd * 4;           // 17408: P tile (8 KB), later the staged PT
     static constexpr int kOffVec = kOffP + 8192;         // beta[64], g log2e[64], d[64]
     static constexpr int kTeamBytes = kOffVec + 3 * 64 * 4 + 256;  // 26624 (multiple of 1024)
-    static constexpr int kOffBar = kTeam + 2 * kTeamBytes;
+    static constexpr int kOffNorm = kTeam + 2 * kTeamBytes;  // kNorm: inverse row norms of K [64] and Q [64], their log2 [128]
+    static constexpr int kOffBar = kOffNorm + 1024;
     static constexpr int kBytes = kOffBar + 128 + 1024;
     static_assert(kOffP % 1024 == 0 && kTeamBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
@@ -67,6 +69,11 @@ __device__ __forceinline__ void team_sync(int team) {
 }
 }  // namespace zp
 
+// kNorm: q and k are L2-normalised per head (x * rsqrt(sum x^2 + 1e-6)) without touching the tiles:
+// (k_i.k_j) r_i r_j and (q_i.k_j) rq_i r_j enter through the row factor of the A / P pass and through
+// the column's gate (g_j - log2 r_j in the exponent), Z = (dT)^T diag(r) K through d_i r_i.  The
+// factors are also written to `norms` for the state kernel.
+template <bool kNorm>
 __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_constant__ CUtensorMap tmK,
                                                                  const __grid_constant__ CUtensorMap tmQ,
                                                                  const ZPParams p) {
@@ -89,6 +96,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     float* sG = sBeta + 64;
     float* sD = sG + 64;
     float* sPart = sD + 64;
+    float* sRn = reinterpret_cast<float*>(smem + L::kOffNorm);  // [128] inverse norms (K rows, then Q rows)
+    float* sLr = sRn + 128;                                      // [128] their log2
     uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* bar_kq = bar_load + 1;
     uint64_t* bar_mma = bar_load + 2;  // [2], one per team
@@ -185,6 +194,31 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
             // ---- K K^T (lanes 0-63) and Q K^T (lanes 64-127): once per unit, shared by its v-heads
             if (rd == 0) {
                 mbar_wait(bar_load, it & 1u, abort_flag);
+                if (kNorm) {
+                    // inverse L2 norm of every row of the stacked K | Q tile: two threads per row, 64 columns each
+                    const int r = tid >> 1, hf = tid & 1;
+                    const uint8_t* rowp = sKQ + hf * 16384 + (r >> 6) * 8192 + (r & 63) * 128;
+                    float ss = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 w = *reinterpret_cast<const uint4*>(rowp + 16 * c);
+                        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = bf16_lo(ww[e]), hi = bf16_hi(ww[e]);
+                            ss = fmaf(lo, lo, ss);
+                            ss = fmaf(hi, hi, ss);
+                        }
+                    }
+                    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                    const float rinv = rsqrtf(ss + 1e-6f);
+                    if (hf == 0) {
+                        sRn[r] = rinv;
+                        sLr[r] = log2f(rinv);
+                        if (*abort_flag == 0) p.norms[static_cast<size_t>(unit) * 128 + r] = rinv;
+                    }
+                    __syncthreads();
+                }
                 if (warp == 0) {
                     tc_fence_after_sync();
                     constexpr uint32_t idesc = make_idesc_bf16(128, 64, false, false);
@@ -211,7 +245,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                     const int rb = tw & 1;
                     const int i = 32 * rb + lane;
                     const float gi = sG[i];
-                    const float f = is_p ? p.p_scale : sBeta[i];
+                    float f = is_p ? p.p_scale : sBeta[i];
+                    if (kNorm) f *= sRn[is_p ? 64 + i : i];
                     const f2 fv = pk(f, f);
                     const int lim = (i < n) ? (is_p ? i : i - 1) : -1;  // columns kept: col <= lim
                     for (int cb = 0; cb <= rb; ++cb) {
@@ -224,7 +259,11 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
 #pragma unroll
                             for (int e4 = 0; e4 < 2; ++e4) {
                                 const float4 gc = *reinterpret_cast<const float4*>(sG + 32 * cb + j + 4 * e4);
-                                const float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
+                                float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
+                                if (kNorm) {  // the column's key norm enters through the exponent
+                                    const float4 lr = *reinterpret_cast<const float4*>(sLr + 32 * cb + j + 4 * e4);
+                                    gcv[0] -= lr.x; gcv[1] -= lr.y; gcv[2] -= lr.z; gcv[3] -= lr.w;
+                                }
 #pragma unroll
                                 for (int e = 0; e < 4; e += 2) {
                                     const int col = 32 * cb + j + 4 * e4 + e, k = j + 4 * e4 + e;
@@ -359,7 +398,7 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                         xs[4 * q] = valid ? t.x : 0.f; xs[4 * q + 1] = valid ? t.y : 0.f;
                         xs[4 * q + 2] = valid ? t.z : 0.f; xs[4 * q + 3] = valid ? t.w : 0.f;
                     }
-                    const float di = sD[i];
+                    const float di = kNorm ? sD[i] * sRn[i] : sD[i];
                     const f2 di2 = pk(di, di);
                     team_sync(team);
 #pragma unroll

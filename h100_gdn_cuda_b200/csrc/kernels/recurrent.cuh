@@ -51,6 +51,11 @@ struct RecurrentParams {
     int batch, seq_len, kh, vh, dv;
     float scale;
     int is_qk_norm, store_step;
+    // Fused gating: `beta` / `gate` then hold the layer's raw projections b / a and the kernel computes
+    // beta = sigmoid(b), g = -exp(A_log[h]) softplus(a + dt_bias[h]) itself (fp32, nothing rounded to bf16).
+    int fused_gating, gating_param_f32;
+    const void* A_log;
+    const void* dt_bias;
     int split_tiles;  // 1: every 32-row tile is a work unit (multi-token runs); 0: a unit = all tiles of a (sequence, v-head)
     long long num_tiles;
     int* status;
@@ -212,6 +217,16 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         } else {
             gt = 0.f;
         }
+        if (p.fused_gating) {
+            const float al = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.A_log) + t.head)
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.A_log)[t.head]);
+            const float db = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.dt_bias) + t.head)
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.dt_bias)[t.head]);
+            const float x = gt + db;
+            const float sp = x > 20.f ? x : log1pf(__expf(x));
+            gt = -__expf(al) * sp;
+            bt = 1.f / (1.f + __expf(-bt));
+        }
     };
 
     // The producer walks (unit, rb) pairs kStages-1 iterations ahead of the consumers.
@@ -262,7 +277,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             // ---- staged data -> registers
             f2 S[4][NQ];
             float vr[4];
-            mbar_wait(&full[stage], parity, &abort_flag);
+            // `ok` turns false when a wait gives up: the tile's data is then garbage and nothing of it is stored
+            bool ok = mbar_wait(&full[stage], parity, &abort_flag);
             const uint8_t* st = smem + stage * Stage::kBytes;
             if (has_in) {
 #pragma unroll
@@ -414,11 +430,11 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                     for (int c = 0; c < NQ; ++c) S[j][c] = fma2(eg2, S[j][c], mul2(br2, k2[c]));
                 }
                 const long long tok = T.tok0 + t;
-                if (l16 >= 8 && (l16 & 1) == 0) {
+                if (ok && l16 >= 8 && (l16 & 1) == 0) {
                     __nv_bfloat16* op = p.out + T.bidx * p.o_sb + tok * p.o_st + T.head * p.o_sh + rb * kRecTileRows;
                     op[warp * 8 + (l16 - 8) + half] = __float2bfloat16(o_mine);
                 }
-                if (p.store_step) {
+                if (p.store_step && ok) {
                     const long long sidx = p.cu_seqlens ? tok : (static_cast<long long>(T.seq) * p.seq_len + t);
                     __nv_bfloat16* sp = p.state_out + sidx * p.so_ss + T.head * p.so_sh +
                                         static_cast<long long>(rb) * kRecTileRows * DK;
@@ -486,7 +502,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         ts = st + Stage::kTileBytes;  // same layout as a ring slot
                     } else {
                         const int slot = (tb_it + blk - 1) & 1;
-                        mbar_wait(&tokfull[slot], static_cast<uint32_t>(((tb_it + blk - 1) >> 1) & 1), &abort_flag);
+                        ok = mbar_wait(&tokfull[slot], static_cast<uint32_t>(((tb_it + blk - 1) >> 1) & 1), &abort_flag) && ok;
                         ts = tokbase + slot * TokSlot::kBytes;
                     }
                     const int nt = min(TB, T.ntok - blk * TB);
@@ -532,7 +548,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             }
 
             }
-            if (!p.store_step) {
+            if (!p.store_step && ok) {
                 __nv_bfloat16* sp = p.state_out + static_cast<long long>(T.seq) * p.so_ss + T.head * p.so_sh +
                                     static_cast<long long>(rb) * kRecTileRows * DK;
 #pragma unroll

@@ -74,7 +74,7 @@ GDN_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // of instructions.
 constexpr long long kWaitLimitCycles = 4000ll * 1000ll * 1000ll;
 
-GDN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+GDN_DEVICE bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit_cycles) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -86,12 +86,15 @@ GDN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fl
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 255u) == 0) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
+}
+GDN_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
 // The same wait for warps that are not on a critical path: sleeps `kSleepNs` between polls so

@@ -101,7 +101,8 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
                                                   std::optional<at::Tensor>& cu_seqlens,
                                                   std::optional<at::Tensor>& chunk_indices,
                                                   std::optional<at::Tensor>& cu_chunks,
-                                                  std::optional<int> total_chunks, cudaStream_t stream) {
+                                                  std::optional<int> total_chunks, cudaStream_t stream,
+                                                  bool is_qk_norm) {
     cuda_bf16(query, "query");
     cuda_bf16(key, "key");
     cuda_bf16(value, "value");
@@ -145,6 +146,7 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     a.workspace = ws.data_ptr();
     a.workspace_bytes = ws_bytes;
     a.stage_events = nullptr;
+    a.is_qk_norm = is_qk_norm ? 1 : 0;
     check(gdn_chunked_forward(&a, stream), "chunked_forward");
     if (d != D) {
         out = out.narrow(-1, 0, d);
@@ -153,12 +155,17 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     return {out, fin};
 }
 
-std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tensor& key, at::Tensor& value,
-                                                    std::optional<at::Tensor>& initial_state, at::Tensor& beta,
-                                                    at::Tensor& gate, std::optional<at::Tensor>& cu_seqlens,
-                                                    std::optional<at::Tensor>& num_accepted_tokens,
-                                                    InferenceMode inference_mode, cudaStream_t stream,
-                                                    bool is_qk_norm, std::optional<float> scale) {
+namespace {
+struct Gating {
+    at::Tensor A_log, dt_bias, a, b;
+};
+std::pair<at::Tensor, at::Tensor> recurrent_impl(at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                                 std::optional<at::Tensor>& initial_state,
+                                                 const std::optional<at::Tensor>& beta, const std::optional<at::Tensor>& gate,
+                                                 const Gating* gating, std::optional<at::Tensor>& cu_seqlens,
+                                                 std::optional<at::Tensor>& num_accepted_tokens,
+                                                 InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
+                                                 std::optional<float> scale) {
     cuda_bf16(query, "query");
     cuda_bf16(key, "key");
     cuda_bf16(value, "value");
@@ -194,8 +201,23 @@ std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tenso
     a.k = tok(k, packed);
     a.v = tok(v, packed);
     a.out = tok(out, packed);
-    a.beta = sca(beta, packed, tokens);
-    a.gate = sca(gate, packed, tokens);
+    at::Tensor Ac, dc;  // keep the contiguous copies alive until the launch
+    if (gating) {
+        require(gating->a.scalar_type() == gating->b.scalar_type() && gating->a.scalar_type() == gating->A_log.scalar_type() &&
+                    gating->a.scalar_type() == gating->dt_bias.scalar_type(),
+                "A_log, dt_bias, a, b must share a dtype");
+        require(gating->A_log.numel() >= vh && gating->dt_bias.numel() >= vh, "A_log and dt_bias need one entry per head");
+        Ac = gating->A_log.contiguous();
+        dc = gating->dt_bias.contiguous();
+        a.gating_a = sca(gating->a, packed, tokens);
+        a.gating_b = sca(gating->b, packed, tokens);
+        a.A_log = Ac.data_ptr();
+        a.dt_bias = dc.data_ptr();
+    } else {
+        require(beta.has_value(), "beta is required");
+        a.beta = sca(beta, packed, tokens);
+        a.gate = sca(gate, packed, tokens);
+    }
     a.state_in = st(s_in);
     a.num_accepted_tokens = i32(num_accepted_tokens, "num_accepted_tokens");
     a.scale = scale.value_or(1.0f / std::sqrt(static_cast<float>(d)));
@@ -205,6 +227,66 @@ std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tenso
     if (dv_al != dv_in) out = out.narrow(-1, 0, dv_in);
     if (d_al != d || dv_al != dv_in) s_out = s_out.narrow(-1, 0, d).narrow(-2, 0, dv_in);
     return {out, s_out};
+}
+}  // namespace
+
+std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                                    std::optional<at::Tensor>& initial_state, at::Tensor& beta,
+                                                    at::Tensor& gate, std::optional<at::Tensor>& cu_seqlens,
+                                                    std::optional<at::Tensor>& num_accepted_tokens,
+                                                    InferenceMode inference_mode, cudaStream_t stream,
+                                                    bool is_qk_norm, std::optional<float> scale) {
+    return recurrent_impl(query, key, value, initial_state, beta, gate.defined() ? std::optional<at::Tensor>(gate) : std::nullopt,
+                          nullptr, cu_seqlens, num_accepted_tokens, inference_mode, stream, is_qk_norm, scale);
+}
+
+std::pair<at::Tensor, at::Tensor> recurrent_forward_fused_gating(
+    at::Tensor& query, at::Tensor& key, at::Tensor& value, std::optional<at::Tensor>& initial_state, at::Tensor& A_log,
+    at::Tensor& dt_bias, at::Tensor& a, at::Tensor& b, std::optional<at::Tensor>& cu_seqlens,
+    std::optional<at::Tensor>& num_accepted_tokens, InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
+    std::optional<float> scale) {
+    Gating g{A_log, dt_bias, a, b};
+    return recurrent_impl(query, key, value, initial_state, std::nullopt, std::nullopt, &g, cu_seqlens, num_accepted_tokens,
+                          inference_mode, stream, is_qk_norm, scale);
+}
+
+void bf16_gdn_recurrent(at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor>& initial_state,
+                        at::Tensor& final_state, at::Tensor& out, std::optional<at::Tensor>& gate, at::Tensor& beta,
+                        const std::string& /*compiled_dims*/, cudaStream_t stream, std::optional<at::Tensor>& cu_seqlens,
+                        std::optional<at::Tensor>& num_accepted_tokens, bool store_step_state, bool is_qk_norm,
+                        float scale) {
+    cuda_bf16(q, "q");
+    cuda_bf16(k, "k");
+    cuda_bf16(v, "v");
+    cuda_bf16(out, "out");
+    cuda_bf16(final_state, "final_state");
+    const bool packed = cu_seqlens.has_value();
+    const int64_t dk = q.size(-1), dv = v.size(-1), vh = v.size(-2);
+    require(k.size(-1) == dk, "q and k head dims differ");
+    require(dk % 64 == 0 && dv % 64 == 0 && dk <= 256 && dv <= 256,
+            "bf16_gdn_recurrent works on the caller's tensors: head dims must be multiples of 64 up to 256");
+    require(out.sizes() == v.sizes(), "out must be shaped like v");
+    require(final_state.is_contiguous() && final_state.size(-1) == dk && final_state.size(-2) == dv,
+            "final_state must be contiguous (..., dv, dk)");
+    GdnRecurrentArgs a{};
+    a.shape = make_shape(q, v, cu_seqlens, std::nullopt, std::nullopt, 0);
+    const int64_t tokens = packed ? q.size(0) : q.size(1);
+    const int64_t want = store_step_state ? a.shape.total_tokens : a.shape.batch;
+    require(final_state.numel() == want * vh * dv * dk,
+            store_step_state ? "final_state must hold one state per token" : "final_state must hold one state per sequence");
+    a.q = tok(q, packed);
+    a.k = tok(k, packed);
+    a.v = tok(v, packed);
+    a.out = tok(out, packed);
+    a.beta = sca(beta, packed, tokens);
+    a.gate = sca(gate, packed, tokens);
+    a.state_in = st(initial_state);
+    a.state_out = GdnState{final_state.data_ptr(), vh * dv * dk, dv * dk};
+    a.num_accepted_tokens = i32(num_accepted_tokens, "num_accepted_tokens");
+    a.scale = scale;
+    a.is_qk_norm = is_qk_norm ? 1 : 0;
+    a.store_step_state = store_step_state ? 1 : 0;
+    check(gdn_recurrent_forward(&a, stream), "bf16_gdn_recurrent");
 }
 
 std::pair<at::Tensor, at::Tensor> fused_gdn_gating(at::Tensor& A_log, at::Tensor& dt_bias, at::Tensor& a,
@@ -231,6 +313,17 @@ void bf16_gdn_compute_u_w(at::Tensor& k, at::Tensor& v, at::Tensor& u, at::Tenso
     cuda_bf16(v, "v");
     cuda_bf16(u, "u");
     cuda_bf16(w, "w");
+    const int64_t d = k.size(-1);
+    require(d > 0 && d <= kPrefillDim && v.size(-1) == d, "low-level chunked kernels need dk = dv <= 128");
+    if (d != kPrefillDim) {
+        // the kernels are built for head dim 128: run on zero-padded copies (exact) and copy the results back
+        at::Tensor kp = pad_last(k, kPrefillDim), vp = pad_last(v, kPrefillDim);
+        at::Tensor up = at::empty_like(vp), wp = at::empty_like(vp);
+        bf16_gdn_compute_u_w(kp, vp, up, wp, beta, gate, "t", stream, cu_seqlens, chunk_indices);
+        u.copy_(up.narrow(-1, 0, d));
+        w.copy_(wp.narrow(-1, 0, d));
+        return;
+    }
     const bool packed = cu_seqlens.has_value();
     const int64_t tokens = packed ? k.size(0) : k.size(1);
     GdnComputeUWArgs a{};
@@ -257,6 +350,30 @@ void bf16_chunked_seq_state_update(at::Tensor& k, at::Tensor& u, at::Tensor& w,
     cuda_bf16(w, "w");
     cuda_bf16(state, "state");
     require(state.is_contiguous(), "state must be contiguous");
+    const int64_t d = k.size(-1);
+    require(d > 0 && d <= kPrefillDim && u.size(-1) == d, "low-level chunked kernels need dk = dv <= 128");
+    if (d != kPrefillDim) {
+        // as the reference's wrapper does (csrc/apis/gdn_forward.cpp:252-302): zero-padded copies, results copied back
+        const int64_t D = kPrefillDim;
+        at::Tensor kp = pad_last(k, D), up = pad_last(u, D), wp = pad_last(w, D);
+        std::vector<int64_t> shp(state.sizes().begin(), state.sizes().end());
+        shp[shp.size() - 1] = D;
+        shp[shp.size() - 2] = D;
+        at::Tensor sp = at::empty(shp, state.options());
+        std::optional<at::Tensor> ip, fp;
+        if (initial_state.has_value()) ip = pad_state(*initial_state, D, D).contiguous();
+        if (final_state.has_value()) {
+            std::vector<int64_t> fs(final_state->sizes().begin(), final_state->sizes().end());
+            fs[fs.size() - 1] = D;
+            fs[fs.size() - 2] = D;
+            fp = at::empty(fs, state.options());
+        }
+        bf16_chunked_seq_state_update(kp, up, wp, ip, sp, fp, gate, "t", stream, cu_seqlens, cu_chunks, total_chunks, chunk_size);
+        u.copy_(up.narrow(-1, 0, d));
+        state.copy_(sp.narrow(-1, 0, d).narrow(-2, 0, d));
+        if (final_state.has_value()) final_state->copy_(fp->narrow(-1, 0, d).narrow(-2, 0, d));
+        return;
+    }
     const bool packed = cu_seqlens.has_value();
     const int64_t tokens = packed ? k.size(0) : k.size(1);
     GdnSeqStateArgs a{};
@@ -285,6 +402,19 @@ void bf16_gdn_chunked_compute_O(at::Tensor& q, at::Tensor& state, at::Tensor& k,
     cuda_bf16(o, "o");
     cuda_bf16(state, "state");
     require(state.is_contiguous(), "state must be contiguous");
+    const int64_t d = q.size(-1);
+    require(d > 0 && d <= kPrefillDim && u.size(-1) == d, "low-level chunked kernels need dk = dv <= 128");
+    if (d != kPrefillDim) {
+        const int64_t D = kPrefillDim;
+        at::Tensor qp = pad_last(q, D), kp = pad_last(k, D), up = pad_last(u, D);
+        at::Tensor sp = pad_state(state, D, D).contiguous();
+        at::Tensor op = at::empty_like(up);
+        std::optional<float> sc = scale.value_or(1.0f / std::sqrt(static_cast<float>(d)));
+        bf16_gdn_chunked_compute_O(qp, sp, kp, up, op, gate, sc, "t", stream, cu_seqlens, chunk_indices, cu_chunks,
+                                   std::nullopt, chunk_size);
+        o.copy_(op.narrow(-1, 0, d));
+        return;
+    }
     const bool packed = cu_seqlens.has_value();
     const int64_t tokens = packed ? q.size(0) : q.size(1);
     GdnComputeOArgs a{};

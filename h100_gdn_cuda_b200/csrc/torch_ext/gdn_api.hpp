@@ -21,7 +21,8 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
                                                   std::optional<at::Tensor>& cu_seqlens,
                                                   std::optional<at::Tensor>& chunk_indices,
                                                   std::optional<at::Tensor>& cu_chunks,
-                                                  std::optional<int> total_chunks, cudaStream_t stream);
+                                                  std::optional<int> total_chunks, cudaStream_t stream,
+                                                  bool is_qk_norm = false);  // last argument: extension, see gdn_b200.h
 
 std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tensor& key, at::Tensor& value,
                                                     std::optional<at::Tensor>& initial_state, at::Tensor& beta,
@@ -29,6 +30,23 @@ std::pair<at::Tensor, at::Tensor> recurrent_forward(at::Tensor& query, at::Tenso
                                                     std::optional<at::Tensor>& num_accepted_tokens,
                                                     InferenceMode inference_mode, cudaStream_t stream,
                                                     bool is_qk_norm, std::optional<float> scale);
+
+// Extension: recurrent_forward with the layer's gating computed inside the kernel from its raw
+// projections (beta = sigmoid(b), gate = -exp(A_log) softplus(a + dt_bias)); no separate gating launch.
+std::pair<at::Tensor, at::Tensor> recurrent_forward_fused_gating(
+    at::Tensor& query, at::Tensor& key, at::Tensor& value, std::optional<at::Tensor>& initial_state, at::Tensor& A_log,
+    at::Tensor& dt_bias, at::Tensor& a, at::Tensor& b, std::optional<at::Tensor>& cu_seqlens,
+    std::optional<at::Tensor>& num_accepted_tokens, InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
+    std::optional<float> scale);
+
+// csrc/apis/gdn_forward.hpp:43-49: the recurrence on caller-provided output tensors.  `final_state` is
+// (B, vh, dv, dk), or one state per token when `store_step_state`; head dims must be multiples of 64
+// here (no padding can be done on the caller's tensors); `compiled_dims` is accepted and ignored.
+void bf16_gdn_recurrent(at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor>& initial_state,
+                        at::Tensor& final_state, at::Tensor& out, std::optional<at::Tensor>& gate, at::Tensor& beta,
+                        const std::string& compiled_dims, cudaStream_t stream, std::optional<at::Tensor>& cu_seqlens,
+                        std::optional<at::Tensor>& num_accepted_tokens, bool store_step_state = false,
+                        bool is_qk_norm = false, float scale = 1.0f);
 
 std::pair<at::Tensor, at::Tensor> fused_gdn_gating(at::Tensor& A_log, at::Tensor& dt_bias, at::Tensor& a,
                                                    at::Tensor& b, bool is_var_len, cudaStream_t stream);

@@ -1,6 +1,7 @@
 // pybind11 module `gdn_cuda`: the names, argument order, keywords and defaults of the reference's
 // csrc/python_api.cpp:17-393, forwarding to namespace gdn_cuda (gdn_api.hpp) on the current torch stream.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 #include <torch/extension.h>
@@ -9,7 +10,12 @@
 
 namespace py = pybind11;
 
-static cudaStream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+// Every call runs on the device of its first tensor and on that device's current torch stream.
+struct OnDevice {
+    c10::cuda::CUDAGuard guard;
+    explicit OnDevice(const at::Tensor& t) : guard(t.device()) {}
+    cudaStream_t stream() const { return at::cuda::getCurrentCUDAStream().stream(); }
+};
 
 PYBIND11_MODULE(gdn_cuda, m) {
     m.doc() = "Gated DeltaNet kernels for B200 (sm_100a) behind the gdn_cuda API";
@@ -22,35 +28,50 @@ PYBIND11_MODULE(gdn_cuda, m) {
         [](at::Tensor& q, at::Tensor& k, at::Tensor& v, at::Tensor& beta, at::Tensor& gate, std::optional<float> scale,
            std::optional<at::Tensor> initial_state, std::optional<at::Tensor> cu_seqlens,
            std::optional<at::Tensor> chunk_indices, std::optional<at::Tensor> cu_chunks,
-           std::optional<int> total_chunks) {
+           std::optional<int> total_chunks, bool is_qk_norm) {
+            OnDevice dev(q);
             return gdn_cuda::chunked_forward(q, k, v, beta, gate, scale, initial_state, cu_seqlens, chunk_indices,
-                                             cu_chunks, total_chunks, current_stream());
+                                             cu_chunks, total_chunks, dev.stream(), is_qk_norm);
         },
         py::arg("query"), py::arg("key"), py::arg("value"), py::arg("beta"), py::arg("gate"),
         py::arg("scale") = py::none(), py::arg("initial_state") = py::none(), py::arg("cu_seqlens") = py::none(),
         py::arg("chunk_indices") = py::none(), py::arg("cu_chunks") = py::none(), py::arg("total_chunks") = py::none(),
+        py::kw_only(), py::arg("is_qk_norm") = false,
         "Chunked (64-token) prefill.  query/key (B,T,kh,d)|(N,kh,d), value (B,T,vh,d)|(N,vh,d), beta bf16 and gate "
         "fp32 (raw log-decay) (B,T,vh)|(N,vh), initial_state (B|S,vh,d,d) bf16.  Returns (output, final_state).");
 
     m.def(
         "recurrent_forward",
-        [](at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor> initial_state, at::Tensor& beta,
-           at::Tensor& gate, std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> num_accepted_tokens,
-           int inference_mode, bool is_qk_norm, std::optional<float> scale) {
-            return gdn_cuda::recurrent_forward(q, k, v, initial_state, beta, gate, cu_seqlens, num_accepted_tokens,
-                                               static_cast<gdn_cuda::InferenceMode>(inference_mode), current_stream(),
-                                               is_qk_norm, scale);
+        [](at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor> initial_state,
+           std::optional<at::Tensor> beta, std::optional<at::Tensor> gate, std::optional<at::Tensor> cu_seqlens,
+           std::optional<at::Tensor> num_accepted_tokens, int inference_mode, bool is_qk_norm, std::optional<float> scale,
+           std::optional<std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor>> gating) {
+            OnDevice dev(q);
+            const auto mode = static_cast<gdn_cuda::InferenceMode>(inference_mode);
+            if (gating.has_value()) {
+                if (beta.has_value() || gate.has_value())
+                    throw std::runtime_error("pass either gating=(A_log, dt_bias, a, b) or beta/gate, not both");
+                auto& [A_log, dt_bias, a, b] = *gating;
+                return gdn_cuda::recurrent_forward_fused_gating(q, k, v, initial_state, A_log, dt_bias, a, b, cu_seqlens,
+                                                                num_accepted_tokens, mode, dev.stream(), is_qk_norm, scale);
+            }
+            if (!beta.has_value()) throw std::runtime_error("beta is required");
+            at::Tensor g = gate.has_value() ? *gate : at::Tensor();
+            return gdn_cuda::recurrent_forward(q, k, v, initial_state, *beta, g, cu_seqlens, num_accepted_tokens, mode,
+                                               dev.stream(), is_qk_norm, scale);
         },
         py::arg("query"), py::arg("key"), py::arg("value"), py::arg("initial_state") = py::none(), py::arg("beta"),
         py::arg("gate"), py::arg("cu_seqlens") = py::none(), py::arg("num_accepted_tokens") = py::none(),
-        py::arg("inference_mode") = 0, py::arg("is_qk_norm") = false, py::arg("scale") = py::none(),
+        py::arg("inference_mode") = 0, py::arg("is_qk_norm") = false, py::arg("scale") = py::none(), py::kw_only(),
+        py::arg("gating") = py::none(),
         "Token recurrence for decode / speculative verify.  Returns (output, new_state); new_state holds one state "
         "per token when inference_mode == SpecVerify.");
 
     m.def(
         "fused_gdn_gating",
         [](at::Tensor& A_log, at::Tensor& dt_bias, at::Tensor& a, at::Tensor& b, bool is_var_len) {
-            return gdn_cuda::fused_gdn_gating(A_log, dt_bias, a, b, is_var_len, current_stream());
+            OnDevice dev(a);
+            return gdn_cuda::fused_gdn_gating(A_log, dt_bias, a, b, is_var_len, dev.stream());
         },
         py::arg("A_log"), py::arg("dt_bias"), py::arg("a"), py::arg("b"), py::arg("is_var_len") = false,
         "(beta, gate) = (sigmoid(b), -exp(A_log) * softplus(a + dt_bias)).");
@@ -60,7 +81,8 @@ PYBIND11_MODULE(gdn_cuda, m) {
         [](at::Tensor& k, at::Tensor& v, at::Tensor& u, at::Tensor& w, at::Tensor& beta, std::optional<at::Tensor> gate,
            const std::string& compiled_dims, std::optional<at::Tensor> cu_seqlens,
            std::optional<at::Tensor> chunk_indices) {
-            gdn_cuda::bf16_gdn_compute_u_w(k, v, u, w, beta, gate, compiled_dims, current_stream(), cu_seqlens,
+            OnDevice dev(k);
+            gdn_cuda::bf16_gdn_compute_u_w(k, v, u, w, beta, gate, compiled_dims, dev.stream(), cu_seqlens,
                                            chunk_indices);
         },
         py::arg("k"), py::arg("v"), py::arg("u"), py::arg("w"), py::arg("beta"), py::arg("gate") = py::none(),
@@ -68,13 +90,30 @@ PYBIND11_MODULE(gdn_cuda, m) {
         "Low-level WY/UT transform; writes u and w.");
 
     m.def(
+        "bf16_gdn_recurrent",
+        [](at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor> initial_state, at::Tensor& final_state,
+           at::Tensor& out, std::optional<at::Tensor> gate, at::Tensor& beta, const std::string& compiled_dims,
+           std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> num_accepted_tokens, bool store_step_state,
+           bool is_qk_norm, float scale) {
+            OnDevice dev(q);
+            gdn_cuda::bf16_gdn_recurrent(q, k, v, initial_state, final_state, out, gate, beta, compiled_dims, dev.stream(),
+                                         cu_seqlens, num_accepted_tokens, store_step_state, is_qk_norm, scale);
+        },
+        py::arg("q"), py::arg("k"), py::arg("v"), py::arg("initial_state"), py::arg("final_state"), py::arg("out"),
+        py::arg("gate"), py::arg("beta"), py::arg("compiled_dims") = "t", py::arg("cu_seqlens") = py::none(),
+        py::arg("num_accepted_tokens") = py::none(), py::arg("store_step_state") = false, py::arg("is_qk_norm") = false,
+        py::arg("scale") = 1.0f,
+        "The recurrence on caller-provided tensors (the C++ gdn_cuda::bf16_gdn_recurrent); writes out and final_state.");
+
+    m.def(
         "bf16_chunked_seq_state_update",
         [](at::Tensor& k, at::Tensor& u, at::Tensor& w, std::optional<at::Tensor>& initial_state, at::Tensor& state,
            std::optional<at::Tensor>& final_state, std::optional<at::Tensor> gate, const std::string& compiled_dims,
            std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> cu_chunks, std::optional<int> total_chunks,
            uint32_t chunk_size) {
+            OnDevice dev(k);
             gdn_cuda::bf16_chunked_seq_state_update(k, u, w, initial_state, state, final_state, gate, compiled_dims,
-                                                    current_stream(), cu_seqlens, cu_chunks, total_chunks, chunk_size);
+                                                    dev.stream(), cu_seqlens, cu_chunks, total_chunks, chunk_size);
         },
         py::arg("k"), py::arg("u"), py::arg("w"), py::arg("initial_state"), py::arg("state"), py::arg("final_state"),
         py::arg("gate") = py::none(), py::arg("compiled_dims") = "t", py::arg("cu_seqlens") = py::none(),
@@ -86,7 +125,8 @@ PYBIND11_MODULE(gdn_cuda, m) {
         [](at::Tensor& q, at::Tensor& state, at::Tensor& k, at::Tensor& u, at::Tensor& o, std::optional<at::Tensor> gate,
            std::optional<float> scale, const std::string& compiled_dims, std::optional<at::Tensor> cu_seqlens,
            std::optional<at::Tensor> chunk_indices, std::optional<at::Tensor> cu_chunks, uint32_t chunk_size) {
-            gdn_cuda::bf16_gdn_chunked_compute_O(q, state, k, u, o, gate, scale, compiled_dims, current_stream(),
+            OnDevice dev(q);
+            gdn_cuda::bf16_gdn_chunked_compute_O(q, state, k, u, o, gate, scale, compiled_dims, dev.stream(),
                                                  cu_seqlens, chunk_indices, cu_chunks, std::nullopt, chunk_size);
         },
         py::arg("q"), py::arg("state"), py::arg("k"), py::arg("u"), py::arg("o"), py::arg("gate") = py::none(),
@@ -98,8 +138,9 @@ PYBIND11_MODULE(gdn_cuda, m) {
         "chunk_local_cumsum_bf16",
         [](at::Tensor& input, at::Tensor& output, int batch_size, int seq_len, int num_heads, bool head_first,
            std::optional<at::Tensor> cu_seqlens, std::optional<at::Tensor> chunk_indices) {
+            OnDevice dev(input);
             gdn_cuda::chunk_local_cumsum_bf16(input, output, batch_size, seq_len, num_heads, head_first, cu_seqlens,
-                                              chunk_indices, current_stream());
+                                              chunk_indices, dev.stream());
         },
         py::arg("input"), py::arg("output"), py::arg("batch_size"), py::arg("seq_len"), py::arg("num_heads"),
         py::arg("head_first") = false, py::arg("cu_seqlens") = py::none(), py::arg("chunk_indices") = py::none(),
@@ -108,7 +149,8 @@ PYBIND11_MODULE(gdn_cuda, m) {
     m.def(
         "transpose_to_mn_major",
         [](at::Tensor& input, uint32_t alignment) {
-            return gdn_cuda::transpose_to_mn_major(input, current_stream(), alignment);
+            OnDevice dev(input);
+            return gdn_cuda::transpose_to_mn_major(input, dev.stream(), alignment);
         },
         py::arg("input"), py::arg("alignment") = 16u, "Transpose the last two dims to a stride(-2) == 1 layout.");
 

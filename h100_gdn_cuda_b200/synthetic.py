@@ -99,9 +99,9 @@ def lognormal_lengths(num_seqs: int, total: int, lo: int, hi: int, seed: int = 0
 
 
 def varlen_inputs(lens, kh: int, vh: int, d: int, seed: int = 0, with_state: bool = True,
-                  dtype=torch.bfloat16, mild_gate: bool = False):
+                  dtype=torch.bfloat16, mild_gate: bool = False, normalize: bool = True):
     N = sum(lens)
-    p = prefill_inputs(1, N, kh, vh, d, seed, with_state=False, dtype=dtype, mild_gate=mild_gate)
+    p = prefill_inputs(1, N, kh, vh, d, seed, with_state=False, dtype=dtype, mild_gate=mild_gate, normalize=normalize)
     cu = [0]
     for n in lens:
         cu.append(cu[-1] + n)

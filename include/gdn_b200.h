@@ -104,6 +104,17 @@ int gdn_version(void);
  * the reference, whose device asserts trap (kernels/common/common.hpp:485-493). */
 int gdn_device_status(int device, int* status_out);
 
+/* Self-test of the bounded waits every kernel of this library uses (no counterpart in the
+ * reference, whose waits spin without a limit, kernels/common/sm90_utils.cuh): launches one warp
+ * that waits on a barrier nothing will ever complete, with a limit of `limit_cycles` SM clock
+ * cycles (1 .. 1e9).  The wait gives up, the kernel sets the device status word to 7 and returns;
+ * gdn_device_status() then reads 7 and the context stays usable.  Status codes of the product
+ * kernels: 1 recurrent, 2 WY/UT and chunk-parallel stage, 4 state/output stage, 6 other prefill
+ * stages.  A kernel whose wait gave up writes none of its outputs where that is cheap to arrange
+ * (recurrent, whole-layer prefill); the entry point has long returned GDN_OK by then, so the
+ * status word, not a return code, is how GDN_ERR_DEVICE conditions are observed. */
+int gdn_selftest_bounded_wait(int64_t limit_cycles, gdn_stream_t stream);
+
 /* Replaces Compiler::build (csrc/jit/compiler.hpp:82-103): compiles `source`, a complete CUDA
  * translation unit that may include the library's kernel headers ("kernels/...") and defines
  * an extern "C" kernel, to an sm_100a cubin, or finds it in the on-disk cache
@@ -150,7 +161,14 @@ int gdn_transpose_mn_major(const void* input, void* output, int32_t elem_size, i
  *   store_step_state != 0 : state_out holds one state per token, addressed
  *                           token_index*stride_seq + head*stride_head (token_index =
  *                           b*seq_len + t, or the packed token index); otherwise one per
- *                           sequence.  state_out may alias state_in when not storing steps. */
+ *                           sequence.  state_out may alias state_in when not storing steps.
+ *   gating_a.ptr != NULL  : the gating of the layer is computed inside the kernel from its raw
+ *                           projections (what gdn_fused_gating does, csrc/apis/gdn_forward.cpp:208-229,
+ *                           without the extra launch and without rounding beta and the gate to bf16):
+ *                               beta = sigmoid(gating_b),  g = -exp(A_log[h]) * softplus(gating_a + dt_bias[h])
+ *                           gating_a / gating_b are per-token scalars like beta / gate (same dtype for
+ *                           both, bf16 or f32); A_log and dt_bias are contiguous vectors of num_v_heads
+ *                           entries of that dtype.  `beta` and `gate` are then ignored. */
 typedef struct {
     GdnShape shape;
     GdnTokenTensor q, k, v, out;
@@ -160,6 +178,10 @@ typedef struct {
     float scale;
     int32_t is_qk_norm;
     int32_t store_step_state;
+    /* fused gating (all four given, or gating_a.ptr == NULL) */
+    GdnTokenScalar gating_a, gating_b;
+    const void* A_log;
+    const void* dt_bias;
 } GdnRecurrentArgs;
 int gdn_recurrent_forward(const GdnRecurrentArgs* args, gdn_stream_t stream);
 
@@ -228,8 +250,13 @@ typedef struct {
     void* workspace;
     size_t workspace_bytes;
     /* Optional profiling aid: NULL, or three cudaEvent_t recorded on `stream` before the first
-     * kernel, between the WY/UT kernel and the state/output kernel, and after the last. */
+     * kernel, between the chunk-parallel kernel and the state/output kernel, and after the last. */
     void* const* stage_events;
+    /* != 0: q and k are L2-normalised per head (x * rsqrt(sum x^2 + 1e-6)) inside the kernels, as
+     * gdn_recurrent_forward does; the tiles are not touched, the factors enter the gate vectors.
+     * (The reference lists this as future work, README.md:113.)  Adds 512 bytes of workspace per
+     * (chunk, k-head); gdn_chunked_forward_workspace_bytes() always includes them. */
+    int32_t is_qk_norm;
 } GdnChunkedArgs;
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* shape);
 int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
@@ -247,8 +274,8 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  * ignored; inputs and outputs are passed as usual.
  *
  *   - Limit: gdn_chunked_forward_workspace_bytes(&args->shape) must not exceed
- *     GDN_STATIC_SCRATCH_BYTES (48 MiB + 8 KiB + 256 bytes).  The scratch holds 24 KiB per 64-token
- *     chunk and v-head (384 bytes per token and v-head),
+ *     GDN_STATIC_SCRATCH_BYTES (49 MiB + 8.5 KiB).  The scratch holds 24 KiB per 64-token
+ *     chunk and v-head (384 bytes per token and v-head) plus 512 bytes per chunk and k-head,
  *     so with whole chunks that is tokens * num_v_heads <= 131072, for example 4096
  *     tokens of 32 v-heads (less where long sequences of few heads add their segment states).
  *     Larger problems are refused with GDN_ERR_WORKSPACE and a message.
@@ -263,7 +290,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
  *     left there.  Nothing in it has to start at zero (every element that is read has been
  *     written earlier in the same call), but two calls whose kernels overlap on the GPU -
  *     different streams, or different host threads - race on it: serialise them. */
-#define GDN_STATIC_SCRATCH_BYTES ((48u << 20) + 8192u + 256u)
+#define GDN_STATIC_SCRATCH_BYTES ((49u << 20) + 8192u + 512u)
 int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* args, gdn_stream_t stream);
 
 #ifdef __cplusplus

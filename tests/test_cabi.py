@@ -73,16 +73,17 @@ def test_workspace_bytes(lib):
     three fp32 states per chain and segment on top (the segmented state propagation)."""
     from h100_gdn_cuda_b200 import api
     unit = 64 * 128 * 2 + 64 * 64 * 2
-    assert api.chunked_forward_workspace_bytes(4, 4096, 32) == 4 * 64 * 32 * unit + 256
-    assert api.chunked_forward_workspace_bytes(1, 65, 2) == 2 * 2 * unit + 256        # ragged tail: whole chunks
+    norm = 512  # q/k norm factors per (chunk, k-head); the size queries below are made with one k-head
+    assert api.chunked_forward_workspace_bytes(4, 4096, 32, num_k_heads=1) == 4 * 64 * (32 * unit + norm) + 256
+    assert api.chunked_forward_workspace_bytes(1, 65, 2, num_k_heads=1) == 2 * (2 * unit + norm) + 256   # ragged tail: whole chunks
     # packed mode counts chunks, not tokens; 256 bytes more hold the sequences ordered by length
-    assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True) == 6 * 4 * unit + 256 + 256
-    assert api.chunked_forward_workspace_bytes(1, 0, 4, total_tokens=200, total_chunks=4, packed=True) == 4 * 4 * unit + 256
+    assert api.chunked_forward_workspace_bytes(3, 0, 4, total_tokens=200, total_chunks=6, packed=True, num_k_heads=1) == 6 * (4 * unit + norm) + 256 + 256
+    assert api.chunked_forward_workspace_bytes(1, 0, 4, total_tokens=200, total_chunks=4, packed=True, num_k_heads=1) == 4 * (4 * unit + norm) + 256
     # B=2, T=131072, 4 v-heads: 8 chains -> 18 segments
-    long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4)
-    assert long_ctx == 2 * 2048 * 4 * unit + 256 + 8 * 18 * 3 * 128 * 128 * 4 + 256
+    long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4, num_k_heads=1)
+    assert long_ctx == 2 * 2048 * (4 * unit + norm) + 256 + 8 * 18 * 3 * 128 * 128 * 4 + 256
     # 128 chains: never segmented
-    assert api.chunked_forward_workspace_bytes(4, 131072, 32) == 4 * 2048 * 32 * unit + 256
+    assert api.chunked_forward_workspace_bytes(4, 131072, 32, num_k_heads=1) == 4 * 2048 * (32 * unit + norm) + 256
 
 
 def test_segment_plan_heuristic():
@@ -115,3 +116,26 @@ def test_segment_plan_heuristic():
     assert rows[5][0] == 3 and rows[5][0] * rows[5][1] >= 97
     assert rows[6] == (1, 2048)          # packed mode: not segmented
     assert rows[7] == (1, 40)            # too short for 32-chunk segments
+
+
+def test_state_alignment_is_checked_on_the_host(lib):
+    """States are accessed 16 bytes at a time: a misaligned pointer or a stride that is not a multiple of
+    8 elements is refused with GDN_ERR_INVALID before anything touches a device."""
+    from h100_gdn_cuda_b200 import _cabi as cabi, api
+    tok = cabi.TokenTensor(0x10000, 64 * 4 * 128, 4 * 128, 128)
+    sc = cabi.TokenScalar(0x20000, cabi.GDN_BF16, 64 * 4, 4, 1)
+    for state in (cabi.State(0x30002, 4 * 128 * 128, 128 * 128), cabi.State(0x30000, 4 * 128 * 128 + 4, 128 * 128)):
+        a = cabi.ChunkedArgs()
+        a.shape = api._shape(1, 64, 64, 4, 4, 128, 128)
+        a.q = a.k = a.v = a.out = tok
+        a.beta = sc
+        a.initial_state = state
+        assert lib.gdn_chunked_forward(ctypes.byref(a), None) == -1
+        assert b"initial_state" in lib.gdn_last_error()
+        s = cabi.SeqStateArgs()
+        s.shape = a.shape
+        s.k = s.u = s.w = tok
+        s.final_state = state
+        s.chunk_states = 0x40000
+        assert lib.gdn_seq_state_update(ctypes.byref(s), None) == -1
+        assert b"final_state" in lib.gdn_last_error()

@@ -37,11 +37,17 @@ def test_jit_recurrent_equals_prebuilt(gdn, monkeypatch, tmp_path, use_nvrtc):
     o_ref, s_ref = _run(gdn, p, beta, g)
     monkeypatch.setenv("GDN_JIT_RECURRENT", "1")
     monkeypatch.setenv("JIT_USE_NVRTC", use_nvrtc)
-    o, s = _run(gdn, p, beta, g)
-    assert torch.equal(o, o_ref) and torch.equal(s, s_ref)
-    assert any(d.startswith("kernel.recurrent_dk128.") for d in os.listdir(tmp_path))
-    o2, s2 = _run(gdn, p, beta, g)  # second call: module already loaded
-    assert torch.equal(o2, o_ref)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    gdn.init(ROOT, cuda_home)  # the library reads its environment switches at init, not per call
+    try:
+        o, s = _run(gdn, p, beta, g)
+        assert torch.equal(o, o_ref) and torch.equal(s, s_ref)
+        assert any(d.startswith("kernel.recurrent_dk128.") for d in os.listdir(tmp_path))
+        o2, s2 = _run(gdn, p, beta, g)  # second call: module already loaded
+        assert torch.equal(o2, o_ref)
+    finally:
+        monkeypatch.delenv("GDN_JIT_RECURRENT")
+        gdn.init(ROOT, cuda_home)
 
 
 def test_head_dim_without_prebuilt_kernel(gdn):

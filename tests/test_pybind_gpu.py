@@ -25,7 +25,7 @@ def dev(d):
 def test_surface(mods):
     _, ext = mods
     for name in ("init", "chunked_forward", "recurrent_forward", "fused_gdn_gating", "bf16_gdn_compute_u_w",
-                 "bf16_chunked_seq_state_update", "bf16_gdn_chunked_compute_O", "chunk_local_cumsum_bf16",
+                 "bf16_chunked_seq_state_update", "bf16_gdn_chunked_compute_O", "bf16_gdn_recurrent", "chunk_local_cumsum_bf16",
                  "transpose_to_mn_major", "InferenceMode"):
         assert hasattr(ext, name)
     assert int(ext.Prefill) == 0 and int(ext.Decode) == 1 and int(ext.SpecVerify) == 2
@@ -102,3 +102,68 @@ def test_errors_raise(mods):
     big = torch.zeros(1, 64, 1, 320, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         ext.chunked_forward(big, big, big, p["beta"], p["g"])
+
+
+@pytest.mark.parametrize("d,varlen", [(64, False), (100, False), (64, True)])
+def test_low_level_chain_small_head_dims_vs_oracle(mods, d, varlen):
+    """The reference's per-stage chain (compute_u_w -> seq_state_update -> compute_O) at head dims below
+    128, through the pybind module, against the fp32 token recurrence.  Tolerance of the prefill tests:
+    relative Frobenius <= 1e-2, max-abs <= 5e-2 * max|ref|."""
+    from oracle import gdn_oracle as O
+    _, ext = mods
+    if varlen:
+        lens = [65, 1, 130]
+        p = synthetic.varlen_inputs(lens, 2, 4, d, seed=40 + d, mild_gate=True)
+        cu = p["cu_seqlens"]
+        nck = p["total_chunks"]
+    else:
+        p = synthetic.prefill_inputs(2, 130, 2, 4, d, seed=40 + d, mild_gate=True)
+        cu, nck = None, 3
+    gc = O.chunk_local_cumsum_ref(p["g"], cu)
+    pd = dev(p)
+    g = gc.cuda()
+    kw_uw = dict(cu_seqlens=pd["cu_seqlens"], chunk_indices=pd["chunk_indices"]) if varlen else {}
+    kw_st = dict(cu_seqlens=pd["cu_seqlens"], cu_chunks=pd["cu_chunks"], total_chunks=nck) if varlen else {}
+    kw_o = dict(cu_seqlens=pd["cu_seqlens"], chunk_indices=pd["chunk_indices"], cu_chunks=pd["cu_chunks"]) if varlen else {}
+    u, w = torch.empty_like(pd["v"]), torch.empty_like(pd["v"])
+    ext.bf16_gdn_compute_u_w(pd["k"], pd["v"], u, w, pd["beta"], g, **kw_uw)
+    state = torch.empty((nck, 4, d, d) if varlen else (2, nck, 4, d, d), dtype=torch.bfloat16, device="cuda")
+    final = torch.empty_like(pd["state"])
+    ext.bf16_chunked_seq_state_update(pd["k"], u, w, pd["state"], state, final, g, **kw_st)
+    o = torch.empty_like(pd["v"])
+    ext.bf16_gdn_chunked_compute_O(pd["q"], state, pd["k"], u, o, g, **kw_o)
+    o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), p["beta"].float(), p["g"],
+                                   p["state"].float(), cu_seqlens=None if cu is None else cu.tolist())
+    for x, ref, what in ((o, o_ref, "o"), (final, s_ref, "final state")):
+        x = x.float().cpu()
+        assert O.rel_fro(x, ref) <= 1e-2 and O.max_abs_over_max(x, ref) <= 5e-2, what
+
+
+def test_bf16_gdn_recurrent_on_caller_tensors(mods):
+    """gdn_cuda::bf16_gdn_recurrent: same bits as recurrent_forward, written into the caller's tensors."""
+    py, ext = mods
+    d = dev(synthetic.decode_inputs(4, 3, 2, 4, 128, seed=8))
+    beta, gate = py.fused_gdn_gating(d["A_log"], d["dt_bias"], d["a"], d["b"])
+    o1, s1 = py.recurrent_forward(d["q"], d["k"], d["v"], d["state"], beta, gate, None, None, 1, True, 0.25)
+    out, fin = torch.empty_like(d["v"]), torch.empty_like(d["state"])
+    ext.bf16_gdn_recurrent(d["q"], d["k"], d["v"], d["state"], fin, out, gate, beta, "t", None, None, False, True, 0.25)
+    assert torch.equal(o1, out) and torch.equal(s1, fin)
+    steps = torch.empty(4, 3, 4, 128, 128, dtype=torch.bfloat16, device="cuda")
+    ext.bf16_gdn_recurrent(d["q"], d["k"], d["v"], d["state"], steps, out, gate, beta, store_step_state=True, is_qk_norm=True,
+                           scale=0.25)
+    assert torch.equal(steps[:, -1], fin)
+    with pytest.raises(RuntimeError):
+        ext.bf16_gdn_recurrent(d["q"][..., :100], d["k"][..., :100], d["v"], d["state"], fin, out, gate, beta)
+
+
+def test_extensions_same_bits(mods):
+    py, ext = mods
+    d = dev(synthetic.decode_inputs(4, 1, 2, 4, 128, seed=9))
+    gating = (d["A_log"], d["dt_bias"], d["a"], d["b"])
+    o1, s1 = py.recurrent_forward(d["q"], d["k"], d["v"], d["state"], None, None, inference_mode=1, is_qk_norm=True, gating=gating)
+    o2, s2 = ext.recurrent_forward(d["q"], d["k"], d["v"], d["state"], None, None, inference_mode=1, is_qk_norm=True, gating=gating)
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    p = dev(synthetic.prefill_inputs(1, 200, 2, 4, 128, seed=3, mild_gate=True, normalize=False))
+    o1, s1 = py.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"], is_qk_norm=True)
+    o2, s2 = ext.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"], is_qk_norm=True)
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
