@@ -10,16 +10,23 @@ every rank processes its own batch of that size - sequences are independent, so 
 shards by sequence with no collective - and `value` is the total over ranks (weak scaling).
 
 The printed JSON line carries:
-  value      prefill tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  value      prefill tokens/s with inputs resident in HBM (CUDA events, max over ranks; the K-step
+             loop is repeated and the median repeat is reported, min and max beside it)
   e2e        the same through the public API from pinned HOST buffers: host->device copies of
              q, k, v, beta, gate and the state and the device->host copy of O and the final
              state are inside the timed region
-  roofline   for the dominant kernel (the longer of the two prefill launches), timed live with CUDA
-             events, against the HBM roof that bounds both of them
-  decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, fused gating) and its
-             HBM roofline fraction
+  roofline   the whole prefill step against the tensor-core roof: algorithmic FLOPs (11.709 MFLOP per
+             64-token chunk and v-head) / step time against the measured bf16 peak, with the byte view
+             (24 768 B per token + the states against the measured copy bandwidth) and the two kernels'
+             own figures beside it
+  decode     decode tokens/s of `recurrent_forward` (B=256, T=1, qk-norm, gating fused in the kernel:
+             one launch per step) and its HBM roofline fraction
+  spec_verify   speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, qk-norm, fused gating)
+  decode_sharded  a decode batch of B=1024 split by sequence over the N ranks (strong scaling)
   packed     packed (varlen) prefill of 16 sequences with log-normal lengths, 32768 tokens per GPU
   long_context  the B=2, T=131072 layer with the value heads sharded over the N ranks (strong scaling)
+  parity     N > 1 only: one shared-seed problem, every rank computes its head shard on its GPU, the
+             shards are gathered with NCCL and rank 0 compares them with the CPU oracle (untimed)
   cpu_baseline  the fp32 CPU token recurrence (the oracle) on a bounded sample, rank 0, N=1
 
 `--impl reference` times only that CPU recurrence (the reference library's own sm_90a kernels
@@ -30,6 +37,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -42,57 +50,73 @@ sys.path.insert(0, ROOT)
 
 CFG = dict(B=4, T=4096, kh=16, vh=32, d=128)
 DECODE = dict(B=256, T=1, kh=16, vh=32, d=128)
+SPEC = dict(B=64, T=4)
+DECODE_SHARDED_B = 1024
 CHUNK = 64
 WORKLOAD = "padded chunked prefill B=4 T=4096 kh=16 vh=32 dk=dv=128 chunk=64 per GPU"
+REF_SAMPLE_TOKENS = 1024
+REPEATS = 5  # the K-step loop is timed this many times; the median is reported
 
 
 def flops_per_unit(d: int, c: int = CHUNK) -> float:
-    """All contractions of one (64-token chunk, v-head): 2C(5Cd + 3dd) + (2/3)C^3."""
+    """Algorithmic work of one (64-token chunk, v-head), every contraction counted dense and per v-head:
+    K K^T, Q K^T, T V, T K, P U_new (2CCd each), W S^T, U_new^T K, Q S^T (2Cdd each), the triangular
+    inverse (2/3 C^3):  2C(5Cd + 3dd) + (2/3)C^3 = 11.709 MFLOP at d = 128."""
     return 2.0 * c * (5 * c * d + 3 * d * d) + (2.0 / 3.0) * c ** 3
 
 
+def zp_kernel_flops_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
+    """What gdn_zp_kernel executes per (chunk, v-head): K K^T and Q K^T once per k-head (2CCd each, shared
+    by vh/kh v-heads), Z = (dT)^T K (2CCd), PT = P T (2CCC), the inverse (2/3 C^3)."""
+    return 2.0 * c * c * d * (2.0 * kh / vh + 1.0) + 2.0 * c ** 3 + (2.0 / 3.0) * c ** 3
+
+
 def seq_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
-    """Contractions done by the state/output kernel: P U_new (2CCd) and
-    W S^T, Q S^T, U_new^T K (2Cdd each)."""
-    return 2.0 * c * (c * d + 3 * d * d)
+    """What gdn_fused_seq_kernel executes per (chunk, v-head): S K^T, S Q^T, R Z (2Cdd each), R PT^T (2CCd)."""
+    return 2.0 * c * (3 * d * d + c * d)
 
 
-def uw_kernel_flops_per_unit(d: int, c: int = CHUNK) -> float:
-    """K K^T, Q K^T, T V, T' K (2CCd each) and the triangular inverse."""
-    return 2.0 * c * (4 * c * d) + (2.0 / 3.0) * c ** 3
+def prefill_min_bytes(tokens: int, seqs: int, kh: int, vh: int, d: int) -> float:
+    """HBM bytes no implementation can avoid: q, k, v in and o out (bf16), beta bf16 and gate fp32 per
+    token and v-head, plus the bf16 state read and written once per sequence."""
+    return tokens * (2.0 * (2 * kh * d + 2 * vh * d) + vh * (2 + 4)) + seqs * 2.0 * vh * d * d * 2
 
 
-# Algorithmic HBM bytes of the two prefill kernels per (64-token chunk, v-head) unit at d = 128:
-#   gdn_uw_kernel        : K, Q tiles 16 KB each per k-head (shared by the vh/kh v-heads of a group),
-#                          V tile 16 KB in; U, W 16 KB each and P 8 KB out
-#   gdn_fused_seq_kernel : U, W, P 40 KB and K, Q (shared as above) in; O 16 KB out
-# Both sit well below the ridge of the measured peaks (1636 TFLOP/s / 6546 GB/s = 250 FLOP/B):
-# 4.37 MFLOP / 72 KB = 61 FLOP/B and 7.34 MFLOP / 72 KB = 102 FLOP/B at vh/kh = 2, so HBM is the
-# roof that bounds them.
-def uw_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
+# HBM bytes the two kernels of this design move per (chunk, v-head) unit at d = 128 (algorithmic):
+#   gdn_zp_kernel        : K, Q tiles 16 KB each per k-head (shared by the vh/kh v-heads of a group) in;
+#                          Z 16 KB and PT 8 KB out
+#   gdn_fused_seq_kernel : V 16 KB, Z, PT 24 KB and K, Q (shared as above) in; O 16 KB out
+def zp_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
     tile = c * d * 2
-    return 2 * tile * kh / vh + tile + 2 * tile + c * c * 2
+    return 2 * tile * kh / vh + tile + c * c * 2
 
 
 def seq_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float:
     tile = c * d * 2
-    return 2 * tile + c * c * 2 + 2 * tile * kh / vh + tile
+    return tile + (tile + c * c * 2) + 2 * tile * kh / vh + tile
 
 
 # DRAM read + write bytes per launch seen by one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum), divided by the units that launch processed.  Traffic is proportional
 # to the units (every CTA streams its own tiles), so a full launch is units x this figure.
-#   gdn_uw_kernel        : B=2 T=4096 vh=32 capture, 135.84 MB read + 116.15 MB written, 4096 units
-#   gdn_fused_seq_kernel : same capture, 238.15 MB read + 50.26 MB written, 4096 units
-#   gdn_recurrent_kernel : B=128 capture, 136.37 MB read + 87.44 MB written, 128 sequence-tokens
+# The captures and their commands are summarised under profiles/.
+#   gdn_zp_kernel        : B=2 T=4096 vh=32 capture, 4096 units
+#   gdn_fused_seq_kernel : same capture, 4096 units
+#   gdn_recurrent_kernel : B=128 capture (gating fused), 128 sequence-tokens
 # (written data still in L2 when a launch ends is not counted by the DRAM counters)
-NCU_UW_TRAFFIC_PER_UNIT = (135.840512e6 + 116.147456e6) / 4096
-NCU_FUSED_TRAFFIC_PER_UNIT = (238.145280e6 + 50.258944e6) / 4096
-NCU_DECODE_TRAFFIC_PER_TOKEN = (136.370432e6 + 87.435776e6) / 128
+NCU_ZP_TRAFFIC_PER_UNIT = (68.746752e6 + 43.661312e6) / 4096
+NCU_FUSED_TRAFFIC_PER_UNIT = (238.145792e6 + 46.908928e6) / 4096
+NCU_DECODE_TRAFFIC_PER_TOKEN = (136.383488e6 + 86.052864e6) / 128
 
 
 def decode_bytes_per_token(kh, vh, d) -> float:
+    """State read + written (2 * vh * d * d bf16), q, k, v, o, and beta, gate (bf16) per v-head."""
     return vh * (2 * d * d * 2) + 2 * (2 * kh * d + 2 * vh * d) + vh * 4
+
+
+def spec_bytes_per_seq(T, kh, vh, d) -> float:
+    """Speculative verify, one state per sequence out: state read once and written once, T tokens of q, k, v, o."""
+    return vh * (2 * d * d * 2) + T * (2 * (2 * kh * d + 2 * vh * d) + vh * 4)
 
 
 def load_peaks():
@@ -155,15 +179,20 @@ class ClockSampler:
                     samples=len(sm))
 
 
+def _cpu_sample(sample_tokens: int):
+    """Inputs of the CPU recurrence: one sequence of `sample_tokens` tokens of the prefill configuration."""
+    from h100_gdn_cuda_b200 import synthetic
+    p = synthetic.prefill_inputs(1, sample_tokens, CFG["kh"], CFG["vh"], CFG["d"], seed=0)
+    return [p[k].float() for k in ("q", "k", "v", "beta")] + [p["g"], p["state"].float()]
+
+
 def cpu_recurrence_tokens_per_s(sample_tokens: int, repeats: int = 1):
     """fp32 CPU token recurrence (the oracle) on one sequence of `sample_tokens` tokens of the
     prefill configuration; returns (tokens/s, threads, description)."""
     from oracle import gdn_oracle as O
-    from h100_gdn_cuda_b200 import synthetic
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    p = synthetic.prefill_inputs(1, sample_tokens, CFG["kh"], CFG["vh"], CFG["d"], seed=0)
-    args = [p[k].float() for k in ("q", "k", "v", "beta")] + [p["g"], p["state"].float()]
+    args = _cpu_sample(sample_tokens)
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
@@ -175,31 +204,36 @@ def cpu_recurrence_tokens_per_s(sample_tokens: int, repeats: int = 1):
 
 def run_reference(args):
     """The reference arm: the CPU recurrence, the only implementation of the path that can run
-    on this box (rank 0 only)."""
+    on this box (rank 0 only).  Each step is a bounded sample of the workload, one sequence of
+    REF_SAMPLE_TOKENS tokens; the figure is a per-token throughput."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 1024
     from oracle import gdn_oracle as O
-    from h100_gdn_cuda_b200 import synthetic
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    p = synthetic.prefill_inputs(1, sample, CFG["kh"], CFG["vh"], CFG["d"], seed=0)
-    a = [p[k].float() for k in ("q", "k", "v", "beta")] + [p["g"], p["state"].float()]
+    a = _cpu_sample(REF_SAMPLE_TOKENS)
     for _ in range(args.warmup):
         O.recurrent_ref(*a)
-    t0 = time.perf_counter()
+    per_step = []
     for _ in range(args.steps):
+        t0 = time.perf_counter()
         O.recurrent_ref(*a)
-    dt = (time.perf_counter() - t0) / args.steps
-    tps = sample / dt
+        per_step.append(time.perf_counter() - t0)
+    dt = sum(per_step) / len(per_step)
+    tps = REF_SAMPLE_TOKENS / dt
+    what = ("each step = ONE sequence of %d tokens (B=1 x T=%d) of the prefill config kh=16 vh=32 dk=dv=128, "
+            "fp32 torch token recurrence on %d host threads; 1/16 of the GPU arm's step, so the ratio of the two "
+            "arms is a per-token throughput ratio" % (REF_SAMPLE_TOKENS, REF_SAMPLE_TOKENS, threads))
     line = {
         "impl": "reference", "metric": "prefill_tokens_per_s", "value": tps, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "ms_per_step_min": min(per_step) * 1e3, "ms_per_step_max": max(per_step) * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sharding": "rank 0 only", "l2": "not applicable (CPU)"},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": "each step = B=1 x T=%d of the prefill config, fp32 torch token recurrence" % sample},
+        "config": {"workload": "CPU sample of the padded chunked prefill config: B=1 T=%d kh=16 vh=32 dk=dv=128 per step "
+                               "(the GPU arm's step is B=4 T=4096)" % REF_SAMPLE_TOKENS,
+                   "sharding": "rank 0 only", "l2": "not applicable (CPU)"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -242,10 +276,9 @@ def run_only(args, gdn, synthetic, dev, peaks):
         B = args.batch or 128
         p = synthetic.decode_inputs(B, 1, kh, vh, d, seed=0)
         t = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in p.items()}
-        beta, gate = gdn.fused_gdn_gating(t["A_log"], t["dt_bias"], t["a"], t["b"])
         states = [t["state"], t["state"].clone()]
-        run = lambda i: gdn.recurrent_forward(t["q"], t["k"], t["v"], states[i & 1], beta, gate, inference_mode=1,
-                                              is_qk_norm=True)
+        run = lambda i: gdn.recurrent_forward(t["q"], t["k"], t["v"], states[i & 1], None, None, inference_mode=1,
+                                              is_qk_norm=True, gating=(t["A_log"], t["dt_bias"], t["a"], t["b"]))
         work, unit = B, "tokens/s"
     for i in range(args.warmup):
         run(i)
@@ -258,6 +291,8 @@ def run_only(args, gdn, synthetic, dev, peaks):
     ms = e0.elapsed_time(e1) / args.steps
     print(json.dumps({"only": args.only, "batch": B, "ms_per_step": ms, "value": work / (ms * 1e-3), "unit": unit,
                       "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 
 
 def main():
@@ -280,7 +315,7 @@ def main():
         return run_reference(args)
 
     import h100_gdn_cuda_b200 as gdn
-    from h100_gdn_cuda_b200 import build, synthetic
+    from h100_gdn_cuda_b200 import build, sharding, synthetic
     import torch.distributed as dist
 
     rank = int(os.environ.get("RANK", "0"))
@@ -329,13 +364,32 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(step, steps, repeats=REPEATS):
+        """`repeats` times: barrier, `steps` calls of step(i) between two events, barrier; every figure is the
+        maximum over the ranks.  Returns (median ms per step, [ms per step of every repeat])."""
+        out = []
+        for _ in range(repeats):
+            barrier()
+            e0.record()
+            for i in range(steps):
+                step(i)
+            e1.record()
+            barrier()
+            out.append(max_over_ranks(e0.elapsed_time(e1) / steps))
+        return statistics.median(out), out
+
+    def spread(xs):
+        return {"repeats": len(xs), "ms_min": min(xs), "ms_max": max(xs)}
+
     from h100_gdn_cuda_b200 import api as gdn_api
-    ws = torch.empty(gdn_api.chunked_forward_workspace_bytes(B, T, vh), dtype=torch.uint8, device=dev)
+    ws = torch.empty(gdn_api.chunked_forward_workspace_bytes(B, T, vh, num_k_heads=kh), dtype=torch.uint8, device=dev)
     stage_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     for e in stage_ev:
         e.record()
 
-    def step_resident(events=None):
+    def step_resident(i=0, events=None):
         return gdn.chunked_forward(devt["q"], devt["k"], devt["v"], devt["beta"], devt["g"], None, devt["state"],
                                    _workspace=ws, _stage_events=events)
 
@@ -346,21 +400,15 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    uw_ms, seq_ms = 0.0, 0.0
-    e0.record()
+    ms_res, ms_res_all = timed(step_resident, args.steps)
+    # per-kernel durations: the same steps again with events between the two kernels
+    zp_ms, seq_ms = 0.0, 0.0
     for _ in range(args.steps):
-        step_resident()
-    e1.record()
-    barrier()
-    ms_res = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    # per-kernel durations: same steps again with events between the two kernels
-    for _ in range(args.steps):
-        step_resident(stage_ev)
+        step_resident(0, stage_ev)
         torch.cuda.synchronize()
-        uw_ms += stage_ev[0].elapsed_time(stage_ev[1])
+        zp_ms += stage_ev[0].elapsed_time(stage_ev[1])
         seq_ms += stage_ev[1].elapsed_time(stage_ev[2])
-    uw_ms /= args.steps
+    zp_ms /= args.steps
     seq_ms /= args.steps
 
     # ---------------- end to end from host buffers
@@ -412,70 +460,86 @@ def main():
     ms_e2e = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     h2d = sum(host[k].numel() * host[k].element_size() for k in host)
     d2h = out_host.numel() * 2 + st_host.numel() * 2
+    del stages
 
-    # ---------------- decode (B=256, T=1): state 268 MB per step, larger than L2
+    # ---------------- decode (B=256, T=1): state 268 MB per step, larger than L2.  beta and the gate are
+    # computed inside the kernel from A_log, dt_bias, a, b: one launch per step.
     dB = DECODE["B"]
     dp = synthetic.decode_inputs(dB, 1, kh, vh, d, seed=100 + rank)
     dd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in dp.items()}
     states = [dd["state"].clone() for _ in range(2)]
+    gating = (dd["A_log"], dd["dt_bias"], dd["a"], dd["b"])
 
     def step_decode(i):
-        beta, gate = gdn.fused_gdn_gating(dd["A_log"], dd["dt_bias"], dd["a"], dd["b"])
-        return gdn.recurrent_forward(dd["q"], dd["k"], dd["v"], states[i & 1], beta, gate, inference_mode=1,
-                                     is_qk_norm=True)
+        return gdn.recurrent_forward(dd["q"], dd["k"], dd["v"], states[i & 1], None, None, inference_mode=1,
+                                     is_qk_norm=True, gating=gating)
 
     for i in range(5):
         step_decode(i)
-    barrier()
     dsteps = max(args.steps, 20)
-    e0.record()
-    for i in range(dsteps):
-        step_decode(i)
-    e1.record()
-    barrier()
-    ms_dec = max_over_ranks(e0.elapsed_time(e1) / dsteps)
-    # the recurrent kernel alone (gating excluded) for its roofline
-    beta, gate = gdn.fused_gdn_gating(dd["A_log"], dd["dt_bias"], dd["a"], dd["b"])
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(dsteps):
-        gdn.recurrent_forward(dd["q"], dd["k"], dd["v"], states[i & 1], beta, gate, inference_mode=1, is_qk_norm=True)
-    e1.record()
-    torch.cuda.synchronize()
-    ms_dec_kernel = e0.elapsed_time(e1) / dsteps
+    ms_dec, ms_dec_all = timed(step_decode, dsteps)
+    del states
+
+    # ---------------- speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, one state per sequence out)
+    sB, sT = SPEC["B"], SPEC["T"]
+    sp = synthetic.decode_inputs(sB, sT, kh, vh, d, seed=300 + rank, spec=True)
+    sd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in sp.items()}
+    s_states = [sd["state"].clone() for _ in range(4)]  # 4 x 67 MB, cycled: larger than L2 between reuses
+    s_gating = (sd["A_log"], sd["dt_bias"], sd["a"], sd["b"])
+
+    def step_spec(i):
+        return gdn.recurrent_forward(sd["q"], sd["k"], sd["v"], s_states[i & 3], None, None, None, sd["num_accepted_tokens"],
+                                     inference_mode=1, is_qk_norm=True, gating=s_gating)
+
+    for i in range(5):
+        step_spec(i)
+    ms_spec, ms_spec_all = timed(step_spec, dsteps)
+    accepted = int(sp["num_accepted_tokens"].sum())
+    del s_states
+
+    # ---------------- decode batch of 1024 sequences split by sequence over the ranks (strong scaling)
+    sl = sharding.seq_shard(rank, world, DECODE_SHARDED_B)
+    nB = sl.stop - sl.start
+    np_ = synthetic.decode_inputs(nB, 1, kh, vh, d, seed=500 + rank)
+    nd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in np_.items()}
+    n_states = [nd["state"], nd["state"].clone()] if nB * vh * d * d * 2 > (160 << 20) else [nd["state"].clone() for _ in range(4)]
+    n_gating = (nd["A_log"], nd["dt_bias"], nd["a"], nd["b"])
+
+    def step_decode_sharded(i):
+        return gdn.recurrent_forward(nd["q"], nd["k"], nd["v"], n_states[i % len(n_states)], None, None, inference_mode=1,
+                                     is_qk_norm=True, gating=n_gating)
+
+    for i in range(5):
+        step_decode_sharded(i)
+    ms_dsh, ms_dsh_all = timed(step_decode_sharded, dsteps)
+    del n_states, nd
+
     # ---------------- packed prefill: 16 sequences of log-normal lengths, 32768 tokens per rank
     pk = None
     if not args.no_packed:
         lens = synthetic.lognormal_lengths(16, 32768, 64, 8192, seed=rank)
         pp = synthetic.varlen_inputs(lens, kh, vh, d, seed=200 + rank)
         pd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in pp.items()}
-        pws = torch.empty(gdn.api.chunked_forward_workspace_bytes(len(lens), 0, vh, total_tokens=sum(lens),
-                                                                  total_chunks=pp["total_chunks"], packed=True),
+        pws = torch.empty(gdn_api.chunked_forward_workspace_bytes(len(lens), 0, vh, total_tokens=sum(lens),
+                                                                  total_chunks=pp["total_chunks"], packed=True, num_k_heads=kh),
                           dtype=torch.uint8, device=dev)
         pev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
         for e in pev:
             e.record()
 
-        def step_packed(events=None):
+        def step_packed(i=0, events=None):
             return gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"], pd["cu_seqlens"],
                                        pd["chunk_indices"], pd["cu_chunks"], pp["total_chunks"], _workspace=pws,
                                        _stage_events=events)
         for _ in range(3):
             step_packed()
-        barrier()
-        psteps = 10
-        e0.record()
-        for _ in range(psteps):
-            step_packed()
-        e1.record()
-        barrier()
-        ms_pk = max_over_ranks(e0.elapsed_time(e1) / psteps)
-        step_packed(pev)
+        ms_pk, ms_pk_all = timed(step_packed, 10)
+        step_packed(0, pev)
         torch.cuda.synchronize()
         pk = {"metric": "prefill_tokens_per_s", "value": world * sum(lens) / (ms_pk * 1e-3), "unit": "tokens/s",
               "config": "packed: 16 sequences of log-normal lengths (%d ... %d tokens), %d tokens per GPU, kh=16 vh=32 d=128"
                         % (min(lens), max(lens), sum(lens)),
-              "ms_per_step": ms_pk, "gdn_uw_kernel_ms": pev[0].elapsed_time(pev[1]),
+              "ms_per_step": ms_pk, "spread": spread(ms_pk_all), "gdn_zp_kernel_ms": pev[0].elapsed_time(pev[1]),
               "gdn_fused_seq_kernel_ms": pev[1].elapsed_time(pev[2])}
         del pd, pws
     # ---------------- long context: B=2, T=131072, the 32 value heads sharded over the ranks
@@ -491,24 +555,47 @@ def main():
         lbeta = torch.sigmoid(torch.randn(lB, lT, lvh, device=dev, generator=gen)).bfloat16()
         lg = -torch.nn.functional.softplus(torch.randn(lB, lT, lvh, device=dev, generator=gen)) * 0.1
         ls0 = (torch.randn(lB, lvh, d, d, device=dev, generator=gen) * 0.02).bfloat16()
-        lws = torch.empty(gdn.api.chunked_forward_workspace_bytes(lB, lT, lvh), dtype=torch.uint8, device=dev)
+        lws = torch.empty(gdn_api.chunked_forward_workspace_bytes(lB, lT, lvh, num_k_heads=lkh), dtype=torch.uint8, device=dev)
+
+        def step_long(i=0):
+            return gdn.chunked_forward(lq, lk, lv, lbeta, lg, None, ls0, _workspace=lws)
         for _ in range(2):
-            gdn.chunked_forward(lq, lk, lv, lbeta, lg, None, ls0, _workspace=lws)
-        barrier()
-        lsteps = 5
-        e0.record()
-        for _ in range(lsteps):
-            gdn.chunked_forward(lq, lk, lv, lbeta, lg, None, ls0, _workspace=lws)
-        e1.record()
-        barrier()
-        ms_lc = max_over_ranks(e0.elapsed_time(e1) / lsteps)
+            step_long()
+        ms_lc, ms_lc_all = timed(step_long, 5, repeats=3)
         lc = {"metric": "prefill_tokens_per_s", "value": lB * lT / (ms_lc * 1e-3), "unit": "tokens/s", "scaling": "strong",
               "config": "B=2 T=131072 kh=16 vh=32 d=128, value heads sharded over %d GPU(s): %d v-heads per GPU" % (world, lvh),
-              "ms_per_step": ms_lc}
+              "ms_per_step": ms_lc, "spread": spread(ms_lc_all)}
         del lq, lk, lv, lbeta, lg, ls0, lws
-    # the sampler ran across every timed region above (prefill resident, end to end, decode, packed, long context)
+    # the sampler ran across every timed region above
     clocks = sampler.stop() if rank == 0 else None
-    dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
+
+    # ---------------- N > 1: sharded result against the oracle (untimed).  One problem from a shared seed;
+    # every rank computes its value-head shard on its own GPU; O and the final state are gathered with
+    # NCCL; rank 0 compares the assembled result with the fp32 CPU recurrence.
+    parity = None
+    if world > 1 and 8 % world == 0:
+        pB, pT, pkh, pvh = 2, 520, 8, 16
+        pp = synthetic.prefill_inputs(pB, pT, pkh, pvh, d, seed=4242)
+        full = {k: pp[k].to(dev) for k in ("q", "k", "v", "beta", "g", "state")}
+        mine = sharding.shard_prefill_by_head(full, rank, world)
+        o_sh, s_sh = gdn.chunked_forward(mine["q"], mine["k"], mine["v"], mine["beta"], mine["g"], None, mine["state"])
+        o_sh, s_sh = o_sh.contiguous(), s_sh.contiguous()
+        o_all = [torch.empty_like(o_sh) for _ in range(world)]
+        s_all = [torch.empty_like(s_sh) for _ in range(world)]
+        dist.all_gather(o_all, o_sh)
+        dist.all_gather(s_all, s_sh)
+        torch.cuda.synchronize()
+        if rank == 0:
+            from oracle import gdn_oracle as O
+            o_ref, s_ref = O.recurrent_ref(pp["q"].float(), pp["k"].float(), pp["v"].float(), pp["beta"].float(), pp["g"],
+                                           pp["state"].float())
+            o_cat, s_cat = torch.cat(o_all, dim=2).float().cpu(), torch.cat(s_all, dim=1).float().cpu()
+            parity = {"config": "B=2 T=520 kh=8 vh=16 d=128, value heads sharded over %d GPUs, NCCL all_gather of O and final state" % world,
+                      "o_rel_fro": O.rel_fro(o_cat, o_ref), "o_max_abs_over_max": O.max_abs_over_max(o_cat, o_ref),
+                      "state_rel_fro": O.rel_fro(s_cat, s_ref), "state_max_abs_over_max": O.max_abs_over_max(s_cat, s_ref),
+                      "gate": "rel_fro <= 1e-2 and max_abs <= 5e-2 * max|ref|"}
+            parity["rel_fro"] = max(parity["o_rel_fro"], parity["state_rel_fro"])
+            parity["ok"] = bool(parity["rel_fro"] <= 1e-2 and max(parity["o_max_abs_over_max"], parity["state_max_abs_over_max"]) <= 5e-2)
 
     if rank != 0:
         if world > 1:
@@ -520,52 +607,81 @@ def main():
         tps, cores, what = cpu_recurrence_tokens_per_s(4096)
         cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": what}
 
-    seq_flops = units * seq_kernel_flops_per_unit(d)
-    uw_flops = units * uw_kernel_flops_per_unit(d)
     total_flops = units * flops_per_unit(d)
-    uw_bytes = units * uw_kernel_bytes_per_unit(kh, vh, d)
+    zp_flops = units * zp_kernel_flops_per_unit(kh, vh, d)
+    seq_flops = units * seq_kernel_flops_per_unit(d)
+    zp_bytes = units * zp_kernel_bytes_per_unit(kh, vh, d)
     seq_bytes = units * seq_kernel_bytes_per_unit(kh, vh, d)
-    # the dominant kernel is the one with the longer launch; both are HBM-bound (see above)
-    if uw_ms >= seq_ms:
-        dom = ("gdn_uw_kernel (WY/UT transform + intra-chunk attention block)", uw_ms, uw_bytes, uw_flops,
-               units * NCU_UW_TRAFFIC_PER_UNIT)
-    else:
-        dom = ("gdn_fused_seq_kernel (state propagation + output)", seq_ms, seq_bytes, seq_flops,
-               units * NCU_FUSED_TRAFFIC_PER_UNIT)
-    achieved = dom[2] / (dom[1] * 1e-3) / 1e9
+    min_bytes = prefill_min_bytes(tokens, B, kh, vh, d)
+    step_tflops = total_flops / (ms_res * 1e-3) / 1e12
+    traffic = None
+    if NCU_ZP_TRAFFIC_PER_UNIT is not None and NCU_FUSED_TRAFFIC_PER_UNIT is not None:
+        traffic = units * (NCU_ZP_TRAFFIC_PER_UNIT + NCU_FUSED_TRAFFIC_PER_UNIT)
+    dec_bytes = dB * decode_bytes_per_token(kh, vh, d)
+    spec_bytes = sB * spec_bytes_per_seq(sT, kh, vh, d)
+    dsh_bytes = nB * decode_bytes_per_token(kh, vh, d)
+
+    def hbm_roof(nbytes, ms, kernel, traffic=None):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"kernel": kernel, "bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": gbs / peaks["hbm_gbs"], "frac_of_nominal_8TBs": gbs / 8000.0, "ms_per_launch": ms,
+                "bytes_per_launch": nbytes, "traffic": traffic, "peak_source": peaks["source"]}
+
     line = {
         "metric": "prefill_tokens_per_s", "value": world * tokens / (ms_res * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res,
+        "spread": spread(ms_res_all),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "sharding": "by sequence, no collective", "l2": "inputs (0.41 GB per step) larger than L2"},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-        "gpu_launches": 2 * args.steps,
-        "roofline": {"kernel": dom[0], "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": dom[4],
-                     "traffic_source": "ncu capture at B=2 scaled by units", "peak_source": peaks["source"],
-                     "ms_per_launch": dom[1], "bytes_per_launch": dom[2], "flops_per_launch": dom[3],
-                     "flop_per_byte": dom[3] / dom[2]},
-        "kernels": {"gdn_uw_kernel_ms": uw_ms, "gdn_fused_seq_kernel_ms": seq_ms,
-                    "uw_gbs": uw_bytes / (uw_ms * 1e-3) / 1e9, "uw_frac_of_hbm_peak": uw_bytes / (uw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                    "fused_gbs": seq_bytes / (seq_ms * 1e-3) / 1e9,
-                    "fused_frac_of_hbm_peak": seq_bytes / (seq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                    "uw_tflops": uw_flops / (uw_ms * 1e-3) / 1e12, "fused_tflops": seq_flops / (seq_ms * 1e-3) / 1e12,
-                    "whole_step_tflops": total_flops / (ms_res * 1e-3) / 1e12,
-                    "whole_step_frac_of_tensor_peak": total_flops / (ms_res * 1e-3) / 1e12 / peaks["tflops"],
-                    "whole_step_hbm_gbs": (uw_bytes + seq_bytes) / (ms_res * 1e-3) / 1e9,
-                    "whole_step_frac_of_hbm_peak": (uw_bytes + seq_bytes) / (ms_res * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
+                "note": "bound by the pinned-host <-> device copies (%.0f MB per rank and step, %.1f GB/s in + %.1f GB/s out per rank); "
+                        "at N > 1 the ranks share the host's memory and PCIe path" % (
+                            (h2d + d2h) / 1e6, h2d / (ms_e2e * 1e-3) / 1e9, d2h / (ms_e2e * 1e-3) / 1e9)},
+        "gpu_launches": 2 * args.steps * REPEATS,
+        "gpu_launches_per_step": 2,
+        # the whole step (two launches) against the tensor-core roof: the path is a dense contraction
+        "roofline": {"kernel": "gdn_zp_kernel + gdn_fused_seq_kernel (one prefill step)", "bound": "tensor",
+                     "achieved": step_tflops, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": step_tflops / peaks["tflops"],
+                     "peak_kind": "burst cuBLAS bf16 figure (the timed region lasts milliseconds)",
+                     "frac_of_sustained_peak": step_tflops / peaks["tflops_sustained"],
+                     "flops_per_step": total_flops, "flops_per_unit": flops_per_unit(d), "units_per_step": units,
+                     "traffic": traffic, "traffic_source": "ncu captures at B=2 scaled by units, both kernels",
+                     "peak_source": peaks["source"],
+                     "bytes": {"min_bytes_per_step": min_bytes, "achieved_gbs": min_bytes / (ms_res * 1e-3) / 1e9,
+                               "peak_gbs": peaks["hbm_gbs"], "frac": min_bytes / (ms_res * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                               "what": "24 768 B per token (q, k, v, o, beta, gate) + the states, against the measured copy bandwidth"}},
+        "kernels": {
+            "gdn_zp_kernel": {"ms": zp_ms, "executed_tflops": zp_flops / (zp_ms * 1e-3) / 1e12,
+                              "frac_of_tensor_peak": zp_flops / (zp_ms * 1e-3) / 1e12 / peaks["tflops"],
+                              "algorithmic_gbs": zp_bytes / (zp_ms * 1e-3) / 1e9,
+                              "frac_of_hbm_peak": zp_bytes / (zp_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                              "traffic": None if NCU_ZP_TRAFFIC_PER_UNIT is None else units * NCU_ZP_TRAFFIC_PER_UNIT},
+            "gdn_fused_seq_kernel": {"ms": seq_ms, "executed_tflops": seq_flops / (seq_ms * 1e-3) / 1e12,
+                                     "frac_of_tensor_peak": seq_flops / (seq_ms * 1e-3) / 1e12 / peaks["tflops"],
+                                     "algorithmic_gbs": seq_bytes / (seq_ms * 1e-3) / 1e9,
+                                     "frac_of_hbm_peak": seq_bytes / (seq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                     "traffic": None if NCU_FUSED_TRAFFIC_PER_UNIT is None else units * NCU_FUSED_TRAFFIC_PER_UNIT}},
         "decode": {"metric": "decode_tokens_per_s", "value": world * dB / (ms_dec * 1e-3), "unit": "tokens/s",
-                   "config": "B=256 T=1 kh=16 vh=32 d=128, qk-norm, fused gating, per GPU", "ms_per_step": ms_dec,
-                   "roofline": {"kernel": "gdn_recurrent_kernel", "bound": "hbm",
-                                "achieved": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
-                                "unit": "GB/s", "frac": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                "frac_of_nominal_8TBs": dec_bytes / (ms_dec_kernel * 1e-3) / 1e9 / 8000.0,
-                                "ms_per_launch": ms_dec_kernel, "bytes_per_launch": dec_bytes,
-                                "traffic": dB * NCU_DECODE_TRAFFIC_PER_TOKEN}},
+                   "config": "B=256 T=1 kh=16 vh=32 d=128, qk-norm, gating fused in the kernel (one launch per step), per GPU",
+                   "ms_per_step": ms_dec, "spread": spread(ms_dec_all), "gpu_launches_per_step": 1,
+                   "roofline": hbm_roof(dec_bytes, ms_dec, "gdn_recurrent_kernel", dB * NCU_DECODE_TRAFFIC_PER_TOKEN)},
+        "spec_verify": {"metric": "verified_tokens_per_s", "value": world * sB * sT / (ms_spec * 1e-3), "unit": "tokens/s",
+                        "accepted_tokens_per_s": world * accepted / (ms_spec * 1e-3),
+                        "config": "B=64 T=4 inference_mode=1, num_accepted_tokens ~ U{1..4} (%d of %d accepted), qk-norm, "
+                                  "gating fused in the kernel, per GPU" % (accepted, sB * sT),
+                        "ms_per_step": ms_spec, "spread": spread(ms_spec_all), "gpu_launches_per_step": 1,
+                        "roofline": hbm_roof(spec_bytes, ms_spec, "gdn_recurrent_kernel")},
+        "decode_sharded": {"metric": "decode_tokens_per_s", "value": DECODE_SHARDED_B / (ms_dsh * 1e-3), "unit": "tokens/s",
+                           "scaling": "strong",
+                           "config": "B=1024 T=1 kh=16 vh=32 d=128 split by sequence over %d GPU(s): %d sequences on rank 0, "
+                                     "qk-norm, fused gating" % (world, nB),
+                           "ms_per_step": ms_dsh, "spread": spread(ms_dsh_all),
+                           "roofline": hbm_roof(dsh_bytes, ms_dsh, "gdn_recurrent_kernel (rank 0's share)")},
         "packed": pk,
         "long_context": lc,
+        "parity": parity,
         "clocks": clocks,
     }
     if cpu is not None:

@@ -142,6 +142,11 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     uint64_t* tokfull = full + kStages;  // [2]
     uint8_t* tokbase = smem + kStages * Stage::kBytes + 128;
     __shared__ int abort_flag;
+    // Fused gating: load_scalars returns the raw projections b and a (fetched a unit ahead like beta and the
+    // gate); the transform is applied where they are consumed, with the per-head parameters A_log and
+    // dt_bias staged here once per CTA (heads beyond the table are read from global memory).
+    constexpr int kGateTable = 128;
+    __shared__ float s_alog[kGateTable], s_dtb[kGateTable];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -154,6 +159,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     const int num_units = static_cast<int>(p.num_tiles / tpu);
     const int stride = static_cast<int>(gridDim.x);
 
+    if (p.fused_gating) {
+        for (int h = threadIdx.x; h < min(p.vh, kGateTable); h += blockDim.x) {
+            s_alog[h] = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.A_log) + h)
+                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.A_log)[h]);
+            s_dtb[h] = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.dt_bias) + h)
+                                          : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.dt_bias)[h]);
+        }
+    }
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
@@ -217,16 +230,24 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         } else {
             gt = 0.f;
         }
-        if (p.fused_gating) {
-            const float al = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.A_log) + t.head)
-                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.A_log)[t.head]);
-            const float db = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.dt_bias) + t.head)
-                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.dt_bias)[t.head]);
-            const float x = gt + db;
-            const float sp = x > 20.f ? x : log1pf(__expf(x));
-            gt = -__expf(al) * sp;
-            bt = 1.f / (1.f + __expf(-bt));
+    };
+
+    // raw projections (b, a) of a token of v-head `head` -> (beta, gate)
+    auto apply_gating = [&](int head, float& bt, float& gt) {
+        float al, db;
+        if (head < kGateTable) {
+            al = s_alog[head];
+            db = s_dtb[head];
+        } else {
+            al = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.A_log) + head)
+                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.A_log)[head]);
+            db = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.dt_bias) + head)
+                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.dt_bias)[head]);
         }
+        const float x = gt + db;
+        const float sp = x > 20.f ? x : log1pf(__expf(x));
+        gt = -__expf(al) * sp;
+        bt = 1.f / (1.f + __expf(-bt));
     };
 
     // The producer walks (unit, rb) pairs kStages-1 iterations ahead of the consumers.
@@ -264,6 +285,9 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             const int tk = kRing ? lane : 0;
             if (tk < tn.ntok) load_scalars(tn, tk, beta_next, g_next);
         }
+        // fused gating: the first token's (the ring instance: the first 32 tokens') raw projections become
+        // beta and the gate once per unit, not once per tile
+        if (p.fused_gating) apply_gating(T.head, beta_first, g_first);
         // per-unit values of the first token (kept across the unit's tiles when ntok == 1)
         f2 k2[NQ], q2[NQ];
         float kq = 0.f;
@@ -491,6 +515,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         if (blk > 0) {
                             bsc = bsn;
                             gsc = gsn;
+                            if (p.fused_gating) apply_gating(T.head, bsc, gsc);  // one lane per token
                         }
                         const int tn = (blk + 4) * TB + lane;
                         bsn = 0.f;
@@ -545,6 +570,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 for (int j = 0; j < 4; ++j) vr[j] = vn[j];
                 beta_t = beta_n;
                 g_t = g_n;
+                if (p.fused_gating && t + 1 < T.ntok) apply_gating(T.head, beta_t, g_t);
             }
 
             }

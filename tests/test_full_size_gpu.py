@@ -145,6 +145,17 @@ def test_config4_long_context_one_gpu_share(gdn):
     check_status()
     close(o, o_rec, "O vs the recurrent kernel")
     close(s, s_rec, "final state vs the recurrent kernel")
+    # (2b) the oracle over ALL 131072 tokens of one (sequence, v-head) chain: an independent check of every
+    # segment of the segmented state propagation (tens of seconds of CPU work)
+    b, h = 1, 3
+    kk = h // (vh // kh)
+    o_1, s_1 = O.recurrent_ref(p["q"][b:b + 1, :, kk:kk + 1].float(), p["k"][b:b + 1, :, kk:kk + 1].float(),
+                               p["v"][b:b + 1, :, h:h + 1].float(), p["beta"][b:b + 1, :, h:h + 1].float(),
+                               p["g"][b:b + 1, :, h:h + 1], p["state"][b:b + 1, h:h + 1].float())
+    close(o[b:b + 1, :, h:h + 1], o_1, "O of one chain over the whole length")
+    for lo in range(0, T, T // 16):   # and segment by segment, so that a late deviation cannot hide in the norm
+        close(o[b:b + 1, lo:lo + T // 16, h:h + 1], o_1[:, lo:lo + T // 16], "O of tokens %d.." % lo)
+    close(s[b:b + 1, h:h + 1], s_1, "final state of one chain")
     # (3) two halves with the state handed over (the hand-over rounds the state to bf16 once)
     h = T // 2
     o1, s1 = gdn.chunked_forward(*(x[:, :h] for x in a), None, pd["state"])
