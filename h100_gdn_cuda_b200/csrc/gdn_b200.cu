@@ -74,28 +74,31 @@ __global__ void gdn_selftest_wait_kernel(long long limit_cycles, int* status) {
 }
 
 // ------------------------------------------------------------------ recurrent
-template <int DK, bool kRing>
+template <int DK, bool kRing, bool kLean = false>
 static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st) {
     constexpr int smem = recurrent_smem_bytes<DK, kRing>();
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK, kRing>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK, kRing, kLean>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set[dev] = true;
     }
     const int per_sm = recurrent_ctas_per_sm<DK, kRing>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
-    gdn_recurrent_kernel<DK, kRing><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
+    gdn_recurrent_kernel<DK, kRing, kLean><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
 
 // `ring`: long runs of tokens (more than kRecTokRingMin per sequence on average) take the instance
-// with the multi-token ring; decode and speculative verify keep the lean one.
+// with the multi-token ring; speculative verify keeps the decode instance; plain single-token decode
+// from a given state (`lean`) takes the decode instance with its run-time tests compiled away.
 template <int DK>
-static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st, bool ring) {
-    return ring ? launch_recurrent_t<DK, true>(p, sms, st) : launch_recurrent_t<DK, false>(p, sms, st);
+static int launch_recurrent(const RecurrentParams& p, int sms, cudaStream_t st, bool ring, bool lean) {
+    if (ring) return launch_recurrent_t<DK, true>(p, sms, st);
+    if (lean) return launch_recurrent_t<DK, false, true>(p, sms, st);
+    return launch_recurrent_t<DK, false>(p, sms, st);
 }
 
 // Head dimensions without a prebuilt kernel (or every call when GDN_JIT_RECURRENT=1) go through
@@ -319,11 +322,12 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
                                    : (s.seq_len > ring_min);
     if (force_jit) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
+    const bool lean = !s.cu_seqlens && s.seq_len == 1 && p.state_in != nullptr && !p.store_step;
     switch (s.head_dim_k) {
-        case 64: return launch_recurrent<64>(p, d->sms, st, ring);
-        case 128: return launch_recurrent<128>(p, d->sms, st, ring);
-        case 192: return launch_recurrent<192>(p, d->sms, st, ring);
-        case 256: return launch_recurrent<256>(p, d->sms, st, ring);
+        case 64: return launch_recurrent<64>(p, d->sms, st, ring, lean);
+        case 128: return launch_recurrent<128>(p, d->sms, st, ring, lean);
+        case 192: return launch_recurrent<192>(p, d->sms, st, ring, lean);
+        case 256: return launch_recurrent<256>(p, d->sms, st, ring, lean);
     }
     return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);  // 320 .. 512: compiled on first use
 }

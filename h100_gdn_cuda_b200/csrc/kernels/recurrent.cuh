@@ -129,8 +129,12 @@ __device__ __forceinline__ float hsum(f2 v) {
 // entry point the run-time compiler generates (csrc/gdn_jit.cu) both instantiate it.
 // kRing: with the multi-token ring (long runs of tokens); without it the kernel is the lean decode
 // kernel (its registers are at the limit of four CTAs per SM at DK = 128).
-template <int DK, bool kRing = true>
+// kLean (decode instance only): the launch is plain single-token decode from a given state - padded
+// inputs with one token per sequence, an initial state, one state per sequence out.  The host
+// promises that, and the corresponding run-time tests compile away.
+template <int DK, bool kRing = true, bool kLean = false>
 __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
+    static_assert(!(kRing && kLean), "the lean instance is a decode instance");
     using namespace ptx;
     using namespace rec;
     using Stage = RecStage<DK, kRing>;
@@ -152,7 +156,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     const int warp = tid >> 5, lane = tid & 31;
     const int half = lane >> 4, l16 = lane & 15;
     const int rblocks = p.dv / kRecTileRows;
-    const bool has_in = p.state_in != nullptr;
+    const bool has_in = kLean || p.state_in != nullptr;
+    const bool store_step = !kLean && p.store_step != 0;
     const int rep = p.vh / p.kh;
     const int tpu = (kRing && p.split_tiles) ? 1 : rblocks;  // tiles per work unit
     const int upg = rblocks / tpu;                // work units per (sequence, v-head)
@@ -180,13 +185,25 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         int seq, head, khead, ntok, rb0;
         long long tok0, bidx;
     };
+    // head counts are almost always powers of two: shifts instead of integer divisions then
+    const int vh_shift = (p.vh & (p.vh - 1)) == 0 ? __ffs(p.vh) - 1 : -1;
+    const int rep_shift = (rep & (rep - 1)) == 0 ? __ffs(rep) - 1 : -1;
     auto decode = [&](int unit) {
         Unit t;
-        const int sh = unit / upg;
-        t.rb0 = (unit - sh * upg) * tpu;
-        t.head = sh % p.vh;
-        t.seq = sh / p.vh;
-        t.khead = t.head / rep;
+        int sh = unit;
+        t.rb0 = 0;
+        if (upg != 1) {
+            sh = unit / upg;
+            t.rb0 = (unit - sh * upg) * tpu;
+        }
+        if (vh_shift >= 0) {
+            t.seq = sh >> vh_shift;
+            t.head = sh & (p.vh - 1);
+        } else {
+            t.seq = sh / p.vh;
+            t.head = sh - t.seq * p.vh;
+        }
+        t.khead = rep_shift >= 0 ? (t.head >> rep_shift) : (t.head / rep);
         if (p.cu_seqlens) {
             t.tok0 = p.cu_seqlens[t.seq];
             t.ntok = p.cu_seqlens[t.seq + 1] - static_cast<int>(t.tok0);
@@ -200,22 +217,28 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         return t;
     };
     // Producer (one thread): everything tile `rb` of `unit` needs for its first token.
+    // source addresses of the producer's current unit (its first token), computed when the unit changes
+    const __nv_bfloat16* prod_s = nullptr;
+    const __nv_bfloat16* prod_k = nullptr;
+    const __nv_bfloat16* prod_q = nullptr;
+    const __nv_bfloat16* prod_v = nullptr;
+    auto producer_bases = [&](const Unit& t) {
+        prod_s = has_in ? p.state_in + t.seq * p.si_ss + t.head * p.si_sh : nullptr;
+        prod_k = p.k + t.bidx * p.k_sb + t.tok0 * p.k_st + t.khead * p.k_sh;
+        prod_q = p.q + t.bidx * p.q_sb + t.tok0 * p.q_st + t.khead * p.q_sh;
+        prod_v = p.v + t.bidx * p.v_sb + t.tok0 * p.v_st + t.head * p.v_sh;
+    };
     auto issue = [&](const Unit& t, int rb, int stage) {
         uint8_t* dst = smem + stage * Stage::kBytes;
         const int nt0 = min(t.ntok, Stage::kTok);  // tokens whose k, q, v travel with the tile
         const uint32_t bytes = (has_in ? Stage::kTileBytes : 0) + static_cast<uint32_t>(nt0) * (4 * DK + kRecTileRows * 2);
         mbar_arrive_expect_tx(&full[stage], bytes);
-        if (has_in) {
-            const __nv_bfloat16* src = p.state_in + t.seq * p.si_ss + t.head * p.si_sh +
-                                       static_cast<long long>(rb) * kRecTileRows * DK;
-            bulk_load(dst, src, Stage::kTileBytes, &full[stage]);
-        }
+        if (has_in) bulk_load(dst, prod_s + rb * (kRecTileRows * DK), Stage::kTileBytes, &full[stage]);
         for (int i = 0; i < nt0; ++i) {
-            const long long tok = t.tok0 + i;
-            bulk_load(dst + Stage::kOffK + i * DK * 2, p.k + t.bidx * p.k_sb + tok * p.k_st + t.khead * p.k_sh, DK * 2, &full[stage]);
-            bulk_load(dst + Stage::kOffQ + i * DK * 2, p.q + t.bidx * p.q_sb + tok * p.q_st + t.khead * p.q_sh, DK * 2, &full[stage]);
-            bulk_load(dst + Stage::kOffV + i * kRecTileRows * 2,
-                      p.v + t.bidx * p.v_sb + tok * p.v_st + t.head * p.v_sh + rb * kRecTileRows, kRecTileRows * 2, &full[stage]);
+            bulk_load(dst + Stage::kOffK + i * DK * 2, prod_k + i * p.k_st, DK * 2, &full[stage]);
+            bulk_load(dst + Stage::kOffQ + i * DK * 2, prod_q + i * p.q_st, DK * 2, &full[stage]);
+            bulk_load(dst + Stage::kOffV + i * kRecTileRows * 2, prod_v + i * p.v_st + rb * kRecTileRows, kRecTileRows * 2,
+                      &full[stage]);
         }
     };
     auto load_scalars = [&](const Unit& t, int tk, float& bt, float& gt) {
@@ -253,7 +276,10 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     // The producer walks (unit, rb) pairs kStages-1 iterations ahead of the consumers.
     int prod_unit = blockIdx.x, prod_rb = 0, prod_it = 0;
     Unit prod_u{};
-    if (tid == 0 && prod_unit < num_units) prod_u = decode(prod_unit);
+    if (tid == 0 && prod_unit < num_units) {
+        prod_u = decode(prod_unit);
+        producer_bases(prod_u);
+    }
     auto produce_one = [&]() {
         if (prod_unit >= num_units) return;
         issue(prod_u, prod_u.rb0 + prod_rb, prod_it % kStages);
@@ -261,7 +287,10 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         if (++prod_rb == tpu) {
             prod_rb = 0;
             prod_unit += stride;
-            if (prod_unit < num_units) prod_u = decode(prod_unit);
+            if (prod_unit < num_units) {
+                prod_u = decode(prod_unit);
+                producer_bases(prod_u);
+            }
         }
     };
     if (tid == 0) {
@@ -277,14 +306,19 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 
     int it = 0;
     int tb_it = 0;  // blocks that have gone through the multi-token ring (slot and parity bookkeeping)
+    Unit T_carry{};
+    if (static_cast<int>(blockIdx.x) < num_units) T_carry = decode(blockIdx.x);
     for (int unit = blockIdx.x; unit < num_units; unit += stride) {
-        const Unit T = decode(unit);
+        const Unit T = T_carry;
         float beta_next = 0.f, g_next = 0.f;
         if (unit + stride < num_units) {
-            const Unit tn = decode(unit + stride);
+            T_carry = decode(unit + stride);
             const int tk = kRing ? lane : 0;
-            if (tk < tn.ntok) load_scalars(tn, tk, beta_next, g_next);
+            if (tk < T_carry.ntok) load_scalars(T_carry, tk, beta_next, g_next);
         }
+        // where this unit's outputs go: computed once per unit, not per tile or token
+        __nv_bfloat16* const out_unit = p.out + T.bidx * p.o_sb + T.tok0 * p.o_st + T.head * p.o_sh;
+        __nv_bfloat16* const sout_unit = p.state_out + T.head * p.so_sh + (store_step ? 0 : static_cast<long long>(T.seq) * p.so_ss);
         // fused gating: the first token's (the ring instance: the first 32 tokens') raw projections become
         // beta and the gate once per unit, not once per tile
         if (p.fused_gating) apply_gating(T.head, beta_first, g_first);
@@ -321,7 +355,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 #pragma unroll
                     for (int c = 0; c < NQ; ++c) S[j][c] = 0ull;
             }
-            const bool fresh_qk = (r == 0) || (T.ntok > 1);
+            const bool fresh_qk = (r == 0) || (!kLean && T.ntok > 1);
             uint2 kw[NQ / 2], qw[NQ / 2];
             if (T.ntok > 0) {
                 if (fresh_qk) {
@@ -393,11 +427,11 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 f2 ak[4], aq[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    ak[j] = 0ull;
-                    aq[j] = 0ull;
+                    ak[j] = mul2(S[j][0], k2[0]);
+                    aq[j] = mul2(S[j][0], q2[0]);
                 }
 #pragma unroll
-                for (int c = 0; c < NQ; ++c) {
+                for (int c = 1; c < NQ; ++c) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         ak[j] = fma2(S[j][c], k2[c], ak[j]);
@@ -453,15 +487,13 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 #pragma unroll
                     for (int c = 0; c < NQ; ++c) S[j][c] = fma2(eg2, S[j][c], mul2(br2, k2[c]));
                 }
-                const long long tok = T.tok0 + t;
                 if (ok && l16 >= 8 && (l16 & 1) == 0) {
-                    __nv_bfloat16* op = p.out + T.bidx * p.o_sb + tok * p.o_st + T.head * p.o_sh + rb * kRecTileRows;
+                    __nv_bfloat16* op = out_unit + t * p.o_st + rb * kRecTileRows;
                     op[warp * 8 + (l16 - 8) + half] = __float2bfloat16(o_mine);
                 }
-                if (p.store_step && ok) {
-                    const long long sidx = p.cu_seqlens ? tok : (static_cast<long long>(T.seq) * p.seq_len + t);
-                    __nv_bfloat16* sp = p.state_out + sidx * p.so_ss + T.head * p.so_sh +
-                                        static_cast<long long>(rb) * kRecTileRows * DK;
+                if (store_step && ok) {
+                    const long long sidx = p.cu_seqlens ? (T.tok0 + t) : (static_cast<long long>(T.seq) * p.seq_len + t);
+                    __nv_bfloat16* sp = sout_unit + sidx * p.so_ss + rb * (kRecTileRows * DK);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int row = warp * 8 + 2 * j + half;
@@ -555,6 +587,13 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 if (nblk > 1) tb_it += nblk - 1;
             } else {
             float beta_t = beta_first, g_t = g_first;
+            if (kLean || T.ntok == 1) {
+                // plain decode: no token loop, nothing fetched ahead (an accepted-token cap of 0 copies the state)
+                if (T.ntok == 1) {
+                    if (fresh_qk) prep_kq(kw, qw);
+                    token_step(0, vr, beta_t, g_t);
+                }
+            } else
             for (int t = 0; t < T.ntok; ++t) {
                 uint2 kn[NQ / 2], qn[NQ / 2];
                 float vn[4], beta_n = 0.f, g_n = 0.f;
@@ -574,9 +613,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             }
 
             }
-            if (!p.store_step && ok) {
-                __nv_bfloat16* sp = p.state_out + static_cast<long long>(T.seq) * p.so_ss + T.head * p.so_sh +
-                                    static_cast<long long>(rb) * kRecTileRows * DK;
+            if (!store_step && ok) {
+                __nv_bfloat16* sp = sout_unit + rb * (kRecTileRows * DK);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int row = warp * 8 + 2 * j + half;
@@ -604,9 +642,9 @@ constexpr int recurrent_ctas_per_sm() {
     return kRing ? (DK <= 64 ? 4 : 3) : (DK <= 128 ? 4 : 2);
 }
 
-template <int DK, bool kRing = false>
+template <int DK, bool kRing = false, bool kLean = false>
 __global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK, kRing>()) gdn_recurrent_kernel(const RecurrentParams p) {
-    gdn_recurrent_body<DK, kRing>(p);
+    gdn_recurrent_body<DK, kRing, kLean>(p);
 }
 
 }  // namespace gdn
