@@ -133,7 +133,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     using L = FusedSmem;
     constexpr int D = 128;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by an offset from the array itself, so that the compiler still knows the pointer is shared memory
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* bar_full = bars;        // [2]
     uint64_t* bar_empty = bars + 2;   // [2]

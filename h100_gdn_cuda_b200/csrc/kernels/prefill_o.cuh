@@ -45,7 +45,8 @@ __global__ void __launch_bounds__(128, 2) gdn_o_kernel(const __grid_constant__ C
     using namespace ptx;
     using L = OSmem;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by an offset from the array itself, so that the compiler still knows the pointer is shared memory
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sQ = smem + L::kOffQ;
     uint8_t* sK = smem + L::kOffK;
     uint8_t* sU = smem + L::kOffU;

@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
     using L = SegCombineSmem;
     constexpr int D = L::D, R = L::R;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t* smem = smem_raw + ((128u - (ptx::smem_u32(smem_raw) & 127u)) & 127u);
     float* sM = reinterpret_cast<float*>(smem + L::kOffM);
     float(*sS)[D] = reinterpret_cast<float(*)[D]>(smem + L::kOffS);
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::kOffBar);

@@ -102,6 +102,19 @@ __device__ __forceinline__ void mma_block(float* d, const float* am, int lda, in
     b[1] = to_tf32(bm[(k0b + t + 4) * ldb + n0 + g]);
     mma_tf32(d, a, b);
 }
+// The two operand fragments of mma_block on their own, for products that share one of them.
+__device__ __forceinline__ void load_afrag(uint32_t* a, const float* am, int lda, int r0, int k0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    a[0] = to_tf32(am[(r0 + g) * lda + k0 + t]);
+    a[1] = to_tf32(am[(r0 + g + 8) * lda + k0 + t]);
+    a[2] = to_tf32(am[(r0 + g) * lda + k0 + t + 4]);
+    a[3] = to_tf32(am[(r0 + g + 8) * lda + k0 + t + 4]);
+}
+__device__ __forceinline__ void load_bfrag(uint32_t* b, const float* bm, int ldb, int k0b, int n0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    b[0] = to_tf32(bm[(k0b + t) * ldb + n0 + g]);
+    b[1] = to_tf32(bm[(k0b + t + 4) * ldb + n0 + g]);
+}
 // d(rows 0-7 of the 16x8 tile) += A(8x8 at [r0][k0] of `am`) * B(8x8 at [k0b][n0] of `bm`): the upper half of
 // the warp MMA; lane (g, t) ends up with d[0], d[1] = rows g, columns 2t, 2t+1 of the product.
 __device__ __forceinline__ void mma_block8(float* d, const float* am, int lda, int r0, int k0, const float* bm,
@@ -136,7 +149,8 @@ __global__ void __launch_bounds__(128, 4) gdn_uw_kernel(const __grid_constant__ 
     constexpr int NA = D / 64;  // 64-column swizzle atoms per tile
     constexpr int LD = L::kLd;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by an offset from the array itself, so that the compiler still knows the pointer is shared memory
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sK = smem + L::kOffK;
     uint8_t* sV = smem + L::kOffV;
     uint8_t* sT = smem + L::kOffA;

@@ -23,6 +23,8 @@
 #pragma once
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "prefill_common.cuh"
 #include "prefill_uw.cuh"  // uw:: helpers (TF32 block products, packed fp32 pairs)
 
@@ -83,7 +85,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     using L = ZPSmem;
     constexpr int LD = L::kLd;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // aligned by an offset from the array itself, so that the compiler still knows the pointer is shared memory
+    uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int team = warp >> 2, tw = warp & 3, tt = tid & 127;
     uint8_t* sKQ = smem + L::kOffKQ;
@@ -121,8 +124,25 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     const int rep = p.vh / p.kh;               // v-heads per k-head
     const int rounds = (rep + 1) >> 1;         // head pairs per unit
     const int total_units = p.num_chunks * p.kh;
+    // Order of the work units.  Padded mode: the chunks of all sequences from the LAST chunk position to the
+    // first (sequences and k-heads inside), so that what this kernel writes last - the blocks of the first
+    // chunks - is what the state kernel, which starts right after it, reads first: still in L2.
+    // Packed mode: chunk_indices order.
+    const int per_pos = p.map.cu_seqlens ? 0 : (p.num_chunks / p.map.chunks_per_seq) * p.kh;  // units per chunk position
+    auto unit_chunk = [&](int unit, int& chunk, int& khead) {
+        if (per_pos) {
+            const int pos = unit / per_pos, rem = unit - pos * per_pos;
+            const int seq = rem / p.kh;
+            khead = rem - seq * p.kh;
+            chunk = seq * p.map.chunks_per_seq + (p.map.chunks_per_seq - 1 - pos);
+        } else {
+            chunk = unit / p.kh;
+            khead = unit - chunk * p.kh;
+        }
+    };
     auto issue_loads = [&](int unit) {  // one thread
-        const int chunk = unit / p.kh, khead = unit - chunk * p.kh;
+        int chunk, khead;
+        unit_chunk(unit, chunk, khead);
         const ChunkPos cp = locate_chunk(p.map, chunk);
         mbar_arrive_expect_tx(bar_load, 4 * 8192);
         for (int a = 0; a < 2; ++a) {
@@ -139,7 +159,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
         g = 0.f;
         const int hloc = 2 * rd + team;
         if (unit >= total_units || hloc >= rep) return;
-        const int chunk = unit / p.kh, khead = unit - chunk * p.kh;
+        int chunk, khead;
+        unit_chunk(unit, chunk, khead);
         const ChunkPos cp = locate_chunk(p.map, chunk);
         if (tt < cp.n) {
             const int head = khead * rep + hloc;
@@ -154,7 +175,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     uint32_t mma_it = 0;  // MMA groups this team has waited for (parity of bar_mma[team])
     bool stores_pending = false;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++it) {
-        const int chunk = unit / p.kh, khead = unit - chunk * p.kh;
+        int chunk, khead;
+        unit_chunk(unit, chunk, khead);
         const ChunkPos cp = locate_chunk(p.map, chunk);
         const int n = cp.n;
         for (int rd = 0; rd < rounds; ++rd) {
@@ -215,7 +237,7 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                     if (hf == 0) {
                         sRn[r] = rinv;
                         sLr[r] = log2f(rinv);
-                        if (*abort_flag == 0) p.norms[static_cast<size_t>(unit) * 128 + r] = rinv;
+                        if (*abort_flag == 0) p.norms[(static_cast<size_t>(chunk) * p.kh + khead) * 128 + r] = rinv;
                     }
                     __syncthreads();
                 }
@@ -253,35 +275,43 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                         uint32_t r[32];
                         tmem_ld32(tmem + kTmKQ + (static_cast<uint32_t>(32 * tw) << 16) + 32 * cb, r);
                         tmem_wait_ld();
+                        // kMask = false: a block of columns entirely below the diagonal in a full chunk keeps every element
+                        auto block = [&](auto mask_tag) {
+                            constexpr bool kMask = decltype(mask_tag)::value;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float o[8];
+                            for (int j = 0; j < 32; j += 8) {
+                                float o[8];
 #pragma unroll
-                            for (int e4 = 0; e4 < 2; ++e4) {
-                                const float4 gc = *reinterpret_cast<const float4*>(sG + 32 * cb + j + 4 * e4);
-                                float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
-                                if (kNorm) {  // the column's key norm enters through the exponent
-                                    const float4 lr = *reinterpret_cast<const float4*>(sLr + 32 * cb + j + 4 * e4);
-                                    gcv[0] -= lr.x; gcv[1] -= lr.y; gcv[2] -= lr.z; gcv[3] -= lr.w;
+                                for (int e4 = 0; e4 < 2; ++e4) {
+                                    const float4 gc = *reinterpret_cast<const float4*>(sG + 32 * cb + j + 4 * e4);
+                                    float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
+                                    if (kNorm) {  // the column's key norm enters through the exponent
+                                        const float4 lr = *reinterpret_cast<const float4*>(sLr + 32 * cb + j + 4 * e4);
+                                        gcv[0] -= lr.x; gcv[1] -= lr.y; gcv[2] -= lr.z; gcv[3] -= lr.w;
+                                    }
+#pragma unroll
+                                    for (int e = 0; e < 4; e += 2) {
+                                        const int col = 32 * cb + j + 4 * e4 + e, k = j + 4 * e4 + e;
+                                        const float d0 = (!kMask || col <= lim) ? ex2(gi - gcv[e]) : 0.f;
+                                        const float d1 = (!kMask || col + 1 <= lim) ? ex2(gi - gcv[e + 1]) : 0.f;
+                                        unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), fv), pk(d0, d1)),
+                                             o[4 * e4 + e], o[4 * e4 + e + 1]);
+                                    }
                                 }
-#pragma unroll
-                                for (int e = 0; e < 4; e += 2) {
-                                    const int col = 32 * cb + j + 4 * e4 + e, k = j + 4 * e4 + e;
-                                    const float d0 = (col <= lim) ? ex2(gi - gcv[e]) : 0.f;
-                                    const float d1 = (col + 1 <= lim) ? ex2(gi - gcv[e + 1]) : 0.f;
-                                    unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), fv), pk(d0, d1)),
-                                         o[4 * e4 + e], o[4 * e4 + e + 1]);
+                                if (!is_p) {
+                                    *reinterpret_cast<float4*>(&sA[i * LD + 32 * cb + j]) = make_float4(o[0], o[1], o[2], o[3]);
+                                    *reinterpret_cast<float4*>(&sA[i * LD + 32 * cb + j + 4]) = make_float4(o[4], o[5], o[6], o[7]);
+                                } else {
+                                    *reinterpret_cast<uint4*>(sP + tile_off(i, (32 * cb + j) >> 3)) =
+                                        make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]),
+                                                   pack_bf16(o[6], o[7]));
                                 }
                             }
-                            if (!is_p) {
-                                *reinterpret_cast<float4*>(&sA[i * LD + 32 * cb + j]) = make_float4(o[0], o[1], o[2], o[3]);
-                                *reinterpret_cast<float4*>(&sA[i * LD + 32 * cb + j + 4]) = make_float4(o[4], o[5], o[6], o[7]);
-                            } else {
-                                *reinterpret_cast<uint4*>(sP + tile_off(i, (32 * cb + j) >> 3)) =
-                                    make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]),
-                                               pack_bf16(o[6], o[7]));
-                            }
-                        }
+                        };
+                        if (cb < rb && n == kChunk)
+                            block(std::false_type{});
+                        else
+                            block(std::true_type{});
                     }
                     if (is_p && rb == 0) {  // rows 0-31 of P: columns 32-63 lie above the diagonal
 #pragma unroll
@@ -365,9 +395,13 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
                         if (ks >= 2 * cb) {
+                            uint32_t af[4], bf[2];
+                            load_afrag(af, sA, LD, 32 + 16 * rb, 8 * ks, lane);  // shared by the two column tiles
 #pragma unroll
-                            for (int nt = 0; nt < 2; ++nt)
-                                mma_block(d[nt], sA, LD, 32 + 16 * rb, 8 * ks, sA, LD, 8 * ks, 16 * cb + 8 * nt, lane);
+                            for (int nt = 0; nt < 2; ++nt) {
+                                load_bfrag(bf, sA, LD, 8 * ks, 16 * cb + 8 * nt, lane);
+                                mma_tf32(d[nt], af, bf);
+                            }
                         }
                     }
 #pragma unroll
@@ -377,9 +411,13 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
                         if (ks < 2 * (rb + 1)) {
+                            uint32_t af[4], bf[2];
+                            load_afrag(af, sA, LD, 32 + 16 * rb, 32 + 8 * ks, lane);
 #pragma unroll
-                            for (int nt = 0; nt < 2; ++nt)
-                                mma_block(e[nt], sA, LD, 32 + 16 * rb, 32 + 8 * ks, sA, LD, 8 * ks, 32 + 16 * cb + 8 * nt, lane);
+                            for (int nt = 0; nt < 2; ++nt) {
+                                load_bfrag(bf, sA, LD, 8 * ks, 32 + 16 * cb + 8 * nt, lane);
+                                mma_tf32(e[nt], af, bf);
+                            }
                         }
                     }
 #pragma unroll
