@@ -106,9 +106,11 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     uint64_t* bar_mma = bar_load + 2;  // [2], one per team
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_load + 4);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    int* teams_done = abort_flag + 1;  // teams that have finished reading the current unit's K tile
 
     if (tid == 0) {
         *abort_flag = 0;
+        *teams_done = 0;
         mbar_init(bar_load, 1);
         mbar_init(bar_kq, 1);
         mbar_init(&bar_mma[0], 1);
@@ -140,44 +142,53 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
             khead = unit - chunk * p.kh;
         }
     };
-    auto issue_loads = [&](int unit) {  // one thread
+    // A unit's coordinates are worked out once (a handful of integer divisions) and carried along.
+    struct UnitPos {
         int chunk, khead;
-        unit_chunk(unit, chunk, khead);
-        const ChunkPos cp = locate_chunk(p.map, chunk);
+        ChunkPos cp;
+        bool valid;
+    };
+    auto decode_unit = [&](int unit) {
+        UnitPos u{};
+        u.valid = unit < total_units;
+        if (u.valid) {
+            unit_chunk(unit, u.chunk, u.khead);
+            u.cp = locate_chunk(p.map, u.chunk);
+        }
+        return u;
+    };
+    auto issue_loads = [&](const UnitPos& u) {  // one thread
         mbar_arrive_expect_tx(bar_load, 4 * 8192);
         for (int a = 0; a < 2; ++a) {
-            tma_load_4d(sKQ + a * 16384, &tmK, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
-            tma_load_4d(sKQ + a * 16384 + 8192, &tmQ, bar_load, a * 64, khead, static_cast<int>(cp.tok0), cp.batch);
+            tma_load_4d(sKQ + a * 16384, &tmK, bar_load, a * 64, u.khead, static_cast<int>(u.cp.tok0), u.cp.batch);
+            tma_load_4d(sKQ + a * 16384 + 8192, &tmQ, bar_load, a * 64, u.khead, static_cast<int>(u.cp.tok0), u.cp.batch);
         }
     };
-    if (tid == 0 && static_cast<int>(blockIdx.x) < total_units) issue_loads(blockIdx.x);
+    UnitPos cur = decode_unit(blockIdx.x), nxt{};
+    if (tid == 0 && cur.valid) issue_loads(cur);
 
     // beta and the raw gate of this thread's token for (unit, round): fetched one round ahead, so that
     // their DRAM latency is not in front of every unit
-    auto fetch_scalars = [&](int unit, int rd, float& b, float& g) {
+    auto fetch_scalars = [&](const UnitPos& u, int rd, float& b, float& g) {
         b = 0.f;
         g = 0.f;
         const int hloc = 2 * rd + team;
-        if (unit >= total_units || hloc >= rep) return;
-        int chunk, khead;
-        unit_chunk(unit, chunk, khead);
-        const ChunkPos cp = locate_chunk(p.map, chunk);
-        if (tt < cp.n) {
-            const int head = khead * rep + hloc;
-            b = p.beta.load(cp.batch, cp.tok0 + tt, head);
-            if (p.gate.ptr) g = p.gate.load(cp.batch, cp.tok0 + tt, head);
+        if (!u.valid || hloc >= rep) return;
+        if (tt < u.cp.n) {
+            const int head = u.khead * rep + hloc;
+            b = p.beta.load(u.cp.batch, u.cp.tok0 + tt, head);
+            if (p.gate.ptr) g = p.gate.load(u.cp.batch, u.cp.tok0 + tt, head);
         }
     };
     float b_next, g_next;
-    fetch_scalars(blockIdx.x, 0, b_next, g_next);
+    fetch_scalars(cur, 0, b_next, g_next);
 
     uint32_t it = 0;      // units done by this CTA (parity of bar_load and bar_kq)
     uint32_t mma_it = 0;  // MMA groups this team has waited for (parity of bar_mma[team])
     bool stores_pending = false;
-    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++it) {
-        int chunk, khead;
-        unit_chunk(unit, chunk, khead);
-        const ChunkPos cp = locate_chunk(p.map, chunk);
+    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x, ++it, cur = nxt) {
+        const int chunk = cur.chunk, khead = cur.khead;
+        const ChunkPos cp = cur.cp;
         const int n = cp.n;
         for (int rd = 0; rd < rounds; ++rd) {
             const int hloc = 2 * rd + team;
@@ -185,7 +196,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
             const int head = khead * rep + hloc;
             // ---- beta, chunk-local cumulative gate, decay to the chunk's last token
             if (!active) {  // (odd number of v-heads per k-head: team 1 sits the last round out)
-                fetch_scalars(unit + gridDim.x, 0, b_next, g_next);
+                nxt = decode_unit(unit + gridDim.x);
+                fetch_scalars(nxt, 0, b_next, g_next);
             } else {
                 const float b_mine = b_next, g_mine = g_next;
                 if (tt < 64) {
@@ -196,11 +208,6 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                         if (lane >= m) g += y;
                     }
                     sPart[tt] = g;  // cumulative sum within each half of the chunk
-                }
-                if (stores_pending) {
-                    // the previous round's staged Z and PT must have been read out before A and P are rewritten
-                    if (tt == 0) bulk_wait_read<0>();
-                    stores_pending = false;
                 }
                 team_sync(team);
                 if (tt < 64) {
@@ -260,6 +267,13 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                 tc_fence_after_sync();
             }
             if (active) {
+                if (stores_pending) {
+                    // the previous round's staged Z and PT must have been read out before A and P are rewritten;
+                    // by now that has long happened and the wait costs nothing
+                    if (tt == 0) bulk_wait_read<0>();
+                    stores_pending = false;
+                    team_sync(team);
+                }
                 // ---- A = tril(beta_i (k_i.k_j) e^{g_i-g_j}, -1) in fp32 (warps 0, 1 of the team) and
                 //      P = scale tril((q_i.k_j) e^{g_i-g_j}) as a bf16 tile (warps 2, 3); thread = row
                 {
@@ -319,10 +333,12 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                             *reinterpret_cast<uint4*>(sP + tile_off(i, c16)) = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
-                if (rd + 1 < rounds)
-                    fetch_scalars(unit, rd + 1, b_next, g_next);
-                else
-                    fetch_scalars(unit + gridDim.x, 0, b_next, g_next);
+                if (rd + 1 < rounds) {
+                    fetch_scalars(cur, rd + 1, b_next, g_next);
+                } else {
+                    nxt = decode_unit(unit + gridDim.x);
+                    fetch_scalars(nxt, 0, b_next, g_next);
+                }
                 tc_fence_before_sync();
                 team_sync(team);
                 // ---- X = (I + A)^-1 in place.  Every warp owns one 16x16 diagonal block: its two 8x8 diagonal
@@ -488,12 +504,14 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                 ++mma_it;
                 tc_fence_after_sync();
             }
-            if (rd == rounds - 1) {
-                // both teams' MMAs have read the K tile and the A / P passes are long done: the next unit's
-                // tiles may land while the epilogue below runs
-                tc_fence_before_sync();
-                __syncthreads();
-                if (tid == 0 && unit + static_cast<int>(gridDim.x) < total_units) issue_loads(unit + gridDim.x);
+            if (rd == rounds - 1 && tt == 0) {
+                // This team's MMAs have read the K tile (or it sat the round out).  The team that gets here second
+                // knows that both are done with the tiles and requests the next unit's, which land while the
+                // epilogues run; the teams do not wait for one another.
+                if (atomicAdd(teams_done, 1) == 1) {
+                    *teams_done = 0;
+                    if (nxt.valid) issue_loads(nxt);
+                }
             }
             if (active) {
                 // ---- accumulators -> bf16 -> staged tiles (Z over T / dT, PT over P) -> two bulk copies
