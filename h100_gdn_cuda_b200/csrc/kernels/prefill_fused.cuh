@@ -458,6 +458,8 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 if (t0 + 32 < seq_tokens) a1 = p.gate.load(batch, seq_tok0 + t0 + 32, head);
             }
         };
+        // the Z, PT blocks and the V tiles are read exactly once: first in line for eviction from L2
+        const uint64_t once = l2_policy_evict_first();
         float ra0, ra1, rb0, rb1;  // raw gates of chunks c and c + 1
         load_raw(0, ra0, ra1);
         load_raw(1, rb0, rb1);
@@ -511,15 +513,15 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 #pragma unroll
                 for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffK + a * 8192, &tmK, &bar_full[s], a * 64, khead, tok, batch);
 #pragma unroll
-                for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffV + a * 8192, &tmV, &bar_full[s], a * 64, head, tok, batch);
+                for (int a = 0; a < 2; ++a) tma_load_4d_hint_w(st + L::kOffV + a * 8192, &tmV, &bar_full[s], a * 64, head, tok, batch, once);
                 if (emit_o) {
                     mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile + kZPBlockBytes);
-                    bulk_load_w(st + L::kOffZ, blk, kZPBlockBytes, &bar_full2[s]);
+                    bulk_load_hint_w(st + L::kOffZ, blk, kZPBlockBytes, &bar_full2[s], once);
 #pragma unroll
                     for (int a = 0; a < 2; ++a) tma_load_4d_w(st + L::kOffQ + a * 8192, &tmQ, &bar_full2[s], a * 64, khead, tok, batch);
                 } else {
                     mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile);  // no output: Z is all the second group needs
-                    bulk_load_w(st + L::kOffZ, blk, L::kTile, &bar_full2[s]);
+                    bulk_load_hint_w(st + L::kOffZ, blk, L::kTile, &bar_full2[s], once);
                 }
             }
         }

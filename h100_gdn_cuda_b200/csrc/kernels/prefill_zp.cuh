@@ -551,8 +551,10 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                 team_sync(team);
                 if (tt == 0 && *abort_flag == 0) {  // nothing is written once a wait has given up
                     uint8_t* dst = p.blocks + (static_cast<size_t>(chunk) * p.vh + head) * kZPBlockBytes;
-                    bulk_store(dst, stZ, 16384);
-                    bulk_store(dst + 16384, sP, 8192);
+                    // the state kernel reads these blocks back soon: ask L2 to hold on to them
+                    const uint64_t keep = l2_policy_evict_last();
+                    bulk_store_hint(dst, stZ, 16384, keep);
+                    bulk_store_hint(dst + 16384, sP, 8192, keep);
                     bulk_commit();
                 }
                 stores_pending = true;

@@ -213,6 +213,43 @@ GDN_DEVICE void bulk_load_w(void* dst, const void* src, uint32_t bytes, uint64_t
         : "memory");
 }
 
+// ------------------------------------------------------------------ L2 cache policies for bulk copies
+// evict_last: keep the lines in L2 as long as possible (data another kernel reads back soon);
+// evict_first: drop them first (data streamed through once).
+GDN_DEVICE uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+GDN_DEVICE uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+GDN_DEVICE void bulk_store_hint(void* dst, const void* src, uint32_t bytes, uint64_t policy) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(
+                     reinterpret_cast<uint64_t>(dst)),
+                 "r"(smem_u32(src)), "r"(bytes), "l"(policy)
+                 : "memory");
+}
+// warp-collective (one elected lane issues), with an L2 policy
+GDN_DEVICE void bulk_load_hint_w(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n\t}\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+GDN_DEVICE void tma_load_4d_hint_w(void* dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3, uint64_t policy) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\telect.sync _|pe, 0xffffffff;\n\t"
+        "@pe cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;\n\t}\n"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+        "l"(policy)
+        : "memory");
+}
+
 // ------------------------------------------------------------------ TMA stores (shared -> global)
 // Untiled bulk copy shared -> global (bulk-group completion); same alignment rules as bulk_load.
 GDN_DEVICE void bulk_store(void* dst, const void* src, uint32_t bytes) {
