@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     uint64_t* bar_go = bars + 12;     // state warps are past their chunk-boundary work: the epilogue may run
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    volatile int* issued = abort_flag + 1;  // chunks whose loads the producer has issued (read by the L2 prefetcher)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = p.seq_order ? p.seq_order[blockIdx.y] : static_cast<int>(blockIdx.x);
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 
     if (tid == 0) {
         *abort_flag = 0;
+        *issued = 0;
         mbar_init(&bar_full[0], 1);
         mbar_init(&bar_full[1], 1);
         mbar_init(&bar_empty[0], 1);
@@ -523,6 +525,30 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                     mbar_arrive_expect_tx_w(&bar_full2[s], L::kTile);  // no output: Z is all the second group needs
                     bulk_load_hint_w(st + L::kOffZ, blk, L::kTile, &bar_full2[s], once);
                 }
+                if (lane == 0) *issued = c + 1;
+            }
+        }
+    } else if (warp == 14) {
+        // =============================================================== L2 prefetcher
+        // With every SM running a chain, a stage's loads (requested one chunk time before they are needed)
+        // take longer than that to arrive from DRAM.  This otherwise idle warp pulls the tiles of the chunk
+        // kLead positions after the one the producer has just requested into L2, so that the producer's own
+        // loads find them there.  A hint only: when its bounded wait runs out it simply stops.
+        constexpr int kLead = 3;
+        if (lane == 0) {
+            for (int c = kLead; c < nchunks; ++c) {
+                int spins = 0;
+                while (*issued < c - kLead + 1 && *abort_flag == 0 && ++spins < (1 << 22)) __nanosleep(256);
+                if (*issued < c - kLead + 1) break;
+                const int tok = static_cast<int>(seq_tok0 + static_cast<long long>(c) * kChunk);
+                const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kZPBlockBytes;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    tma_prefetch_4d(&tmK, a * 64, khead, tok, batch);
+                    tma_prefetch_4d(&tmV, a * 64, head, tok, batch);
+                    if (emit_o) tma_prefetch_4d(&tmQ, a * 64, khead, tok, batch);
+                }
+                bulk_prefetch_l2(blk, emit_o ? kZPBlockBytes : L::kTile);
             }
         }
     } else if (warp == 13) {

@@ -197,6 +197,10 @@ GDN_DEVICE void tma_prefetch_2d(const void* tmap, int c0, int c1) {
                  "r"(c0), "r"(c1)
                  : "memory");
 }
+// Untiled counterpart: pull `bytes` (a multiple of 16) at a 16-byte aligned address into L2.
+GDN_DEVICE void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes) : "memory");
+}
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(
