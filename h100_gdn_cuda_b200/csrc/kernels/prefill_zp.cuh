@@ -50,8 +50,8 @@ struct ZPSmem {
     static constexpr int kTeam = 32768;                  // per-team area starts here, two of them
     static constexpr int kOffA = 0;                      // A / X fp32 (17 KB), later T | (dT)^T, later the staged Z
     static constexpr int kOffP = 64 * kLd * 4;           // 17408: P tile (8 KB), later the staged PT
-    static constexpr int kOffVec = kOffP + 8192;         // beta[64], g log2e[64], d[64]
-    static constexpr int kTeamBytes = kOffVec + 3 * 64 * 4 + 256;  // 26624 (multiple of 1024)
+    static constexpr int kOffVec = kOffP + 8192;         // beta[64], g log2e[64], d[64], scan partials[64], column factors[32]
+    static constexpr int kTeamBytes = kOffVec + 2048;    // 27648 (multiple of 1024)
     static constexpr int kOffNorm = kTeam + 2 * kTeamBytes;  // kNorm: inverse row norms of K [64] and Q [64], their log2 [128]
     static constexpr int kOffBar = kOffNorm + 1024;
     static constexpr int kBytes = kOffBar + 128 + 1024;
@@ -98,7 +98,8 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     float* sBeta = reinterpret_cast<float*>(tbase + L::kOffVec);
     float* sG = sBeta + 64;
     float* sD = sG + 64;
-    float* sPart = sD + 64;
+    float* sPart = sD + 64;   // 64 floats: partial sums of the gate scan (each half of the chunk on its own)
+    float* sC = sPart + 64;    // 32 floats: e^{g_32 - g_j} for the columns j < 32 of the block below the diagonal
     float* sRn = reinterpret_cast<float*>(smem + L::kOffNorm);  // [128] inverse norms (K rows, then Q rows)
     float* sLr = sRn + 128;                                      // [128] their log2
     uint64_t* bar_load = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                     sBeta[tt] = b_mine;
                     sG[tt] = g * 1.4426950408889634f;  // times log2(e): decay factors are ex2 of differences
                     sD[tt] = __expf(gl - g);
+                    if (tt < 32) sC[tt] = __expf(sPart[32] + sPart[31] - g);  // g_32 is the first entry of the second scan plus the first half's total
                 }
                 team_sync(team);
             }
@@ -289,15 +291,25 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                         uint32_t r[32];
                         tmem_ld32(tmem + kTmKQ + (static_cast<uint32_t>(32 * tw) << 16) + 32 * cb, r);
                         tmem_wait_ld();
-                        // kMask = false: a block of columns entirely below the diagonal in a full chunk keeps every element
-                        auto block = [&](auto mask_tag) {
-                            constexpr bool kMask = decltype(mask_tag)::value;
+                        // kMode 0: the block meets the diagonal (or the chunk is ragged): every element masked.
+                        // kMode 1: a block entirely below the diagonal of a full chunk: every element kept.
+                        // kMode 2: the same, with the decay of the block factored: for rows i >= 32 and columns j < 32
+                        //          e^{g_i-g_j} = e^{g_i-g_32} e^{g_32-g_j}, both factors <= 1 (the cumulative gate only
+                        //          falls), so the column factors come from a table and no ex2 is left per element.
+                        auto block = [&](auto mode_tag) {
+                            constexpr int kMode = decltype(mode_tag)::value;
+                            constexpr bool kMask = kMode == 0;
+                            f2 fvr = fv;
+                            if (kMode == 2) {
+                                const float ri = ex2(gi - sG[32]);
+                                fvr = mul2(fv, pk(ri, ri));
+                            }
 #pragma unroll
                             for (int j = 0; j < 32; j += 8) {
                                 float o[8];
 #pragma unroll
                                 for (int e4 = 0; e4 < 2; ++e4) {
-                                    const float4 gc = *reinterpret_cast<const float4*>(sG + 32 * cb + j + 4 * e4);
+                                    const float4 gc = *reinterpret_cast<const float4*>((kMode == 2 ? sC : sG) + 32 * cb + j + 4 * e4);
                                     float gcv[4] = {gc.x, gc.y, gc.z, gc.w};
                                     if (kNorm) {  // the column's key norm enters through the exponent
                                         const float4 lr = *reinterpret_cast<const float4*>(sLr + 32 * cb + j + 4 * e4);
@@ -306,9 +318,15 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
 #pragma unroll
                                     for (int e = 0; e < 4; e += 2) {
                                         const int col = 32 * cb + j + 4 * e4 + e, k = j + 4 * e4 + e;
-                                        const float d0 = (!kMask || col <= lim) ? ex2(gi - gcv[e]) : 0.f;
-                                        const float d1 = (!kMask || col + 1 <= lim) ? ex2(gi - gcv[e + 1]) : 0.f;
-                                        unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), fv), pk(d0, d1)),
+                                        float d0, d1;
+                                        if (kMode == 2) {
+                                            d0 = gcv[e];
+                                            d1 = gcv[e + 1];
+                                        } else {
+                                            d0 = (!kMask || col <= lim) ? ex2(gi - gcv[e]) : 0.f;
+                                            d1 = (!kMask || col + 1 <= lim) ? ex2(gi - gcv[e + 1]) : 0.f;
+                                        }
+                                        unpk(mul2(mul2(pk(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), fvr), pk(d0, d1)),
                                              o[4 * e4 + e], o[4 * e4 + e + 1]);
                                     }
                                 }
@@ -322,10 +340,14 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
                                 }
                             }
                         };
-                        if (cb < rb && n == kChunk)
-                            block(std::false_type{});
-                        else
-                            block(std::true_type{});
+                        if (cb < rb && n == kChunk) {
+                            if (kNorm)
+                                block(std::integral_constant<int, 1>{});
+                            else
+                                block(std::integral_constant<int, 2>{});
+                        } else {
+                            block(std::integral_constant<int, 0>{});
+                        }
                     }
                     if (is_p && rb == 0) {  // rows 0-31 of P: columns 32-63 lie above the diagonal
 #pragma unroll
