@@ -40,7 +40,8 @@ class RecurrentArgs(C.Structure):
                 ("out", TokenTensor), ("beta", TokenScalar), ("gate", TokenScalar),
                 ("state_in", State), ("state_out", State), ("num_accepted_tokens", C.c_void_p),
                 ("scale", C.c_float), ("is_qk_norm", C.c_int32), ("store_step_state", C.c_int32),
-                ("gating_a", TokenScalar), ("gating_b", TokenScalar), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p)]
+                ("gating_a", TokenScalar), ("gating_b", TokenScalar), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p),
+                ("state_indices", C.c_void_p), ("state_dtype", C.c_int32)]
 
 
 class ComputeUWArgs(C.Structure):

@@ -177,18 +177,22 @@ def transpose_to_mn_major(input: torch.Tensor, alignment: int = 16) -> torch.Ten
 def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=None, cu_seqlens=None,
                       num_accepted_tokens=None, inference_mode: int = 0, is_qk_norm: bool = False,
                       scale: Optional[float] = None, *, inplace_state: bool = False, gating=None,
-                      _max_head_dim: int = 256):
+                      state_indices=None, _max_head_dim: int = 256):
     """Token recurrence for decode / speculative verify / short prefill; python_api.cpp:107-122
     and csrc/apis/gdn_forward.cpp:134-206.
 
     Returns (output, new_state).  new_state is (B, vh, dv, dk), or one state per token
     ((B,T,vh,dv,dk) / (N,vh,dv,dk)) when inference_mode == SpecVerify.  `gate` may be bf16
-    or fp32 (or None for no decay).  Extensions (keyword-only): with `inplace_state=True` the new
+    or fp32 (or None for no decay).  An fp32 `initial_state` (extension; head dims 64 and 128) keeps the
+    state in fp32: it is read, updated and returned as fp32.  Extensions (keyword-only): with `inplace_state=True` the new
     state overwrites `initial_state`, which is returned (its (dv, dk) blocks must be contiguous);
     with `gating=(A_log, dt_bias, a, b)` the kernel computes beta = sigmoid(b) and
     gate = -exp(A_log) * softplus(a + dt_bias) itself from the layer's raw projections (what
     fused_gdn_gating would produce, without the extra launch or the bf16 rounding of its
-    outputs) and `beta` / `gate` must be None."""
+    outputs) and `beta` / `gate` must be None; with `state_indices` (int32, one entry per sequence)
+    `initial_state` is a pool of states (P, vh, dv, dk): sequence s uses slot state_indices[s], the new
+    state is written back to the same slot (the pool is returned), and a negative slot marks a padding
+    sequence that is skipped altogether."""
     if gating is not None:
         _require(beta is None and gate is None, "pass either gating=(A_log, dt_bias, a, b) or beta/gate, not both")
         g_A, g_dt, g_a, g_b = gating
@@ -212,8 +216,11 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
         scale = 1.0 / math.sqrt(d)
     q, k, v = _pad_last(query, d_al), _pad_last(key, d_al), _pad_last(value, dv_al)
     s_in = initial_state
+    state_dtype = torch.bfloat16
     if s_in is not None:
-        _cuda_bf16(s_in, "initial_state")
+        # an fp32 initial state selects the fp32-state kernels: the state stays fp32 (extension)
+        _require(s_in.is_cuda and s_in.dtype in (torch.bfloat16, torch.float32), "initial_state must be a bf16 or fp32 CUDA tensor")
+        state_dtype = s_in.dtype
         if s_in.shape[-1] != d_al or s_in.shape[-2] != dv_al:
             _require(not inplace_state, "in-place state needs head dims that are multiples of 64")
             s_in = torch.nn.functional.pad(s_in, (0, d_al - s_in.shape[-1], 0, dv_al - s_in.shape[-2]))
@@ -229,20 +236,27 @@ def recurrent_forward(query, key, value, initial_state=None, beta=None, gate=Non
     out = torch.empty_like(v)
     if store_steps:
         lead = (total,) if varlen else (batch, seq_len)
-        s_out = torch.empty(*lead, vh, dv_al, d_al, dtype=torch.bfloat16, device=q.device)
+        s_out = torch.empty(*lead, vh, dv_al, d_al, dtype=state_dtype, device=q.device)
         so_desc = cabi.State(s_out.data_ptr(), vh * dv_al * d_al, dv_al * d_al)
-    elif inplace_state:
-        _require(s_in is not None, "inplace_state needs an initial_state")
+    elif inplace_state or state_indices is not None:
+        _require(s_in is not None, "inplace_state / state_indices need an initial_state")
+        _require(s_in is initial_state or s_in.data_ptr() == initial_state.data_ptr(),
+                 "the state pool must have head dims that are multiples of 64 and contiguous (dv, dk) blocks")
         s_out = s_in
         so_desc = _state_desc(s_out)
     else:
-        s_out = torch.empty(batch, vh, dv_al, d_al, dtype=torch.bfloat16, device=q.device)
+        s_out = torch.empty(batch, vh, dv_al, d_al, dtype=state_dtype, device=q.device)
         so_desc = _state_desc(s_out)
     args = cabi.RecurrentArgs(
         _shape(batch, seq_len, total, kh, vh, d_al, dv_al, cu_seqlens),
         _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(v, varlen), _token_tensor(out, varlen),
         _token_scalar(beta, varlen), _token_scalar(gate, varlen), _state_desc(s_in), so_desc,
         _i32(num_accepted_tokens, "num_accepted_tokens"), float(scale), int(bool(is_qk_norm)), int(store_steps))
+    args.state_dtype = cabi.GDN_F32 if state_dtype == torch.float32 else cabi.GDN_BF16
+    if state_indices is not None:
+        _require(not store_steps, "state_indices cannot be combined with per-token states")
+        _require(state_indices.numel() == batch, "state_indices needs one entry per sequence")
+        args.state_indices = _i32(state_indices, "state_indices")
     if gating is not None:
         args.gating_a, args.gating_b = _token_scalar(g_a, varlen), _token_scalar(g_b, varlen)
         args.A_log, args.dt_bias = g_A.data_ptr(), g_dt.data_ptr()

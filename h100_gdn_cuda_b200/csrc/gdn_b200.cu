@@ -74,19 +74,19 @@ __global__ void gdn_selftest_wait_kernel(long long limit_cycles, int* status) {
 }
 
 // ------------------------------------------------------------------ recurrent
-template <int DK, bool kRing, bool kLean = false>
+template <int DK, bool kRing, bool kLean = false, bool kF32 = false>
 static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st) {
-    constexpr int smem = recurrent_smem_bytes<DK, kRing>();
+    constexpr int smem = recurrent_smem_bytes<DK, kRing, kF32>();
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev]) {
-        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK, kRing, kLean>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        GDN_CUDA(cudaFuncSetAttribute(gdn_recurrent_kernel<DK, kRing, kLean, kF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_set[dev] = true;
     }
-    const int per_sm = recurrent_ctas_per_sm<DK, kRing>();
+    const int per_sm = recurrent_ctas_per_sm<DK, kRing, kF32>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
-    gdn_recurrent_kernel<DK, kRing, kLean><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
+    gdn_recurrent_kernel<DK, kRing, kLean, kF32><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
@@ -282,6 +282,9 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
         GDN_REQUIRE(!(a->store_step_state && a->state_in.ptr == a->state_out.ptr),
                     "state_out may not alias state_in when step states are stored");
     }
+    GDN_REQUIRE(a->state_dtype == GDN_BF16 || a->state_dtype == GDN_F32, "gdn_recurrent_forward: state_dtype must be bf16 or f32");
+    GDN_REQUIRE(!(a->state_indices && a->store_step_state), "gdn_recurrent_forward: state_indices cannot be combined with step states");
+    GDN_REQUIRE(!(a->state_indices && !a->state_in.ptr), "gdn_recurrent_forward: state_indices needs a state_in pool");
     DeviceInfo* d = nullptr;
     if (int rc = get_device_info(&d)) return rc;
 
@@ -301,10 +304,11 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.gating_param_f32 = fused_gating && a->gating_a.dtype == GDN_F32;
     p.A_log = a->A_log;
     p.dt_bias = a->dt_bias;
-    p.state_in = (const __nv_bfloat16*)a->state_in.ptr; p.si_ss = a->state_in.stride_seq; p.si_sh = a->state_in.stride_head;
-    p.state_out = (__nv_bfloat16*)a->state_out.ptr; p.so_ss = a->state_out.stride_seq; p.so_sh = a->state_out.stride_head;
+    p.state_in = a->state_in.ptr; p.si_ss = a->state_in.stride_seq; p.si_sh = a->state_in.stride_head;
+    p.state_out = a->state_out.ptr; p.so_ss = a->state_out.stride_seq; p.so_sh = a->state_out.stride_head;
     p.cu_seqlens = s.cu_seqlens;
     p.num_accepted = a->num_accepted_tokens;
+    p.state_idx = a->state_indices;
     p.batch = s.batch; p.seq_len = s.seq_len; p.kh = s.num_k_heads; p.vh = s.num_v_heads; p.dv = s.head_dim_v;
     p.scale = a->scale;
     p.is_qk_norm = a->is_qk_norm; p.store_step = a->store_step_state;
@@ -321,8 +325,14 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     const int force_jit = g_force_jit.load(std::memory_order_relaxed);
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
                                    : (s.seq_len > ring_min);
-    if (force_jit) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
-    const bool lean = !s.cu_seqlens && s.seq_len == 1 && p.state_in != nullptr && !p.store_step;
+    if (force_jit && a->state_dtype != GDN_F32) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
+    if (a->state_dtype == GDN_F32) {
+        // fp32 states: the two head dims serving configurations use, on the decode and the multi-token instance
+        if (s.head_dim_k == 128) return ring ? launch_recurrent_t<128, true, false, true>(p, d->sms, st) : launch_recurrent_t<128, false, false, true>(p, d->sms, st);
+        if (s.head_dim_k == 64) return ring ? launch_recurrent_t<64, true, false, true>(p, d->sms, st) : launch_recurrent_t<64, false, false, true>(p, d->sms, st);
+        return fail(GDN_ERR_UNSUPPORTED, "gdn_recurrent_forward: fp32 states are built for dk = 64 and 128 (got %d)", s.head_dim_k);
+    }
+    const bool lean = !s.cu_seqlens && s.seq_len == 1 && p.state_in != nullptr && !p.store_step && !p.state_idx;
     switch (s.head_dim_k) {
         case 64: return launch_recurrent<64>(p, d->sms, st, ring, lean);
         case 128: return launch_recurrent<128>(p, d->sms, st, ring, lean);

@@ -43,11 +43,12 @@ struct RecurrentParams {
     int beta_f32, gate_f32;
     int64_t beta_sb, beta_st, beta_sh;
     int64_t gate_sb, gate_st, gate_sh;
-    const __nv_bfloat16* state_in;
-    __nv_bfloat16* state_out;
+    const void* state_in;   // bf16, or fp32 in the kF32 instances; strides in elements of that type
+    void* state_out;
     int64_t si_ss, si_sh, so_ss, so_sh;
     const int* cu_seqlens;
     const int* num_accepted;
+    const int* state_idx;  // indexed state pool: slot of every sequence (negative: padding sequence), or NULL
     int batch, seq_len, kh, vh, dv;
     float scale;
     int is_qk_norm, store_step;
@@ -71,10 +72,10 @@ constexpr int kRecTokRingMin = 16;  // sequences longer than this use it
 // One ring stage: the 32 x DK state tile, then k and q (DK bf16 each) and the 32 entries of v that
 // belong to the tile's rows, for the unit's first token (decode instance) or its first
 // kRecTokBlock tokens (multi-token instance; same layout as a slot of the token ring).
-template <int DK, bool kRing = false>
+template <int DK, bool kRing = false, bool kF32 = false>
 struct RecStage {
     static constexpr int kTok = kRing ? kRecTokBlock : 1;
-    static constexpr int kTileBytes = kRecTileRows * DK * 2;
+    static constexpr int kTileBytes = kRecTileRows * DK * (kF32 ? 4 : 2);
     static constexpr int kOffK = kTileBytes;
     static constexpr int kOffQ = kOffK + kTok * DK * 2;
     static constexpr int kOffV = kOffQ + kTok * DK * 2;
@@ -90,9 +91,14 @@ struct RecTokSlot {
     static constexpr int kBytes = kOffV + kRecTokBlock * kRecTileRows * 2;
 };
 
-template <int DK, bool kRing = true>
+// fp32 states double the tile: the decode instance then keeps two tiles in flight instead of four
+template <bool kRing, bool kF32>
+constexpr int recurrent_stages() {
+    return kRing ? kRecStagesRing : (kF32 ? 2 : kRecStages);
+}
+template <int DK, bool kRing = true, bool kF32 = false>
 constexpr int recurrent_smem_bytes() {
-    return (kRing ? kRecStagesRing : kRecStages) * RecStage<DK, kRing>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
+    return recurrent_stages<kRing, kF32>() * RecStage<DK, kRing, kF32>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
 }
 
 namespace rec {
@@ -132,16 +138,31 @@ __device__ __forceinline__ float hsum(f2 v) {
 // kLean (decode instance only): the launch is plain single-token decode from a given state - padded
 // inputs with one token per sequence, an initial state, one state per sequence out.  The host
 // promises that, and the corresponding run-time tests compile away.
-template <int DK, bool kRing = true, bool kLean = false>
+// kF32: the state is kept in fp32 in memory (read, updated and written as such; serving engines that run
+// many decode steps on one state use it to avoid a bf16 rounding per step).
+namespace rec {
+template <bool kF32>
+struct StateElem {
+    typedef __nv_bfloat16 type;
+};
+template <>
+struct StateElem<true> {
+    typedef float type;
+};
+}  // namespace rec
+template <int DK, bool kRing = true, bool kLean = false, bool kF32 = false>
 __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     static_assert(!(kRing && kLean), "the lean instance is a decode instance");
     using namespace ptx;
     using namespace rec;
-    using Stage = RecStage<DK, kRing>;
+    using Stage = RecStage<DK, kRing, kF32>;
+    using ST = typename StateElem<kF32>::type;
+    const ST* const state_in = static_cast<const ST*>(p.state_in);
+    ST* const state_out = static_cast<ST*>(p.state_out);
     constexpr int NQ = DK / 32;  // packed pairs per row per lane (lane owns 4 columns of every 64)
     extern __shared__ __align__(128) uint8_t smem[];
     using TokSlot = RecTokSlot<DK>;
-    constexpr int kStages = kRing ? kRecStagesRing : kRecStages;
+    constexpr int kStages = recurrent_stages<kRing, kF32>();
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * Stage::kBytes);
     uint64_t* tokfull = full + kStages;  // [2]
     uint8_t* tokbase = smem + kStages * Stage::kBytes + 128;
@@ -183,6 +204,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
 
     struct Unit {
         int seq, head, khead, ntok, rb0;
+        int slot;  // where the sequence's state lives (its index, or its slot of an indexed pool; negative: skip)
         long long tok0, bidx;
     };
     // head counts are almost always powers of two: shifts instead of integer divisions then
@@ -214,16 +236,21 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             t.bidx = t.seq;
         }
         if (p.num_accepted) t.ntok = min(t.ntok, p.num_accepted[t.seq]);
+        t.slot = t.seq;
+        if (!kLean && p.state_idx) {
+            t.slot = p.state_idx[t.seq];
+            if (t.slot < 0) t.ntok = 0;
+        }
         return t;
     };
     // Producer (one thread): everything tile `rb` of `unit` needs for its first token.
     // source addresses of the producer's current unit (its first token), computed when the unit changes
-    const __nv_bfloat16* prod_s = nullptr;
+    const ST* prod_s = nullptr;
     const __nv_bfloat16* prod_k = nullptr;
     const __nv_bfloat16* prod_q = nullptr;
     const __nv_bfloat16* prod_v = nullptr;
     auto producer_bases = [&](const Unit& t) {
-        prod_s = has_in ? p.state_in + t.seq * p.si_ss + t.head * p.si_sh : nullptr;
+        prod_s = has_in ? state_in + static_cast<long long>(max(t.slot, 0)) * p.si_ss + t.head * p.si_sh : nullptr;
         prod_k = p.k + t.bidx * p.k_sb + t.tok0 * p.k_st + t.khead * p.k_sh;
         prod_q = p.q + t.bidx * p.q_sb + t.tok0 * p.q_st + t.khead * p.q_sh;
         prod_v = p.v + t.bidx * p.v_sb + t.tok0 * p.v_st + t.head * p.v_sh;
@@ -318,7 +345,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         }
         // where this unit's outputs go: computed once per unit, not per tile or token
         __nv_bfloat16* const out_unit = p.out + T.bidx * p.o_sb + T.tok0 * p.o_st + T.head * p.o_sh;
-        __nv_bfloat16* const sout_unit = p.state_out + T.head * p.so_sh + (store_step ? 0 : static_cast<long long>(T.seq) * p.so_ss);
+        ST* const sout_unit = state_out + T.head * p.so_sh + (store_step ? 0 : static_cast<long long>(max(T.slot, 0)) * p.so_ss);
         // fused gating: the first token's (the ring instance: the first 32 tokens') raw projections become
         // beta and the gate once per unit, not once per tile
         if (p.fused_gating) apply_gating(T.head, beta_first, g_first);
@@ -344,9 +371,15 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                     const int row = warp * 8 + 2 * j + half;
 #pragma unroll
                     for (int pc = 0; pc < NQ / 2; ++pc) {
-                        const uint2 w = *reinterpret_cast<const uint2*>(st + (row * DK + pc * 64 + l16 * 4) * 2);
-                        S[j][2 * pc] = bf2_to_f2(w.x);
-                        S[j][2 * pc + 1] = bf2_to_f2(w.y);
+                        if (kF32) {
+                            const float4 w = *reinterpret_cast<const float4*>(st + (row * DK + pc * 64 + l16 * 4) * 4);
+                            S[j][2 * pc] = pk(w.x, w.y);
+                            S[j][2 * pc + 1] = pk(w.z, w.w);
+                        } else {
+                            const uint2 w = *reinterpret_cast<const uint2*>(st + (row * DK + pc * 64 + l16 * 4) * 2);
+                            S[j][2 * pc] = bf2_to_f2(w.x);
+                            S[j][2 * pc + 1] = bf2_to_f2(w.y);
+                        }
                     }
                 }
             } else {
@@ -493,7 +526,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 }
                 if (store_step && ok) {
                     const long long sidx = p.cu_seqlens ? (T.tok0 + t) : (static_cast<long long>(T.seq) * p.seq_len + t);
-                    __nv_bfloat16* sp = sout_unit + sidx * p.so_ss + rb * (kRecTileRows * DK);
+                    ST* sp = sout_unit + sidx * p.so_ss + rb * (kRecTileRows * DK);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int row = warp * 8 + 2 * j + half;
@@ -502,10 +535,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                             float a0, a1, a2, a3;
                             unpk(S[j][2 * pc], a0, a1);
                             unpk(S[j][2 * pc + 1], a2, a3);
-                            uint2 w;
-                            w.x = pack_bf16(a0, a1);
-                            w.y = pack_bf16(a2, a3);
-                            *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                            if (kF32) {
+                                *reinterpret_cast<float4*>(sp + row * DK + pc * 64 + l16 * 4) = make_float4(a0, a1, a2, a3);
+                            } else {
+                                uint2 w;
+                                w.x = pack_bf16(a0, a1);
+                                w.y = pack_bf16(a2, a3);
+                                *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                            }
                         }
                     }
                 }
@@ -613,8 +650,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             }
 
             }
-            if (!store_step && ok) {
-                __nv_bfloat16* sp = sout_unit + rb * (kRecTileRows * DK);
+            if (!store_step && ok && T.slot >= 0) {
+                ST* sp = sout_unit + rb * (kRecTileRows * DK);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int row = warp * 8 + 2 * j + half;
@@ -623,10 +660,14 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                         float a0, a1, a2, a3;
                         unpk(S[j][2 * pc], a0, a1);
                         unpk(S[j][2 * pc + 1], a2, a3);
-                        uint2 w;
-                        w.x = pack_bf16(a0, a1);
-                        w.y = pack_bf16(a2, a3);
-                        *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                        if (kF32) {
+                            *reinterpret_cast<float4*>(sp + row * DK + pc * 64 + l16 * 4) = make_float4(a0, a1, a2, a3);
+                        } else {
+                            uint2 w;
+                            w.x = pack_bf16(a0, a1);
+                            w.y = pack_bf16(a2, a3);
+                            *reinterpret_cast<uint2*>(sp + row * DK + pc * 64 + l16 * 4) = w;
+                        }
                     }
                 }
             }
@@ -637,14 +678,15 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     if (tid == 0 && abort_flag && p.status) atomicExch(p.status, 1);
 }
 
-template <int DK, bool kRing = false>
+// (fp32 states at DK = 128: the 16-byte accesses need a few more registers than four CTAs per SM leave)
+template <int DK, bool kRing = false, bool kF32 = false>
 constexpr int recurrent_ctas_per_sm() {
-    return kRing ? (DK <= 64 ? 4 : 3) : (DK <= 128 ? 4 : 2);
+    return kRing ? (DK <= 64 ? 4 : 3) : (DK <= 128 ? ((kF32 && DK > 64) ? 3 : 4) : 2);
 }
 
-template <int DK, bool kRing = false, bool kLean = false>
-__global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK, kRing>()) gdn_recurrent_kernel(const RecurrentParams p) {
-    gdn_recurrent_body<DK, kRing, kLean>(p);
+template <int DK, bool kRing = false, bool kLean = false, bool kF32 = false>
+__global__ void __launch_bounds__(kRecThreads, recurrent_ctas_per_sm<DK, kRing, kF32>()) gdn_recurrent_kernel(const RecurrentParams p) {
+    gdn_recurrent_body<DK, kRing, kLean, kF32>(p);
 }
 
 }  // namespace gdn

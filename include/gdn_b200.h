@@ -168,7 +168,13 @@ int gdn_transpose_mn_major(const void* input, void* output, int32_t elem_size, i
  *                               beta = sigmoid(gating_b),  g = -exp(A_log[h]) * softplus(gating_a + dt_bias[h])
  *                           gating_a / gating_b are per-token scalars like beta / gate (same dtype for
  *                           both, bf16 or f32); A_log and dt_bias are contiguous vectors of num_v_heads
- *                           entries of that dtype.  `beta` and `gate` are then ignored. */
+ *                           entries of that dtype.  `beta` and `gate` are then ignored.
+ *   state_indices != NULL : indexed state pool, as serving engines keep one (no counterpart in the reference):
+ *                           device int32[batch]; sequence s reads its state from slot state_indices[s] of
+ *                           state_in and writes the new one to the same slot of state_out (addressed
+ *                           slot*stride_seq; the two may be the same pool).  A negative slot marks a padding
+ *                           sequence: nothing is read, computed or written for it.  Not combined with
+ *                           store_step_state. */
 typedef struct {
     GdnShape shape;
     GdnTokenTensor q, k, v, out;
@@ -182,6 +188,11 @@ typedef struct {
     GdnTokenScalar gating_a, gating_b;
     const void* A_log;
     const void* dt_bias;
+    const int32_t* state_indices;
+    /* GDN_BF16 (0, the reference's only state type) or GDN_F32: element type of state_in and state_out, whose
+     * strides then count fp32 elements.  A state kept in fp32 is not rounded between decode steps.  No
+     * counterpart in the reference; built for dk = 64 and 128. */
+    int32_t state_dtype;
 } GdnRecurrentArgs;
 int gdn_recurrent_forward(const GdnRecurrentArgs* args, gdn_stream_t stream);
 

@@ -189,3 +189,51 @@ def test_bounded_wait_gives_up_and_context_survives(gdn):
     o_ref, _ = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), beta.bfloat16().float(), g, p["state"].float())
     close(o, o_ref, "o after the self-test")
     assert check_status(gdn) == 0
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_indexed_state_pool(gdn, T):
+    """A pool of states addressed through state_indices (what a serving engine keeps): the sequences of the
+    batch read and update their own slots, a negative slot skips the sequence, the other slots stay as they were."""
+    B, kh, vh, d, P = 6, 2, 4, 128, 10
+    p = synthetic.decode_inputs(B, T, kh, vh, d, seed=21 + T)
+    beta, g = O.gating_ref(p["A_log"], p["dt_bias"], p["a"], p["b"])
+    gen = torch.Generator().manual_seed(5)
+    pool0 = (torch.randn(P, vh, d, d, generator=gen) * 0.02).bfloat16()
+    idx = torch.tensor([7, 2, -1, 9, 0, 4], dtype=torch.int32)
+    pool = pool0.clone().cuda()
+    pd = dev(p)
+    o, ret = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pool, beta.bfloat16().cuda(), g.cuda(), inference_mode=gdn.Decode,
+                                   is_qk_norm=True, state_indices=idx.cuda())
+    assert ret.data_ptr() == pool.data_ptr()
+    live = [i for i in range(B) if idx[i] >= 0]
+    s0 = pool0[idx[live].long()].float()
+    o_ref, s_ref = O.recurrent_ref(p["q"][live].float(), p["k"][live].float(), p["v"][live].float(), beta.bfloat16()[live].float(),
+                                   g[live], s0, is_qk_norm=True)
+    close(o[live], o_ref, "o of the live sequences")
+    close(pool[idx[live].long()], s_ref, "updated slots")
+    untouched = [s for s in range(P) if s not in idx.tolist()]
+    assert torch.equal(pool[untouched].cpu(), pool0[untouched])
+    assert check_status(gdn) == 0
+
+
+@pytest.mark.parametrize("B,T,kh,vh,d", [(6, 1, 2, 4, 128), (3, 4, 2, 4, 64), (2, 40, 1, 2, 128)])
+def test_fp32_state(gdn, B, T, kh, vh, d):
+    """A state kept in fp32: read, updated and returned as fp32 (decode, a few tokens, and a run long enough for
+    the multi-token instance).  The state is compared with a tighter gate than bf16 states allow."""
+    p = synthetic.decode_inputs(B, T, kh, vh, d, seed=51 + T)
+    beta, g = O.gating_ref(p["A_log"], p["dt_bias"], p["a"], p["b"])
+    s0 = p["state"].float() + 1e-4 * torch.randn(p["state"].shape, generator=torch.Generator().manual_seed(1))  # not bf16-exact
+    pd = dev(p)
+    o, s = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], s0.cuda(), beta.bfloat16().cuda(), g.cuda(), inference_mode=gdn.Decode,
+                                 is_qk_norm=True)
+    assert s.dtype == torch.float32
+    o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), beta.bfloat16().float(), g, s0, is_qk_norm=True)
+    close(o, o_ref, "o")
+    assert O.rel_fro(s.cpu(), s_ref) < 1e-5, O.rel_fro(s.cpu(), s_ref)
+    # two decode steps on an fp32 state equal one two-token call bit for bit in the state's precision class
+    if T == 1:
+        o2, s2 = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], s, beta.bfloat16().cuda(), g.cuda(), inference_mode=gdn.Decode, is_qk_norm=True)
+        _, s2_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), beta.bfloat16().float(), g, s_ref, is_qk_norm=True)
+        assert O.rel_fro(s2.cpu(), s2_ref) < 1e-5
+    assert check_status(gdn) == 0
