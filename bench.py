@@ -23,6 +23,7 @@ The printed JSON line carries:
              one launch per step) and its HBM roofline fraction
   spec_verify   speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, qk-norm, fused gating)
   decode_sharded  a decode batch of B=1024 split by sequence over the N ranks (strong scaling)
+  layer_adjacent  the causal conv1d + SiLU in front of the layer and the gated RMS norm behind it (HBM-bound)
   packed     packed (varlen) prefill of 16 sequences with log-normal lengths, 32768 tokens per GPU
   long_context  the B=2, T=131072 layer with the value heads sharded over the N ranks (strong scaling)
   parity     N > 1 only: one shared-seed problem, every rank computes its head shard on its GPU, the
@@ -514,6 +515,27 @@ def main():
     ms_dsh, ms_dsh_all = timed(step_decode_sharded, dsteps)
     del n_states, nd
 
+    # ---------------- the layer-adjacent steps at the benchmark shape: causal conv1d + SiLU over the q/k/v
+    # projections (B=4, T=4096, 2*kh*d + vh*d = 8192 channels, width 4) and the gated RMS norm of the output
+    gen_la = torch.Generator(device=dev).manual_seed(900 + rank)
+    la_C = 2 * kh * d + vh * d
+    la_x = torch.randn(B, T, la_C, device=dev, generator=gen_la).bfloat16()
+    la_w = (torch.randn(la_C, 4, device=dev, generator=gen_la) * 0.5).bfloat16()
+    la_b = torch.randn(la_C, device=dev, generator=gen_la).bfloat16()
+    for _ in range(3):
+        gdn.causal_conv1d(la_x, la_w, la_b)
+    ms_conv, ms_conv_all = timed(lambda i: gdn.causal_conv1d(la_x, la_w, la_b), 10)
+    conv_bytes = 2 * la_x.numel() * 2
+    del la_x
+    la_o = torch.randn(B, T, vh, d, device=dev, generator=gen_la).bfloat16()
+    la_z = torch.randn(B, T, vh, d, device=dev, generator=gen_la).bfloat16()
+    la_g = torch.ones(d, device=dev).bfloat16()
+    for _ in range(3):
+        gdn.gated_rmsnorm(la_o, la_z, la_g)
+    ms_norm, ms_norm_all = timed(lambda i: gdn.gated_rmsnorm(la_o, la_z, la_g), 10)
+    norm_bytes = 3 * la_o.numel() * 2
+    del la_o, la_z
+
     # ---------------- packed prefill: 16 sequences of log-normal lengths, 32768 tokens per rank
     pk = None
     if not args.no_packed:
@@ -679,6 +701,13 @@ def main():
                                      "qk-norm, fused gating" % (world, nB),
                            "ms_per_step": ms_dsh, "spread": spread(ms_dsh_all),
                            "roofline": hbm_roof(dsh_bytes, ms_dsh, "gdn_recurrent_kernel (rank 0's share)")},
+        "layer_adjacent": {
+            "causal_conv1d_silu": {"config": "B=4 T=4096 channels=8192 (q, k, v projections) width=4, bias, SiLU, per GPU",
+                                   "value": world * tokens / (ms_conv * 1e-3), "unit": "tokens/s", "ms_per_step": ms_conv,
+                                   "spread": spread(ms_conv_all), "roofline": hbm_roof(conv_bytes, ms_conv, "gdn_causal_conv1d_kernel<4>")},
+            "gated_rmsnorm": {"config": "B=4 T=4096 vh=32 d=128: 524288 rows of 128, per GPU",
+                              "value": world * tokens / (ms_norm * 1e-3), "unit": "tokens/s", "ms_per_step": ms_norm,
+                              "spread": spread(ms_norm_all), "roofline": hbm_roof(norm_bytes, ms_norm, "gdn_gated_rmsnorm_kernel")}},
         "packed": pk,
         "long_context": lc,
         "parity": parity,

@@ -8,6 +8,7 @@ All compute happens in libgdn_b200.so (hand-written sm_100a CUDA behind a C ABI,
 in include/gdn_b200.h).  Importing this package does not need a GPU; calling an operation
 without the built library or on a non-sm_100 device raises RuntimeError.
 """
+from . import api  # noqa: F401
 from .api import (  # noqa: F401
     Decode,
     InferenceMode,
@@ -16,9 +17,11 @@ from .api import (  # noqa: F401
     bf16_chunked_seq_state_update,
     bf16_gdn_chunked_compute_O,
     bf16_gdn_compute_u_w,
+    causal_conv1d,
     chunk_local_cumsum_bf16,
     chunked_forward,
     fused_gdn_gating,
+    gated_rmsnorm,
     init,
     recurrent_forward,
     transpose_to_mn_major,

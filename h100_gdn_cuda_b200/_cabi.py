@@ -69,6 +69,14 @@ class ChunkedArgs(C.Structure):
                 ("stage_events", C.POINTER(C.c_void_p)), ("is_qk_norm", C.c_int32)]
 
 
+class ConvArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p),
+                ("state_in", C.c_void_p), ("state_out", C.c_void_p), ("x_stride_batch", C.c_int64),
+                ("x_stride_token", C.c_int64), ("y_stride_batch", C.c_int64), ("y_stride_token", C.c_int64),
+                ("batch", C.c_int32), ("seq_len", C.c_int32), ("total_tokens", C.c_int64), ("cu_seqlens", C.c_void_p),
+                ("channels", C.c_int32), ("width", C.c_int32), ("silu", C.c_int32)]
+
+
 # name -> (restype, argtypes); every symbol include/gdn_b200.h declares
 SYMBOLS = {
     "gdn_init": (C.c_int, [C.c_char_p, C.c_char_p]),
@@ -89,6 +97,9 @@ SYMBOLS = {
     "gdn_chunked_forward_workspace_bytes": (C.c_size_t, [C.POINTER(Shape)]),
     "gdn_chunked_forward": (C.c_int, [C.POINTER(ChunkedArgs), C.c_void_p]),
     "gdn_chunked_forward_static_scratch": (C.c_int, [C.POINTER(ChunkedArgs), C.c_void_p]),
+    "gdn_causal_conv1d": (C.c_int, [C.POINTER(ConvArgs), C.c_void_p]),
+    "gdn_gated_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64,
+                                    C.c_int64, C.c_int64, C.c_float, C.c_void_p]),
 }
 
 _lib = None

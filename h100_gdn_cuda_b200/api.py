@@ -461,3 +461,61 @@ def bf16_gdn_chunked_compute_O(q, state, k, u, o, gate=None, scale: Optional[flo
     args = cabi.ComputeOArgs(shape, _token_tensor(q, varlen), _token_tensor(k, varlen), _token_tensor(u, varlen),
                              _token_tensor(o, varlen), _token_scalar(gate, varlen), state.data_ptr(), float(scale))
     cabi.check(cabi.load().gdn_compute_o(C.byref(args), _stream()), "bf16_gdn_chunked_compute_O")
+
+
+# --------------------------------------------------------------------------
+# layer-adjacent steps (not in the reference: its callers run them)
+# --------------------------------------------------------------------------
+def causal_conv1d(x, weight, bias=None, initial_state=None, cu_seqlens=None, activation: bool = True,
+                  final_state=None, return_final_state: bool = False):
+    """Depthwise causal convolution along the token axis (+ SiLU), as applied to the q/k/v projections in
+    front of Gated DeltaNet.  x: (B, T, C) or packed (N, C) bf16 with contiguous channels; weight: (C, W)
+    bf16, W = 2 .. 4; bias: (C) or None; initial_state: (sequences, W-1, C) holding the W-1 inputs before
+    each sequence (None: zeros).  Returns y, or (y, final_state) with the last W-1 inputs of every sequence
+    when `return_final_state` (or when a `final_state` buffer is given; it may be `initial_state` itself for
+    decode-sized calls)."""
+    _cuda_bf16(x, "x")
+    _cuda_bf16(weight, "weight")
+    _require(x.stride(-1) == 1, "channels must be contiguous")
+    varlen = cu_seqlens is not None
+    C_, W = weight.shape
+    _require(x.shape[-1] == C_, "weight must be (channels, width)")
+    if varlen:
+        _require(x.dim() == 2, "packed input is (tokens, channels)")
+        batch, seq_len, total, xsb, xst = cu_seqlens.numel() - 1, 0, x.shape[0], 0, x.stride(0)
+    else:
+        _require(x.dim() == 3, "padded input is (batch, tokens, channels)")
+        batch, seq_len, total, xsb, xst = x.shape[0], x.shape[1], x.shape[0] * x.shape[1], x.stride(0), x.stride(1)
+    y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    w = weight.contiguous()
+    b = None if bias is None else bias.contiguous()
+    s_in = None if initial_state is None else initial_state.contiguous()
+    if s_in is not None:
+        _require(tuple(s_in.shape) == (batch, W - 1, C_) and s_in.dtype == torch.bfloat16, "initial_state must be (sequences, W-1, C) bf16")
+    s_out = final_state
+    if s_out is None and return_final_state:
+        s_out = torch.empty(batch, W - 1, C_, dtype=x.dtype, device=x.device)
+    if s_out is not None:
+        _require(s_out.is_contiguous() and tuple(s_out.shape) == (batch, W - 1, C_), "final_state must be contiguous (sequences, W-1, C)")
+    args = cabi.ConvArgs(x.data_ptr(), y.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(),
+                         None if s_in is None else s_in.data_ptr(), None if s_out is None else s_out.data_ptr(),
+                         xsb, xst, 0 if varlen else y.stride(0), y.stride(0) if varlen else y.stride(1),
+                         batch, seq_len, total, _i32(cu_seqlens, "cu_seqlens"), C_, W, int(bool(activation)))
+    cabi.check(cabi.load().gdn_causal_conv1d(C.byref(args), _stream()), "causal_conv1d")
+    return (y, s_out) if s_out is not None else y
+
+
+def gated_rmsnorm(x, z, weight, eps: float = 1e-6):
+    """y = x * rsqrt(mean(x^2) + eps) * weight * silu(z) over the last axis: the output norm that follows Gated
+    DeltaNet (x: the layer's output, z: the gate projection, both (..., D) bf16; weight (D))."""
+    _cuda_bf16(x, "x")
+    _cuda_bf16(z, "z")
+    _cuda_bf16(weight, "weight")
+    _require(x.shape == z.shape and x.shape[-1] == weight.numel(), "x and z must have the same shape, weight one entry per column")
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D) if x.is_contiguous() else x.contiguous().view(-1, D)
+    z2 = z.reshape(-1, D) if z.is_contiguous() else z.contiguous().view(-1, D)
+    y = torch.empty(x2.shape, dtype=x.dtype, device=x.device)
+    cabi.check(cabi.load().gdn_gated_rmsnorm(x2.data_ptr(), z2.data_ptr(), y.data_ptr(), weight.contiguous().data_ptr(), x2.shape[0], D,
+                                             x2.stride(0), z2.stride(0), y.stride(0), float(eps), _stream()), "gated_rmsnorm")
+    return y.view(x.shape)

@@ -5,6 +5,7 @@
 #include "host_common.hpp"
 #include "jit/jit.hpp"
 #include "kernels/helpers.cuh"
+#include "kernels/layer_adjacent.cuh"
 #include "kernels/recurrent.cuh"
 
 #include <atomic>
@@ -248,6 +249,87 @@ int gdn_transpose_mn_major(const void* input, void* output, int32_t elem_size, i
         gdn_transpose_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)input, (uint32_t*)output, mn, k, mn_aligned);
     else
         gdn_transpose_kernel<uint16_t><<<grid, 256, 0, st>>>((const uint16_t*)input, (uint16_t*)output, mn, k, mn_aligned);
+    GDN_CUDA(cudaGetLastError());
+    return GDN_OK;
+}
+
+int gdn_causal_conv1d(const GdnConvArgs* a, gdn_stream_t stream) {
+    GDN_REQUIRE(a != nullptr, "gdn_causal_conv1d: args is NULL");
+    GDN_REQUIRE(a->x && a->y && a->weight, "gdn_causal_conv1d: x, y and weight are required");
+    GDN_REQUIRE(a->width >= 2 && a->width <= kConvMaxWidth, "gdn_causal_conv1d: width must be 2 .. 4 (got %d)", a->width);
+    GDN_REQUIRE(a->channels > 0 && a->channels % 8 == 0, "gdn_causal_conv1d: channels must be a positive multiple of 8");
+    GDN_REQUIRE(a->batch > 0, "gdn_causal_conv1d: batch must be positive");
+    GDN_REQUIRE(aligned16(a->x) && aligned16(a->y) && a->x_stride_token % 8 == 0 && a->y_stride_token % 8 == 0 &&
+                    a->x_stride_batch % 8 == 0 && a->y_stride_batch % 8 == 0,
+                "gdn_causal_conv1d: x and y must be 16-byte aligned with strides that are multiples of 8 elements");
+    GDN_REQUIRE(a->x_stride_token >= a->channels && a->y_stride_token >= a->channels, "gdn_causal_conv1d: token stride below channels");
+    GDN_REQUIRE((!a->state_in || aligned16(a->state_in)) && (!a->state_out || aligned16(a->state_out)),
+                "gdn_causal_conv1d: states must be 16-byte aligned");
+    const bool packed = a->cu_seqlens != nullptr;
+    const long long tokens = packed ? a->total_tokens : a->seq_len;
+    GDN_REQUIRE(tokens >= 0, "gdn_causal_conv1d: negative token count");
+    if (a->state_out && a->state_out == a->state_in)
+        GDN_REQUIRE(packed ? a->total_tokens <= a->batch : a->seq_len <= kConvTokBlock,
+                    "gdn_causal_conv1d: state_out may alias state_in only when no sequence spans more than one %d-token block",
+                    kConvTokBlock);
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    if (tokens == 0 && !packed) return GDN_OK;
+    ConvParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(a->x);
+    p.y = static_cast<__nv_bfloat16*>(a->y);
+    p.w = static_cast<const __nv_bfloat16*>(a->weight);
+    p.bias = static_cast<const __nv_bfloat16*>(a->bias);
+    p.state_in = static_cast<const __nv_bfloat16*>(a->state_in);
+    p.state_out = static_cast<__nv_bfloat16*>(a->state_out);
+    p.x_sb = a->x_stride_batch; p.x_st = a->x_stride_token; p.y_sb = a->y_stride_batch; p.y_st = a->y_stride_token;
+    p.cu_seqlens = a->cu_seqlens;
+    p.batch = a->batch; p.seq_len = a->seq_len; p.channels = a->channels; p.width = a->width; p.silu = a->silu;
+    p.total_tokens = a->total_tokens;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long tblocks = (tokens + kConvTokBlock - 1) / kConvTokBlock;
+    GDN_REQUIRE(tblocks <= 65535 && a->batch <= 65535, "gdn_causal_conv1d: too many token blocks or sequences for one launch");
+    if (tblocks > 0) {
+        dim3 grid(static_cast<unsigned>((a->channels / 8 + 127) / 128), static_cast<unsigned>(tblocks), packed ? 1u : static_cast<unsigned>(a->batch));
+        switch (a->width) {
+            case 2: gdn_causal_conv1d_kernel<2><<<grid, 128, 0, st>>>(p); break;
+            case 3: gdn_causal_conv1d_kernel<3><<<grid, 128, 0, st>>>(p); break;
+            default: gdn_causal_conv1d_kernel<4><<<grid, 128, 0, st>>>(p); break;
+        }
+        GDN_CUDA(cudaGetLastError());
+    }
+    if (packed && p.state_out && p.state_in && p.state_out != p.state_in) {
+        gdn_conv_state_passthrough_kernel<<<a->batch, 128, 0, st>>>(p);
+        GDN_CUDA(cudaGetLastError());
+    }
+    return GDN_OK;
+}
+
+int gdn_gated_rmsnorm(const void* x, const void* z, void* y, const void* weight, int64_t rows, int32_t dim,
+                      int64_t x_row_stride, int64_t z_row_stride, int64_t y_row_stride, float eps, gdn_stream_t stream) {
+    GDN_REQUIRE(x && z && y && weight, "gdn_gated_rmsnorm: NULL pointer");
+    GDN_REQUIRE(rows >= 0 && dim > 0 && dim % 8 == 0 && dim <= 1024, "gdn_gated_rmsnorm: dim must be a multiple of 8 up to 1024");
+    GDN_REQUIRE(aligned16(x) && aligned16(z) && aligned16(y) && aligned16(weight) && x_row_stride % 8 == 0 && z_row_stride % 8 == 0 &&
+                    y_row_stride % 8 == 0 && x_row_stride >= dim && z_row_stride >= dim && y_row_stride >= dim,
+                "gdn_gated_rmsnorm: pointers must be 16-byte aligned, row strides multiples of 8 and at least dim");
+    DeviceInfo* d = nullptr;
+    if (int rc = get_device_info(&d)) return rc;
+    if (rows == 0) return GDN_OK;
+    NormParams p{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(y),
+                 static_cast<const __nv_bfloat16*>(weight), rows, x_row_stride, z_row_stride, y_row_stride, dim, eps};
+    // lanes per row: the smallest power of two (4 .. 32) whose 16-byte pieces cover the row in one pass
+    int lpr = 4;
+    while (lpr < 32 && lpr * 8 < dim) lpr *= 2;
+    const long long rows_per_block = 8ll * (32 / lpr) * (lpr == 32 ? 1 : 2);  // 8 warps, rows in flight per lane group as in the kernel
+    const long long blocks = (rows + rows_per_block - 1) / rows_per_block;
+    GDN_REQUIRE(blocks < (1ll << 31), "gdn_gated_rmsnorm: too many rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (lpr) {
+        case 4: gdn_gated_rmsnorm_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
+        case 8: gdn_gated_rmsnorm_kernel<8><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
+        case 16: gdn_gated_rmsnorm_kernel<16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
+        default: gdn_gated_rmsnorm_kernel<32><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
+    }
     GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }

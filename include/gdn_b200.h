@@ -304,6 +304,47 @@ int gdn_chunked_forward(const GdnChunkedArgs* args, gdn_stream_t stream);
 #define GDN_STATIC_SCRATCH_BYTES ((49u << 20) + 8192u + 512u)
 int gdn_chunked_forward_static_scratch(const GdnChunkedArgs* args, gdn_stream_t stream);
 
+/* ---------------------------------------------------------------- layer-adjacent steps
+ * No counterpart in the reference, which leaves them to its callers: the two memory-bound steps on either
+ * side of Gated DeltaNet in Qwen3-Next-style blocks.
+ *
+ * gdn_causal_conv1d: depthwise causal convolution along the token axis, optionally followed by SiLU, as
+ * applied to the q/k/v projections before the layer:
+ *     y[t, c] = act( bias[c] + sum_{i < width} weight[c, i] * x[t - (width-1) + i, c] )
+ * x, y are bf16 with the channels contiguous (addressed batch*stride_batch + token*stride_token + c; packed
+ * mode: global token index, no batch stride); weight is (channels, width) bf16, bias (channels) bf16 or
+ * NULL; width 2 .. 4; channels a multiple of 8.  Inputs before a sequence's first token come from
+ * state_in (sequences, width-1, channels; row width-2 is the input right before the sequence) or are zero
+ * when it is NULL; state_out (same shape, or NULL) receives the sequence's last width-1 inputs, so that a
+ * later call continues it (decode).  state_out may be the same buffer as state_in only when no sequence
+ * spans more than one 32-token block: padded mode with seq_len <= 32, packed mode with one token per
+ * sequence at most (total_tokens <= batch). */
+typedef struct {
+    const void* x;
+    void* y;
+    const void* weight;
+    const void* bias;
+    const void* state_in;
+    void* state_out;
+    int64_t x_stride_batch, x_stride_token, y_stride_batch, y_stride_token;
+    int32_t batch;
+    int32_t seq_len;
+    int64_t total_tokens;
+    const int32_t* cu_seqlens;
+    int32_t channels;
+    int32_t width;
+    int32_t silu; /* != 0: SiLU after the convolution */
+} GdnConvArgs;
+int gdn_causal_conv1d(const GdnConvArgs* args, gdn_stream_t stream);
+
+/* gdn_gated_rmsnorm: the output norm of the block, one row per (token, v-head):
+ *     y = x * rsqrt(mean(x^2) + eps) * weight * silu(z)
+ * x, z, y bf16 (rows, dim) with row strides in elements (multiples of 8) and contiguous rows; weight (dim)
+ * bf16; dim a multiple of 8 up to 1024. */
+int gdn_gated_rmsnorm(const void* x, const void* z, void* y, const void* weight, int64_t rows, int32_t dim,
+                      int64_t x_row_stride, int64_t z_row_stride, int64_t y_row_stride, float eps,
+                      gdn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,9 +51,9 @@ def test_struct_sizes_match_c(lib):
         #include <stdio.h>
         #include "gdn_b200.h"
         int main(void) {
-            printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(GdnTokenTensor), sizeof(GdnTokenScalar),
+            printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(GdnTokenTensor), sizeof(GdnTokenScalar),
                    sizeof(GdnState), sizeof(GdnShape), sizeof(GdnRecurrentArgs), sizeof(GdnComputeUWArgs),
-                   sizeof(GdnSeqStateArgs), sizeof(GdnComputeOArgs), sizeof(GdnChunkedArgs));
+                   sizeof(GdnSeqStateArgs), sizeof(GdnComputeOArgs), sizeof(GdnChunkedArgs), sizeof(GdnConvArgs));
             return 0;
         }''')
     with tempfile.TemporaryDirectory() as d:
@@ -64,7 +64,7 @@ def test_struct_sizes_match_c(lib):
         sizes = [int(x) for x in subprocess.check_output([exe]).split()]
     py = [ctypes.sizeof(t) for t in (_cabi.TokenTensor, _cabi.TokenScalar, _cabi.State, _cabi.Shape,
                                      _cabi.RecurrentArgs, _cabi.ComputeUWArgs, _cabi.SeqStateArgs,
-                                     _cabi.ComputeOArgs, _cabi.ChunkedArgs)]
+                                     _cabi.ComputeOArgs, _cabi.ChunkedArgs, _cabi.ConvArgs)]
     assert sizes == py
 
 

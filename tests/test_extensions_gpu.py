@@ -237,3 +237,59 @@ def test_fp32_state(gdn, B, T, kh, vh, d):
         _, s2_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), beta.bfloat16().float(), g, s_ref, is_qk_norm=True)
         assert O.rel_fro(s2.cpu(), s2_ref) < 1e-5
     assert check_status(gdn) == 0
+
+
+@pytest.mark.parametrize("B,T,C_,W,bias,state", [(2, 70, 64, 4, True, True), (1, 5, 24, 3, False, False), (3, 1, 128, 4, True, True),
+                                                (2, 33, 8, 2, True, True)])
+def test_causal_conv1d_padded(gdn, B, T, C_, W, bias, state):
+    """Causal depthwise convolution + SiLU against the fp32 definition; bf16 in and out (gate: relative
+    Frobenius <= 1e-2, as for the other bf16 outputs); the final state is a copy of inputs and must be exact."""
+    gen = torch.Generator().manual_seed(B * 100 + T)
+    x = torch.randn(B, T, C_, generator=gen).bfloat16()
+    w = (torch.randn(C_, W, generator=gen) * 0.5).bfloat16()
+    b = torch.randn(C_, generator=gen).bfloat16() if bias else None
+    s0 = torch.randn(B, W - 1, C_, generator=gen).bfloat16() if state else None
+    y, fin = gdn.api.causal_conv1d(x.cuda(), w.cuda(), None if b is None else b.cuda(), None if s0 is None else s0.cuda(),
+                                   return_final_state=True)
+    y_ref, fin_ref = O.causal_conv1d_ref(x, w, b, s0)
+    close(y, y_ref, "y")
+    assert torch.equal(fin.float().cpu(), fin_ref)
+    if T <= 32 and state:   # decode-sized call: the state may be updated in place
+        s_io = s0.clone().cuda()
+        y2, fin2 = gdn.api.causal_conv1d(x.cuda(), w.cuda(), None if b is None else b.cuda(), s_io, final_state=s_io)
+        assert torch.equal(y2, y) and torch.equal(s_io.float().cpu(), fin_ref)
+    # continuation: the two halves with the state handed over equal the whole
+    if T >= 8:
+        h = T // 2
+        ya, sa = gdn.api.causal_conv1d(x[:, :h].cuda(), w.cuda(), None if b is None else b.cuda(), None if s0 is None else s0.cuda(),
+                                       return_final_state=True)
+        yb, sb = gdn.api.causal_conv1d(x[:, h:].cuda(), w.cuda(), None if b is None else b.cuda(), sa, return_final_state=True)
+        assert torch.equal(torch.cat([ya, yb], dim=1), y) and torch.equal(sb, fin)
+
+
+def test_causal_conv1d_packed(gdn):
+    lens = [1, 40, 0, 3, 64, 2]
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32)
+    C_, W = 40, 4
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(sum(lens), C_, generator=gen).bfloat16()
+    w = (torch.randn(C_, W, generator=gen) * 0.5).bfloat16()
+    b = torch.randn(C_, generator=gen).bfloat16()
+    s0 = torch.randn(len(lens), W - 1, C_, generator=gen).bfloat16()
+    y, fin = gdn.api.causal_conv1d(x.cuda(), w.cuda(), b.cuda(), s0.cuda(), cu_seqlens=cu.cuda(), return_final_state=True)
+    y_ref, fin_ref = O.causal_conv1d_ref(x, w, b, s0, cu_seqlens=cu.tolist())
+    close(y, y_ref, "y")
+    assert torch.equal(fin.float().cpu(), fin_ref)   # the empty sequence keeps its state
+    with pytest.raises(RuntimeError):                # a sequence spanning several blocks cannot be updated in place
+        s_io = s0.clone().cuda()
+        gdn.api.causal_conv1d(x.cuda(), w.cuda(), b.cuda(), s_io, cu_seqlens=cu.cuda(), final_state=s_io)
+
+
+@pytest.mark.parametrize("shape", [(2, 50, 4, 128), (3, 7, 64), (5, 1024), (4, 3, 2, 200)])
+def test_gated_rmsnorm(gdn, shape):
+    gen = torch.Generator().manual_seed(len(shape))
+    x = torch.randn(*shape, generator=gen).bfloat16()
+    z = torch.randn(*shape, generator=gen).bfloat16()
+    w = (1 + 0.1 * torch.randn(shape[-1], generator=gen)).bfloat16()
+    y = gdn.api.gated_rmsnorm(x.cuda(), z.cuda(), w.cuda(), 1e-6)
+    close(y, O.gated_rmsnorm_ref(x, z, w, 1e-6), "y")
