@@ -264,6 +264,17 @@ def run_only(args, gdn, synthetic, dev, peaks):
              "state": (torch.randn(B, lvh, d, d, device=dev, generator=gen) * 0.02).bfloat16()}
         ws = torch.empty(gdn.api.chunked_forward_workspace_bytes(B, T, lvh), dtype=torch.uint8, device=dev)
         run = lambda i: gdn.chunked_forward(t["q"], t["k"], t["v"], t["beta"], t["g"], None, t["state"], _workspace=ws)
+        if args.varlen:
+            # the same sequences as one packed batch (cu_seqlens): segments are then found on the device
+            cu = [i * T for i in range(B + 1)]
+            m = [torch.tensor(x, dtype=torch.int32, device=dev) for x in
+                 (cu, synthetic.prepare_chunk_indices(cu), synthetic.prepare_cu_chunks(cu))]
+            f = {k: t[k].view(B * T, *t[k].shape[2:]) for k in ("q", "k", "v", "beta", "g")}
+            nc = B * (T // 64)
+            ws = torch.empty(gdn.api.chunked_forward_workspace_bytes(B, 0, lvh, total_tokens=B * T, total_chunks=nc, packed=True),
+                             dtype=torch.uint8, device=dev)
+            run = lambda i: gdn.chunked_forward(f["q"], f["k"], f["v"], f["beta"], f["g"], None, t["state"], m[0], m[1], m[2], nc,
+                                                _workspace=ws)
         work, unit = B * T, "tokens/s"
     elif args.only == "packed":
         # 16 sequences of log-normal lengths in one packed batch of 32768 tokens
@@ -309,6 +320,7 @@ def main():
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
     ap.add_argument("--heads", type=int, default=None, help="with --only long: v-heads of this GPU's share (default 4)")
+    ap.add_argument("--varlen", action="store_true", help="with --only long: pass the sequences as one packed batch")
     args = ap.parse_args()
     if args.only is None:
         args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -587,7 +599,23 @@ def main():
         lc = {"metric": "prefill_tokens_per_s", "value": lB * lT / (ms_lc * 1e-3), "unit": "tokens/s", "scaling": "strong",
               "config": "B=2 T=131072 kh=16 vh=32 d=128, value heads sharded over %d GPU(s): %d v-heads per GPU" % (world, lvh),
               "ms_per_step": ms_lc, "spread": spread(ms_lc_all)}
-        del lq, lk, lv, lbeta, lg, ls0, lws
+        # the same two sequences as one packed (varlen) batch: what a serving engine passes
+        cu_host = [0, lT, 2 * lT]
+        lnc = 2 * (lT // 64)
+        lcu, lci, lcc = (torch.tensor(x, dtype=torch.int32, device=dev) for x in
+                         (cu_host, synthetic.prepare_chunk_indices(cu_host), synthetic.prepare_cu_chunks(cu_host)))
+        lpws = torch.empty(gdn_api.chunked_forward_workspace_bytes(lB, 0, lvh, total_tokens=lB * lT, total_chunks=lnc, packed=True,
+                                                                   num_k_heads=lkh), dtype=torch.uint8, device=dev)
+        pq, pk_, pv, pb, pg = (t.view(lB * lT, *t.shape[2:]) for t in (lq, lk, lv, lbeta, lg))
+
+        def step_long_packed(i=0):
+            return gdn.chunked_forward(pq, pk_, pv, pb, pg, None, ls0, lcu, lci, lcc, lnc, _workspace=lpws)
+        for _ in range(2):
+            step_long_packed()
+        ms_lcp, ms_lcp_all = timed(step_long_packed, 5, repeats=3)
+        lc["packed_ms_per_step"] = ms_lcp
+        lc["packed_spread"] = spread(ms_lcp_all)
+        del lq, lk, lv, lbeta, lg, ls0, lws, lpws, pq, pk_, pv, pb, pg
     # the sampler ran across every timed region above
     clocks = sampler.stop() if rank == 0 else None
 

@@ -311,21 +311,27 @@ static int chunked_forward_wide(const GdnChunkedArgs* a, gdn_stream_t stream) {
 static size_t ws_blocks_bytes(size_t chunks, int vh) { return (chunks * static_cast<size_t>(vh) * kZPBlockBytes + 255) / 256 * 256; }
 static size_t ws_norms_bytes(size_t chunks, int kh) { return (chunks * static_cast<size_t>(kh) * 128 * sizeof(float) + 255) / 256 * 256; }
 
+// The segment plan of a problem (heuristics.hpp); num_segments == 1: not segmented.
+static SegmentPlan segment_plan_of(const GdnShape& s) {
+    if (s.cu_seqlens) return prefill_segments_packed(s.batch, s.num_v_heads, s.total_chunks > 0 ? s.total_chunks : 0);
+    SegmentPlan plan = prefill_segments(static_cast<long long>(s.batch) * s.num_v_heads, (s.seq_len + kChunk - 1) / kChunk, false);
+    plan.slots = s.batch * plan.num_segments;
+    return plan;
+}
+
 size_t gdn_chunked_forward_workspace_bytes(const GdnShape* s) {
     if (!s) return 0;
     if (wide_heads(*s)) return 0;
     const size_t chunks = s->cu_seqlens ? static_cast<size_t>(s->total_chunks > 0 ? s->total_chunks : 0)
                                         : static_cast<size_t>(s->batch) * static_cast<size_t>((s->seq_len + kChunk - 1) / kChunk);
     // one block of Z (64 x 128 bf16) and PT (64 x 64 bf16) per (chunk, v-head); for a
-    // segmented run (few long padded sequences) three fp32 states per chain and segment on top
+    // segmented run (few long sequences) three fp32 states per v-head and segment slot on top
     size_t bytes = ws_blocks_bytes(chunks, s->num_v_heads) + ws_norms_bytes(chunks, s->num_k_heads) + 256;
-    if (!s->cu_seqlens) {
-        const long long chains = static_cast<long long>(s->batch) * s->num_v_heads;
-        const SegmentPlan plan = prefill_segments(chains, (s->seq_len + kChunk - 1) / kChunk, false);
-        if (plan.num_segments > 1) bytes += static_cast<size_t>(chains) * plan.num_segments * 3 * kD * kD * sizeof(float) + 256;
-    } else if (s->batch > 1 && s->batch <= kMaxOrderedSeqs) {
+    const SegmentPlan plan = segment_plan_of(*s);
+    if (plan.num_segments > 1)
+        bytes += static_cast<size_t>(plan.slots) * s->num_v_heads * 3 * kD * kD * sizeof(float) + 256;
+    else if (s->cu_seqlens && s->batch > 1 && s->batch <= kMaxOrderedSeqs)
         bytes += (static_cast<size_t>(s->batch) * sizeof(int) + 255) / 256 * 256;  // sequences by length
-    }
     return bytes;
 }
 
@@ -395,8 +401,8 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         constexpr int smem = FusedSmem::kBytes;
         if (int rc = set_smem(gdn_fused_seq_kernel, smem)) return rc;
         const long long chains = static_cast<long long>(s.batch) * s.num_v_heads;
-        const SegmentPlan plan = prefill_segments(chains, (s.seq_len + kChunk - 1) / kChunk, packed);
-        if (packed && s.batch > 1 && s.batch <= kMaxOrderedSeqs && chains > d->sms) {
+        const SegmentPlan plan = segment_plan_of(s);
+        if (plan.num_segments <= 1 && packed && s.batch > 1 && s.batch <= kMaxOrderedSeqs && chains > d->sms) {
             // more chains than SMs and unequal lengths: dispatch the longest sequences first
             int* order = reinterpret_cast<int*>(ws_extra);
             gdn_seq_order_kernel<<<(s.batch + 127) / 128, 128, 0, st>>>(s.cu_seqlens, s.batch, order);
@@ -410,13 +416,15 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
         } else {
             // composite transitions of all segments, their start states, then all segments at once
             float* seg_mn = reinterpret_cast<float*>(ws_extra);
-            float* seg_start = seg_mn + static_cast<size_t>(chains) * plan.num_segments * 2 * kD * kD;
+            const size_t seg_units = static_cast<size_t>(plan.slots) * s.num_v_heads;
+            float* seg_start = seg_mn + seg_units * 2 * kD * kD;
             p.seg_chunks = plan.seg_chunks;
             p.num_segments = plan.num_segments;
+            p.num_seqs = s.batch;
             p.seg_mn = seg_mn;
             p.seg_start = seg_start;
             p.mode = 1;
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, 2 * plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(plan.slots, s.num_v_heads, 2), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
             SegCombineParams cp{};
             cp.seg_mn = seg_mn;
@@ -426,12 +434,14 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.si_sh = p.si_sh;
             cp.vh = s.num_v_heads;
             cp.num_segments = plan.num_segments;
+            cp.map = p.map;
+            cp.seg_chunks = plan.seg_chunks;
             cp.status = d->status;
             if (int rc = set_smem(gdn_seg_combine_kernel, SegCombineSmem::kBytes)) return rc;
             gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R), 128, SegCombineSmem::kBytes, st>>>(cp);
             GDN_CUDA(cudaGetLastError());
             p.mode = 2;
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads, plan.num_segments), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
+            gdn_fused_seq_kernel<<<dim3(plan.slots, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
             GDN_CUDA(cudaGetLastError());
         }
     }

@@ -36,28 +36,34 @@ struct PrefillConfig {
 
 inline PrefillConfig prefill_config() { return PrefillConfig{4, 512}; }
 
-// Segmented state propagation for few long padded sequences.  The state kernel is a serial chain
+// Segmented state propagation for few long sequences.  The state kernel is a serial chain
 // per (sequence, v-head); with fewer chains than SMs most of the GPU idles.  The chain obeys
-// S' = S M_c + N_c per chunk, so the sequence is cut into P (at most 32) segments: one launch finds every
+// S' = S M_c + N_c per chunk, so a sequence is cut into segments: one launch finds every
 // segment's composite (M, N) (two CTAs per chain and segment), a small kernel chains them into the
 // segments' start states, and a second launch of the state kernel produces the output of all
-// segments at once.  Three passes instead of one, P segments wide.
+// segments at once.  Three passes instead of one, many segments wide.
 // The plan must not depend on the device (the scratch size is computed without one), so it is
 // made for the 148 SMs of a B200.
 struct SegmentPlan {
-    int num_segments;  // 1: not segmented
+    int num_segments;  // padded mode: segments per sequence; 1: not segmented
     int seg_chunks;    // chunks per segment
+    int slots;         // (sequence, segment) pairs the launches cover: batch x num_segments in padded mode,
+                       // an upper bound in packed mode (the lengths are only known on the device)
 };
+namespace plan_detail {
+constexpr long long kSms = 148;
+// Cost model fitted to measurements (B=1..2, T=4096..131072, 4..32 v-heads), in units of "one
+// chunk of the state kernel": a CTA costs its chunks plus about 3 for start-up and pipeline
+// fill; a launch costs that times its CTA waves.  Plans whose second launch needs more than
+// one wave, or whose first needs more than two, measured worse than the model and are not made.
+constexpr int kFixed = 3, kMinSegment = 32;
+inline long long waves(long long ctas) { return (ctas + kSms - 1) / kSms; }
+}  // namespace plan_detail
+
 inline SegmentPlan prefill_segments(long long chains, int chunks_per_seq, bool packed) {
-    SegmentPlan plan{1, chunks_per_seq};
+    using namespace plan_detail;
+    SegmentPlan plan{1, chunks_per_seq, 0};
     if (packed || chains <= 0) return plan;
-    constexpr long long kSms = 148;
-    // Cost model fitted to measurements (B=1..2, T=4096..131072, 4..32 v-heads), in units of "one
-    // chunk of the state kernel": a CTA costs its chunks plus about 3 for start-up and pipeline
-    // fill; a launch costs that times its CTA waves.  Plans whose second launch needs more than
-    // one wave, or whose first needs more than two, measured worse than the model and are not made.
-    auto waves = [&](long long ctas) { return (ctas + kSms - 1) / kSms; };
-    constexpr int kFixed = 3, kMinSegment = 32;
     double best = 0.8 * static_cast<double>(waves(chains) * (chunks_per_seq + kFixed));
     for (int P = 2; P <= 32 && chunks_per_seq / P >= kMinSegment; ++P) {
         const long long w1 = waves(2 * chains * P), w3 = waves(chains * P);
@@ -68,6 +74,35 @@ inline SegmentPlan prefill_segments(long long chains, int chunks_per_seq, bool p
             best = cost;
             plan.num_segments = P;
             plan.seg_chunks = len;
+        }
+    }
+    return plan;
+}
+
+// Packed mode: the host sees the number of sequences and the total number of chunks, not the
+// lengths.  Segments have one length L for all sequences; sequence s gets max(1, ceil(chunks_s / L))
+// of them, at most total / L + num_seqs altogether: that many slots are launched and the surplus
+// CTAs leave at once.  The unsegmented run is costed as if all sequences were equally long (its
+// best case), so unequal lengths only make the segmented plan better than assumed.
+constexpr int kMaxSegmentedSeqs = 64;
+inline SegmentPlan prefill_segments_packed(int num_seqs, int num_v_heads, long long total_chunks) {
+    using namespace plan_detail;
+    SegmentPlan plan{1, static_cast<int>(std::min<long long>(total_chunks, 1 << 30)), 0};
+    if (num_seqs <= 0 || num_seqs > kMaxSegmentedSeqs || num_v_heads <= 0 || total_chunks <= 0 || total_chunks > (1 << 30)) return plan;
+    const long long chains = static_cast<long long>(num_seqs) * num_v_heads;
+    const long long even = (total_chunks + num_seqs - 1) / num_seqs;
+    double best = 0.8 * static_cast<double>(waves(chains) * (even + kFixed));
+    for (int P = 2; P <= 128 && total_chunks / P >= kMinSegment; ++P) {
+        const int len = static_cast<int>((total_chunks + P - 1) / P);
+        const long long slots = total_chunks / len + num_seqs;
+        const long long w1 = waves(2 * slots * num_v_heads), w3 = waves(slots * num_v_heads);
+        if (w3 > 1 || w1 > 2) break;
+        const double cost = static_cast<double>((w1 + w3) * (len + kFixed));
+        if (cost < best) {
+            best = cost;
+            plan.num_segments = P;
+            plan.seg_chunks = len;
+            plan.slots = static_cast<int>(slots);
         }
     }
     return plan;

@@ -67,6 +67,37 @@ __device__ __forceinline__ ChunkPos locate_chunk(const ChunkMap& m, int c) {
     return r;
 }
 
+// Segmented runs of the state kernel (few long sequences): which (sequence, segment) a launch slot is.
+// Padded mode: every sequence has `num_segments` segments, slot = seq * num_segments + segment.
+// Packed mode: segments of `seg_chunks` chunks, sequence s has max(1, ceil(chunks_s / seg_chunks)) of
+// them (an empty sequence keeps one, so that its final state is still written); slots follow the
+// sequences in order and the launch covers an upper bound of them (seq = -1 for the surplus).
+struct SegPos {
+    int seq, segment, nseg, first_slot;  // nseg, first_slot: segments of the sequence and the slot of its first one
+};
+__device__ __forceinline__ int packed_seq_segments(const int* cu_seqlens, int s, int seg_chunks) {
+    const int chunks = (cu_seqlens[s + 1] - cu_seqlens[s] + kChunk - 1) / kChunk;
+    const int n = (chunks + seg_chunks - 1) / seg_chunks;
+    return n > 0 ? n : 1;
+}
+__device__ __forceinline__ SegPos locate_segment(const ChunkMap& m, int slot, int seg_chunks, int num_segments, int num_seqs) {
+    if (!m.cu_seqlens) return SegPos{slot / num_segments, slot % num_segments, num_segments, slot - slot % num_segments};
+    int first = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+        const int n = packed_seq_segments(m.cu_seqlens, s, seg_chunks);
+        if (slot < first + n) return SegPos{s, slot - first, n, first};
+        first += n;
+    }
+    return SegPos{-1, 0, 0, 0};
+}
+// the segments of sequence `seq` (the `segment` field is not meaningful)
+__device__ __forceinline__ SegPos sequence_segments(const ChunkMap& m, int seq, int seg_chunks, int num_segments) {
+    if (!m.cu_seqlens) return SegPos{seq, 0, num_segments, seq * num_segments};
+    int first = 0;
+    for (int s = 0; s < seq; ++s) first += packed_seq_segments(m.cu_seqlens, s, seg_chunks);
+    return SegPos{seq, 0, packed_seq_segments(m.cu_seqlens, seq, seg_chunks), first};
+}
+
 // Offset of 16-byte chunk `chunk` of row `row` in a staging tile of D bf16 per row whose
 // chunks are XOR-swizzled by the row so that 16 rows written at once hit distinct banks.
 template <int D>

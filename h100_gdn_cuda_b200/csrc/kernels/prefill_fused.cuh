@@ -44,15 +44,16 @@ struct FusedParams {
     // q/k L2 normalisation: NULL, or per (global chunk, k-head) 64 inverse key norms then 64 inverse query
     // norms (written by gdn_zp_kernel); they enter through the two per-token factors of a chunk
     const float* norms;
-    // Segmented runs (padded mode, few long sequences; see gdn_chunked_forward).  The state obeys
+    // Segmented runs (few long sequences; see gdn_chunked_forward).  The state obeys
     // S' = S M_c + N_c per chunk, so a segment of chunks has a composite (M, N) as well.
-    //   mode 0: one CTA walks the whole sequence (blockIdx.z = 0).
-    //   mode 1: blockIdx.z = 2 * segment + kind; no output.  kind 0 starts from S = 0 and ends with
-    //           N of the segment; kind 1 starts from S = I with V taken as 0 and ends with M.
-    //           Both are written in fp32 to seg_mn[((chain * num_segments + segment) * 2 + kind)].
-    //   mode 2: blockIdx.z = segment; starts from seg_start[chain * num_segments + segment] (fp32),
-    //           writes the output of its chunks; the last segment writes the final state.
-    int mode, seg_chunks, num_segments;
+    //   mode 0: one CTA walks the whole sequence (grid = sequences x heads, or heads x ranks with seq_order).
+    //   mode 1: grid = (slots, heads, 2); blockIdx.x = slot of a (sequence, segment) pair (locate_segment),
+    //           blockIdx.z = kind; no output.  kind 0 starts from S = 0 and ends with N of the segment;
+    //           kind 1 starts from S = I with V taken as 0 and ends with M.
+    //           Both are written in fp32 to seg_mn[(slot * vh + head) * 2 + kind].
+    //   mode 2: grid = (slots, heads); starts from seg_start[slot * vh + head] (fp32), writes the
+    //           output of its chunks; the last segment of a sequence writes the final state.
+    int mode, seg_chunks, num_segments, num_seqs;
     float* seg_mn;
     const float* seg_start;
     // Packed mode with more CTAs than SMs: sequences sorted by length, longest first (written by
@@ -151,8 +152,16 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     volatile int* issued = abort_flag + 1;  // chunks whose loads the producer has issued (read by the L2 prefetcher)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seq = p.seq_order ? p.seq_order[blockIdx.y] : static_cast<int>(blockIdx.x);
-    const int head = p.seq_order ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.y);
+    SegPos sp{0, 0, 1, 0};
+    if (p.mode != 0) {
+        sp = locate_segment(p.map, static_cast<int>(blockIdx.x), p.seg_chunks, p.num_segments, p.num_seqs);
+        if (sp.seq < 0) return;  // packed mode launches an upper bound of slots
+    }
+    const int seq = p.mode != 0 ? sp.seq : (p.seq_order ? p.seq_order[blockIdx.y] : static_cast<int>(blockIdx.x));
+    const int head = p.mode == 0 && p.seq_order ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.y);
+    const int segment = sp.segment, seq_nseg = sp.nseg;
+    const int seg_kind = p.mode == 1 ? static_cast<int>(blockIdx.z) : 0;
+    const long long seg_idx = static_cast<long long>(blockIdx.x) * p.vh + head;  // modes 1, 2
     const int khead = head / (p.vh / p.kh);
 
     int batch, gchunk0;
@@ -171,8 +180,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
     }
     int nchunks = static_cast<int>((seq_tokens + kChunk - 1) / kChunk);
     // A segment is handled as a sequence of its own: shift the token and chunk origins.
-    const int segment = p.mode == 1 ? static_cast<int>(blockIdx.z >> 1) : (p.mode == 2 ? static_cast<int>(blockIdx.z) : 0);
-    const int seg_kind = p.mode == 1 ? static_cast<int>(blockIdx.z & 1) : 0;
     const bool emit_o = p.mode != 1;
     const bool zero_u = p.mode == 1 && seg_kind == 1;
     if (p.mode != 0) {
@@ -183,7 +190,6 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         gchunk0 += c0;
         nchunks = c1 - c0;
     }
-    const long long chain = static_cast<long long>(seq) * p.vh + head;
     auto chunk_n = [&](int c) {
         const long long rem = seq_tokens - static_cast<long long>(c) * kChunk;
         return rem < kChunk ? static_cast<int>(rem) : kChunk;
@@ -228,7 +234,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             uoff8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
         float S[64];
         if (p.mode == 2) {
-            const float4* src = reinterpret_cast<const float4*>(p.seg_start + (chain * p.num_segments + segment) * (D * D) +
+            const float4* src = reinterpret_cast<const float4*>(p.seg_start + seg_idx * (D * D) +
                                                                 static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll
             for (int q = 0; q < 16; ++q) {
@@ -359,11 +365,11 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         const bool healthy = *abort_flag == 0;
         if (!healthy) {
         } else if (p.mode == 1) {
-            float4* d4 = reinterpret_cast<float4*>(p.seg_mn + ((chain * p.num_segments + segment) * 2 + seg_kind) * (D * D) +
+            float4* d4 = reinterpret_cast<float4*>(p.seg_mn + (seg_idx * 2 + seg_kind) * (D * D) +
                                                    static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll
             for (int q = 0; q < 16; ++q) d4[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
-        } else if (p.state_out && (p.mode == 0 || segment == p.num_segments - 1)) {
+        } else if (p.state_out && (p.mode == 0 || segment == seq_nseg - 1)) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
                                                  static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll

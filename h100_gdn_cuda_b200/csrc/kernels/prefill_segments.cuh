@@ -1,7 +1,9 @@
 // Start states of the segments of a segmented prefill run (see FusedParams in prefill_fused.cuh):
 //     S_start[0] = initial state,   S_start[p + 1] = S_start[p] M_p + N_p
 // with M_p, N_p the composite transition of segment p (fp32, dv x dk and dk x dk with dv = dk = 128)
-// produced by the mode-1 launch of gdn_fused_seq_kernel.  The work is tiny (one 128 x 128 x 128
+// produced by the mode-1 launch of gdn_fused_seq_kernel.  Segment p of a sequence sits in launch
+// slot first_slot + p (locate_segment in prefill_common.cuh); in packed mode the sequences have
+// different numbers of segments.  The work is tiny (one 128 x 128 x 128
 // product per chain and segment) and strictly sequential in p; it stays in fp32 on CUDA cores.
 // One CTA of 128 threads per (chain, block of 8 state rows); thread = column of the state.
 // M_p (64 KB) comes into shared memory by one bulk copy, the copy of M_{p+1} running while M_p is
@@ -10,13 +12,16 @@
 #pragma once
 #include <cuda_bf16.h>
 
+#include "prefill_common.cuh"
 #include "sm100_ptx.cuh"
 
 namespace gdn {
 
 struct SegCombineParams {
-    const float* seg_mn;   // [chain][segment][2][128][128]: N then M
-    float* seg_start;      // [chain][segment][128][128]
+    const float* seg_mn;   // [slot][head][2][128][128]: N then M
+    float* seg_start;      // [slot][head][128][128]
+    ChunkMap map;
+    int seg_chunks;
     const __nv_bfloat16* state_in;  // or NULL
     long long si_ss, si_sh;
     int vh, num_segments;
@@ -45,8 +50,10 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
     const long long chain = blockIdx.x;
     const int r0 = blockIdx.y * R, col = threadIdx.x;
     const int seq = static_cast<int>(chain / p.vh), head = static_cast<int>(chain % p.vh);
-    const int nseg = p.num_segments;
-    auto m_of = [&](int s) { return p.seg_mn + ((chain * nseg + s) * 2 + 1) * (D * D); };
+    const SegPos sp = sequence_segments(p.map, seq, p.seg_chunks, p.num_segments);
+    const int nseg = sp.nseg;
+    auto idx = [&](int s) { return static_cast<long long>(sp.first_slot + s) * p.vh + head; };
+    auto m_of = [&](int s) { return p.seg_mn + (idx(s) * 2 + 1) * (D * D); };
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(&bar[0], 1);
@@ -62,14 +69,14 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
     for (int r = 0; r < R; ++r)
         acc[r] = p.state_in ? __bfloat162float(p.state_in[seq * p.si_ss + head * p.si_sh + static_cast<long long>(r0 + r) * D + col]) : 0.f;
     auto load_n = [&](int s) {
-        const float* N = p.seg_mn + (chain * nseg + s) * 2 * (D * D);
+        const float* N = p.seg_mn + idx(s) * 2 * (D * D);
 #pragma unroll
         for (int r = 0; r < R; ++r) nxt[r] = (s + 1 < nseg) ? N[(r0 + r) * D + col] : 0.f;
     };
     load_n(0);
     __syncthreads();
     for (int s = 0; s < nseg; ++s) {
-        float* dst = p.seg_start + (chain * nseg + s) * (D * D);
+        float* dst = p.seg_start + idx(s) * (D * D);
 #pragma unroll
         for (int r = 0; r < R; ++r) dst[(r0 + r) * D + col] = acc[r];
         if (s + 1 == nseg) break;

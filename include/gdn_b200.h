@@ -244,11 +244,11 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * memory of at least gdn_chunked_forward_workspace_bytes(&shape) bytes, 256-byte aligned; its
  * contents need not be initialised and are garbage afterwards.  It holds one 24 KiB block per
  * 64-token chunk and v-head (the WY/UT transform folded into a 64 x 128 and a 64 x 64 bf16
- * matrix that the state kernel consumes) and, when few long padded
- * sequences are propagated in segments, three fp32 states (192 KiB) per (sequence, v-head) and
- * segment; packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the sequences ordered
- * by length: the state kernel takes the longest first when there are more (sequence, v-head)
- * pairs than SMs).
+ * matrix that the state kernel consumes) and, when few long sequences (padded, or packed with
+ * at most 64 sequences) are propagated in segments, three fp32 states (192 KiB) per (sequence,
+ * v-head) and segment; other packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the
+ * sequences ordered by length: the state kernel takes the longest first when there are more
+ * (sequence, v-head) pairs than SMs).
  * Head dims: dk = dv = 128 for the tensor-core kernels (callers zero-pad smaller head dims);
  * dk = dv = 192 or 256 are accepted as well and run on the kernel of gdn_recurrent_forward
  * (no workspace: gdn_chunked_forward_workspace_bytes returns 0; final_state.ptr must be given). */

@@ -69,8 +69,8 @@ def test_struct_sizes_match_c(lib):
 
 
 def test_workspace_bytes(lib):
-    """Scratch of chunked_forward: 24 KB per (64-token chunk, v-head); for few long padded sequences
-    three fp32 states per chain and segment on top (the segmented state propagation)."""
+    """Scratch of chunked_forward: 24 KB per (64-token chunk, v-head); for few long sequences
+    three fp32 states per v-head and segment slot on top (the segmented state propagation)."""
     from h100_gdn_cuda_b200 import api
     unit = 64 * 128 * 2 + 64 * 64 * 2
     norm = 512  # q/k norm factors per (chunk, k-head); the size queries below are made with one k-head
@@ -82,6 +82,9 @@ def test_workspace_bytes(lib):
     # B=2, T=131072, 4 v-heads: 8 chains -> 18 segments
     long_ctx = api.chunked_forward_workspace_bytes(2, 131072, 4, num_k_heads=1)
     assert long_ctx == 2 * 2048 * (4 * unit + norm) + 256 + 8 * 18 * 3 * 128 * 128 * 4 + 256
+    # the same two sequences packed: segments of 114 chunks, at most 4096 // 114 + 2 = 37 slots
+    packed_long = api.chunked_forward_workspace_bytes(2, 0, 4, total_tokens=2 * 131072, total_chunks=4096, packed=True, num_k_heads=1)
+    assert packed_long == 4096 * (4 * unit + norm) + 256 + 37 * 4 * 3 * 128 * 128 * 4 + 256
     # 128 chains: never segmented
     assert api.chunked_forward_workspace_bytes(4, 131072, 32, num_k_heads=1) == 4 * 2048 * (32 * unit + norm) + 256
 
@@ -100,6 +103,13 @@ def test_segment_plan_heuristic():
                 const gdn::SegmentPlan p = gdn::prefill_segments(chains[i], chunks[i], packed[i]);
                 std::printf("%d %d\\n", p.num_segments, p.seg_chunks);
             }
+            // packed mode: sequences, v-heads, total chunks
+            const int seqs[] = {2, 1, 16, 65, 2, 4}, vh[] = {4, 32, 32, 2, 1, 2};
+            const long long total[] = {4096, 2048, 520, 6000, 259, 267};
+            for (int i = 0; i < 6; ++i) {
+                const gdn::SegmentPlan p = gdn::prefill_segments_packed(seqs[i], vh[i], total[i]);
+                std::printf("%d %d %d\\n", p.num_segments, p.seg_chunks, p.slots);
+            }
             return 0;
         }''')
     with tempfile.TemporaryDirectory() as d:
@@ -114,8 +124,15 @@ def test_segment_plan_heuristic():
     assert rows[3] == (1, 2048)          # 64 chains: three passes cost more than they save
     assert rows[4] == (1, 64)            # the benchmark shape is never segmented
     assert rows[5][0] == 3 and rows[5][0] * rows[5][1] >= 97
-    assert rows[6] == (1, 2048)          # packed mode: not segmented
+    assert rows[6][:2] == (1, 2048)      # the padded plan is not made for packed inputs
     assert rows[7] == (1, 40)            # too short for 32-chunk segments
+    assert rows[8] == (36, 114, 37)      # two long packed sequences of 4 heads: like the padded plan, one CTA wave
+    assert rows[8][2] * 4 <= 148
+    assert rows[9][0] == 1               # 32 heads of one sequence: the slack slot would cost a second wave
+    assert rows[10][0] == 1              # the packed benchmark batch (512 chains) is never segmented
+    assert rows[11][0] == 1              # more sequences than the lookup scans
+    assert rows[12] == (8, 33, 9)        # total // 33 + 2 slots cover any split of 259 chunks over 2 sequences
+    assert rows[13][0] == 1              # four equal sequences would already run side by side
 
 
 def test_state_alignment_is_checked_on_the_host(lib):

@@ -147,6 +147,31 @@ def test_chunked_forward_segmented(gdn, B, T, kh, vh, with_state):
     close(s, s_ref, "final state")
 
 
+@pytest.mark.parametrize("lens,kh,vh,qk_norm", [([6161], 1, 2, False), ([16384 + 70, 70], 1, 1, False),
+                                                ([20000, 0, 5600], 2, 2, False), ([9000, 9100], 1, 2, True)])
+def test_chunked_forward_segmented_packed(gdn, lens, kh, vh, qk_norm):
+    """Few long PACKED sequences take the segmented path as well: segments of one length for all sequences,
+    a sequence shorter than a segment (or empty) keeps one segment, surplus launch slots leave at once."""
+    from h100_gdn_cuda_b200 import api
+    p = synthetic.varlen_inputs(lens, kh, vh, 128, seed=sum(lens), mild_gate=True, normalize=not qk_norm)
+    plain = (64 * 128 * 2 + 64 * 64 * 2) * vh * p["total_chunks"] + 512 * kh * p["total_chunks"]
+    need = api.chunked_forward_workspace_bytes(len(lens), 0, vh, total_tokens=sum(lens), total_chunks=p["total_chunks"],
+                                               packed=True, num_k_heads=kh)
+    assert need > plain + 3 * 128 * 128 * 4, "this shape is meant to be segmented"
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"], is_qk_norm=qk_norm)
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"],
+                               is_qk_norm=qk_norm)
+    check_status(gdn)
+    close(o, o_ref, "O")
+    close(s, s_ref, "final states")
+    for i, n in enumerate(lens):
+        if n == 0:
+            assert torch.equal(s[i], pd["state"][i])
+
+
 def test_chunked_forward_no_state_custom_scale(gdn):
     p = synthetic.prefill_inputs(2, 300, 2, 4, 128, seed=77, with_state=False, mild_gate=True)
     o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], None, scale=0.5)
