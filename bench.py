@@ -36,6 +36,7 @@ cannot run on a B200 and it has no CPU path).
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -241,6 +242,34 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+@contextlib.contextmanager
+def near_gpu(dev, note):
+    """Bind the process to the CPUs NVML reports as local to the GPU while pinned host buffers are
+    allocated (the pages are first touched there, so they land on the GPU's NUMA node and the
+    copies of several ranks do not all cross the socket link); the previous affinity is restored
+    on exit, so nothing else in the run is restricted.  `note` receives what was done."""
+    old = os.sched_getaffinity(0)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(dev).uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(old) + 64) // 64)
+        local = {64 * w + b for w, x in enumerate(words) for b in range(64) if (x >> b) & 1}
+        cpus = local & old
+        if cpus and cpus != old:
+            os.sched_setaffinity(0, cpus)
+            note["host_affinity"] = "pinned buffers allocated on %d of %d allowed CPUs (local to the GPU)" % (len(cpus), len(old))
+        else:
+            note["host_affinity"] = "not bound (%d local CPUs among the %d allowed)" % (len(cpus), len(old))
+    except Exception as e:  # no NVML, no affinity call: allocate wherever the pages fall
+        note["host_affinity"] = "not bound (%s)" % type(e).__name__
+    try:
+        yield
+    finally:
+        os.sched_setaffinity(0, old)
+
+
 def run_only(args, gdn, synthetic, dev, peaks):
     """Small single-path runs for profiler captures (few launches, a few hundred MB)."""
     kh, vh, d = CFG["kh"], CFG["vh"], CFG["d"]
@@ -360,7 +389,11 @@ def main():
     if args.only is not None:
         return run_only(args, gdn, synthetic, dev, peaks)
     p = synthetic.prefill_inputs(B, T, kh, vh, d, seed=rank)
-    host = {k: p[k].pin_memory() for k in ("q", "k", "v", "beta", "g", "state")}
+    affinity_note = {}
+    with near_gpu(dev, affinity_note):
+        host = {k: p[k].pin_memory() for k in ("q", "k", "v", "beta", "g", "state")}
+        out_host = torch.empty(B, T, vh, d, dtype=torch.bfloat16).pin_memory()
+        st_host = torch.empty(B, vh, d, d, dtype=torch.bfloat16).pin_memory()
     devt = {k: v.to(dev) for k, v in host.items()}
     tokens = B * T
     units = B * ((T + CHUNK - 1) // CHUNK) * vh
@@ -425,8 +458,6 @@ def main():
     seq_ms /= args.steps
 
     # ---------------- end to end from host buffers
-    out_host = torch.empty(B, T, vh, d, dtype=torch.bfloat16).pin_memory()
-    st_host = torch.empty(B, vh, d, d, dtype=torch.bfloat16).pin_memory()
     # Three streams (host->device, compute, device->host) and two sets of device staging buffers:
     # every step still copies all of its inputs in and its results out, but the copies of
     # neighbouring steps overlap the kernels and each other (PCIe is full duplex).
@@ -685,7 +716,7 @@ def main():
         "config": {"workload": WORKLOAD,
                    "sharding": "by sequence, no collective", "l2": "inputs (0.41 GB per step) larger than L2"},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "host_affinity": affinity_note.get("host_affinity"),
                 "note": "bound by the pinned-host <-> device copies (%.0f MB per rank and step, %.1f GB/s in + %.1f GB/s out per rank); "
                         "at N > 1 the ranks share the host's memory and PCIe path" % (
                             (h2d + d2h) / 1e6, h2d / (ms_e2e * 1e-3) / 1e9, d2h / (ms_e2e * 1e-3) / 1e9)},
