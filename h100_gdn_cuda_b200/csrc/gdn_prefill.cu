@@ -307,6 +307,24 @@ static int chunked_forward_wide(const GdnChunkedArgs* a, gdn_stream_t stream) {
     return GDN_OK;
 }
 
+// Launch of the state kernel right after the chunk-parallel kernel in the same stream, with
+// programmatic stream serialization: its CTAs may be placed (each takes a whole SM) and set up while
+// that kernel drains; the kernel waits (grid_dep_wait) before it reads that kernel's results.
+static cudaError_t launch_fused_after_zp(dim3 grid, int smem, cudaStream_t st, const CUtensorMap& tmQ, const CUtensorMap& tmK,
+                                         const CUtensorMap& tmV, const CUtensorMap& tmO, const FusedParams& p) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(fused::kThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gdn_fused_seq_kernel, tmQ, tmK, tmV, tmO, p);
+}
+
 // Workspace layout of gdn_chunked_forward: [Z, PT blocks][q/k norm factors][segment states | sequence order]
 static size_t ws_blocks_bytes(size_t chunks, int vh) { return (chunks * static_cast<size_t>(vh) * kZPBlockBytes + 255) / 256 * 256; }
 static size_t ws_norms_bytes(size_t chunks, int kh) { return (chunks * static_cast<size_t>(kh) * 128 * sizeof(float) + 255) / 256 * 256; }
@@ -373,9 +391,13 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     const size_t nchunks = static_cast<size_t>(num_chunks(s));
     float* const norms = a->is_qk_norm ? reinterpret_cast<float*>(ws + ws_blocks_bytes(nchunks, s.num_v_heads)) : nullptr;
     uint8_t* const ws_extra = ws + ws_blocks_bytes(nchunks, s.num_v_heads) + ws_norms_bytes(nchunks, s.num_k_heads);
-    if (int rc = launch_zp(s, a->q, a->k, a->beta, a->gate, a->workspace, norms, a->scale, d, st)) return rc;
-    if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
-
+    // Both kernels are prepared before the first is launched, so that the state kernel is in the stream
+    // when the chunk-parallel kernel starts to drain.
+    auto run_zp = [&]() -> int {
+        if (int rc = launch_zp(s, a->q, a->k, a->beta, a->gate, a->workspace, norms, a->scale, d, st)) return rc;
+        if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[1]), st));
+        return GDN_OK;
+    };
     {
         CUtensorMap tmQ, tmK, tmV, tmO;
         if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
@@ -408,11 +430,11 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             gdn_seq_order_kernel<<<(s.batch + 127) / 128, 128, 0, st>>>(s.cu_seqlens, s.batch, order);
             GDN_CUDA(cudaGetLastError());
             p.seq_order = order;
-            gdn_fused_seq_kernel<<<dim3(s.num_v_heads, s.batch), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
-            GDN_CUDA(cudaGetLastError());
+            if (int rc = run_zp()) return rc;
+            GDN_CUDA(launch_fused_after_zp(dim3(s.num_v_heads, s.batch), smem, st, tmQ, tmK, tmV, tmO, p));
         } else if (plan.num_segments <= 1) {
-            gdn_fused_seq_kernel<<<dim3(s.batch, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
-            GDN_CUDA(cudaGetLastError());
+            if (int rc = run_zp()) return rc;
+            GDN_CUDA(launch_fused_after_zp(dim3(s.batch, s.num_v_heads), smem, st, tmQ, tmK, tmV, tmO, p));
         } else {
             // composite transitions of all segments, their start states, then all segments at once
             float* seg_mn = reinterpret_cast<float*>(ws_extra);
@@ -424,8 +446,9 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             p.seg_mn = seg_mn;
             p.seg_start = seg_start;
             p.mode = 1;
-            gdn_fused_seq_kernel<<<dim3(plan.slots, s.num_v_heads, 2), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
-            GDN_CUDA(cudaGetLastError());
+            if (int rc = set_smem(gdn_seg_combine_kernel, SegCombineSmem::kBytes)) return rc;
+            if (int rc = run_zp()) return rc;
+            GDN_CUDA(launch_fused_after_zp(dim3(plan.slots, s.num_v_heads, 2), smem, st, tmQ, tmK, tmV, tmO, p));
             SegCombineParams cp{};
             cp.seg_mn = seg_mn;
             cp.seg_start = seg_start;
@@ -437,7 +460,6 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.map = p.map;
             cp.seg_chunks = plan.seg_chunks;
             cp.status = d->status;
-            if (int rc = set_smem(gdn_seg_combine_kernel, SegCombineSmem::kBytes)) return rc;
             gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R), 128, SegCombineSmem::kBytes, st>>>(cp);
             GDN_CUDA(cudaGetLastError());
             p.mode = 2;

@@ -471,6 +471,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         float ra0, ra1, rb0, rb1;  // raw gates of chunks c and c + 1
         load_raw(0, ra0, ra1);
         load_raw(1, rb0, rb1);
+        // Everything up to here (and the state warps' load of the initial state) touches only the caller's
+        // inputs and may run while the chunk-parallel kernel drains; its blocks and norm factors are read below.
+        grid_dep_wait();
         for (int c = 0; c < nchunks; ++c) {
             const int s = c & 1;
             const int n = chunk_n(c);
@@ -541,6 +544,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
         // kLead positions after the one the producer has just requested into L2, so that the producer's own
         // loads find them there.  A hint only: when its bounded wait runs out it simply stops.
         constexpr int kLead = 3;
+        grid_dep_wait();
         if (lane == 0) {
             for (int c = kLead; c < nchunks; ++c) {
                 int spins = 0;

@@ -123,6 +123,10 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // The state kernel that follows may be placed on SMs as this grid drains (it takes a whole SM, so
+    // never beside a CTA of this kernel) and do its set-up there; it reads this kernel's results only
+    // after its own grid_dep_wait.
+    if (tid == 0) grid_dep_launch();
 
     const int rep = p.vh / p.kh;               // v-heads per k-head
     const int rounds = (rep + 1) >> 1;         // head pairs per unit

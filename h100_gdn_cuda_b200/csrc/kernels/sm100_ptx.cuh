@@ -201,6 +201,12 @@ GDN_DEVICE void tma_prefetch_2d(const void* tmap, int c0, int c1) {
 GDN_DEVICE void bulk_prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes) : "memory");
 }
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialization may
+// start while the kernel before it in the stream is still running; `grid_dep_wait` blocks until that
+// kernel has completed and its writes are visible (a no-op for an ordinary launch), and
+// `grid_dep_launch` in the earlier kernel lets the later one be scheduled as SMs free up.
+GDN_DEVICE void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+GDN_DEVICE void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 GDN_DEVICE void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(
