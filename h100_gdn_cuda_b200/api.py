@@ -322,9 +322,10 @@ def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None
     _require(0 < d <= _PREFILL_D_MAX, "chunked_forward supports head dims up to %d (got %d)" % (_PREFILL_D_MAX, d))
     if scale is None:
         scale = 1.0 / math.sqrt(d)
-    # up to 128: the tensor-core kernels (zero-padded to 128); 129..256: the library runs the
-    # token recurrence on 192 or 256 columns instead (no scratch)
-    D = _PREFILL_D if d <= _PREFILL_D else _aligned_dim(d)
+    # up to 128: the tensor-core kernels, which compute on 128 columns.  A head dim that is a multiple of 8
+    # goes in as it is (the library's tensor maps supply the zero columns, nothing is copied); any other is
+    # zero-padded to 128 here.  129..256: the library runs the token recurrence on 192 or 256 columns instead.
+    D = (d if d % 8 == 0 else _PREFILL_D) if d <= _PREFILL_D else _aligned_dim(d)
     q, k, v = _pad_last(query, D), _pad_last(key, D), _pad_last(value, D)
     s_in = _pad_state(initial_state, D)
     if s_in is not None:

@@ -26,15 +26,17 @@ int require_d128(const GdnShape& s, const char* who) {
 }
 
 // 4-D map over a token tensor: (dim, head, token, batch), box 64 x 1 x 64 x 1, 128-byte swizzle.
-int make_token_map(CUtensorMap* out, const GdnTokenTensor& t, const GdnShape& s, int heads, const char* name) {
+// `dim` below 128 (a multiple of 8): loads fill the columns past it with zeros and stores leave them out,
+// so a kernel built for 128 sees a zero-padded head without a padded copy in memory.
+int make_token_map(CUtensorMap* out, const GdnTokenTensor& t, const GdnShape& s, int heads, const char* name, int dim = kD) {
     const bool packed = s.cu_seqlens != nullptr;
     const uint64_t tokens = packed ? static_cast<uint64_t>(s.total_tokens) : static_cast<uint64_t>(s.seq_len);
     const uint64_t batch = packed ? 1 : static_cast<uint64_t>(s.batch);
-    uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(heads), tokens, batch};
+    uint64_t dims[4] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(heads), tokens, batch};
     uint64_t sb = static_cast<uint64_t>(t.stride_batch) * 2;
     if (packed || sb == 0) sb = std::max<uint64_t>(16, tokens * static_cast<uint64_t>(t.stride_token) * 2);
     uint64_t strides[3] = {static_cast<uint64_t>(t.stride_head) * 2, static_cast<uint64_t>(t.stride_token) * 2, sb};
-    if (heads == 1 && strides[0] == 0) strides[0] = kD * 2;
+    if (heads == 1 && strides[0] == 0) strides[0] = static_cast<uint64_t>(dim) * 2;
     uint32_t box[4] = {64, 1, 64, 1};
     if (tokens == 0) return fail(GDN_ERR_INVALID, "%s: no tokens", name);
     if (!make_tmap_bf16(out, t.ptr, 4, dims, strides, box, true))
@@ -130,8 +132,8 @@ int launch_zp(const GdnShape& s, const GdnTokenTensor& q, const GdnTokenTensor& 
     const int nc = num_chunks(s);
     if (nc == 0) return GDN_OK;
     CUtensorMap tmK, tmQ;
-    if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k")) return rc;
-    if (int rc = make_token_map(&tmQ, q, s, s.num_k_heads, "q")) return rc;
+    if (int rc = make_token_map(&tmK, k, s, s.num_k_heads, "k", s.head_dim_k)) return rc;
+    if (int rc = make_token_map(&tmQ, q, s, s.num_k_heads, "q", s.head_dim_k)) return rc;
     ZPParams p{};
     p.map = chunk_map(s);
     p.beta = scalar_view(beta);
@@ -358,11 +360,18 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     const GdnShape& s = a->shape;
     if (int rc = check_shape(s, true)) return rc;
     if (wide_heads(s)) return chunked_forward_wide(a, stream);
-    if (int rc = require_d128(s, "gdn_chunked_forward")) return rc;
-    if (int rc = check_token_tensor(a->q, "q", kD)) return rc;
-    if (int rc = check_token_tensor(a->k, "k", kD)) return rc;
-    if (int rc = check_token_tensor(a->v, "v", kD)) return rc;
-    if (int rc = check_token_tensor(a->out, "out", kD)) return rc;
+    // The kernels are built for dk = dv = 128.  A smaller head dim that is a multiple of 8 (the 16-byte
+    // rule of the copies) runs on them as it is: the tensor maps deliver zero columns past it and the state
+    // is read and written with a column predicate, which is the zero-padded problem without padded copies.
+    const int hd = s.head_dim_k;
+    if (s.head_dim_k != s.head_dim_v || hd % 8 != 0)
+        return fail(GDN_ERR_UNSUPPORTED,
+                    "gdn_chunked_forward: head dims must be dk = dv, a multiple of 8 up to 128, or 192 / 256 (got %d, %d); "
+                    "pad the head dimension with zeros (the Python and C++ wrappers do)", s.head_dim_k, s.head_dim_v);
+    if (int rc = check_token_tensor(a->q, "q", hd)) return rc;
+    if (int rc = check_token_tensor(a->k, "k", hd)) return rc;
+    if (int rc = check_token_tensor(a->v, "v", hd)) return rc;
+    if (int rc = check_token_tensor(a->out, "out", hd)) return rc;
     if (int rc = check_scalar(a->beta, "beta", true)) return rc;
     if (int rc = check_scalar(a->gate, "gate", false)) return rc;
     if (int rc = check_state(a->initial_state, "initial_state")) return rc;
@@ -400,11 +409,12 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
     };
     {
         CUtensorMap tmQ, tmK, tmV, tmO;
-        if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q")) return rc;
-        if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k")) return rc;
-        if (int rc = make_token_map(&tmV, a->v, s, s.num_v_heads, "v")) return rc;
-        if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "out")) return rc;
+        if (int rc = make_token_map(&tmQ, a->q, s, s.num_k_heads, "q", hd)) return rc;
+        if (int rc = make_token_map(&tmK, a->k, s, s.num_k_heads, "k", hd)) return rc;
+        if (int rc = make_token_map(&tmV, a->v, s, s.num_v_heads, "v", hd)) return rc;
+        if (int rc = make_token_map(&tmO, a->out, s, s.num_v_heads, "out", hd)) return rc;
         FusedParams p{};
+        p.d = hd;
         p.map = chunk_map(s);
         p.gate = scalar_view(a->gate);
         p.out = token_view(a->out);
@@ -455,6 +465,7 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.state_in = p.state_in;
             cp.si_ss = p.si_ss;
             cp.si_sh = p.si_sh;
+            cp.d = hd;
             cp.vh = s.num_v_heads;
             cp.num_segments = plan.num_segments;
             cp.map = p.map;

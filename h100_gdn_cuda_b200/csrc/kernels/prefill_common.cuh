@@ -131,13 +131,14 @@ __device__ __forceinline__ uint32_t tile_off(int row, int c16) {
 
 // Row-predicated copy of rows [0, n) of such a tile to global memory (used where a TMA store
 // would write past the end of a packed sequence).
+// `pieces`: 16-byte pieces of a row that exist in the destination (head dim / 8).
 template <int THREADS>
 __device__ __forceinline__ void store_tile_rows(const uint8_t* tile, const TokenView& dst, int batch, long long tok0,
-                                                int head, int n, int tid) {
+                                                int head, int n, int tid, int pieces = 16) {
     __nv_bfloat16* base = dst.ptr + batch * dst.sb + tok0 * dst.st + static_cast<long long>(head) * dst.sh;
     for (int idx = tid; idx < kChunk * 16; idx += THREADS) {
         const int row = idx >> 4, c16 = idx & 15;
-        if (row < n) {
+        if (row < n && c16 < pieces) {
             const uint4 v = *reinterpret_cast<const uint4*>(tile + tile_off(row, c16));
             *reinterpret_cast<uint4*>(base + row * dst.st + c16 * 8) = v;
         }

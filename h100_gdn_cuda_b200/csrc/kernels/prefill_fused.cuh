@@ -38,6 +38,8 @@ struct FusedParams {
     __nv_bfloat16* state_out;  // final state or NULL
     long long so_ss, so_sh;
     int kh, vh;
+    int d;  // head dim of the caller's tensors and states (a multiple of 8, at most 128); the kernel computes on 128
+            // columns, the tensor maps fill the rest with zeros, states are read and written with a predicate
     float scale;
     int* status;
     const uint8_t* blocks;  // Z, PT of every (global chunk, v-head): kZPBlockBytes each
@@ -246,10 +248,10 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             for (int q = 0; q < 64; ++q) S[q] = (seg_kind == 1 && row == 64 * hf + q) ? 1.f : 0.f;
         } else if (p.state_in) {
             const uint4* src = reinterpret_cast<const uint4*>(p.state_in + seq * p.si_ss + head * p.si_sh +
-                                                              static_cast<long long>(row) * D + 64 * hf);
+                                                              static_cast<long long>(row) * p.d + 64 * hf);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-                const uint4 v = __ldg(src + q);
+                const uint4 v = (row < p.d && 64 * hf + 8 * q < p.d) ? __ldg(src + q) : make_uint4(0u, 0u, 0u, 0u);
                 S[q * 8 + 0] = bf16_lo(v.x); S[q * 8 + 1] = bf16_hi(v.x);
                 S[q * 8 + 2] = bf16_lo(v.y); S[q * 8 + 3] = bf16_hi(v.y);
                 S[q * 8 + 4] = bf16_lo(v.z); S[q * 8 + 5] = bf16_hi(v.z);
@@ -371,7 +373,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             for (int q = 0; q < 16; ++q) d4[q] = make_float4(S[4 * q], S[4 * q + 1], S[4 * q + 2], S[4 * q + 3]);
         } else if (p.state_out && (p.mode == 0 || segment == seq_nseg - 1)) {
             uint4* d4 = reinterpret_cast<uint4*>(p.state_out + seq * p.so_ss + head * p.so_sh +
-                                                 static_cast<long long>(row) * D + 64 * hf);
+                                                 static_cast<long long>(row) * p.d + 64 * hf);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 uint4 v;
@@ -379,7 +381,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 v.y = pack_bf16(S[q * 8 + 2], S[q * 8 + 3]);
                 v.z = pack_bf16(S[q * 8 + 4], S[q * 8 + 5]);
                 v.w = pack_bf16(S[q * 8 + 6], S[q * 8 + 7]);
-                d4[q] = v;
+                if (row < p.d && 64 * hf + 8 * q < p.d) d4[q] = v;
             }
         }
     } else if (warp < 12) {
@@ -441,12 +443,12 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 // a wait has given up: the tile is garbage and stays on chip
             } else if (!ragged) {
                 if (otid == 0) {
-                    tma_store_4d(&tmO, sO, 0, head, static_cast<int>(tok0), batch);
-                    tma_store_4d(&tmO, sO + 8192, 64, head, static_cast<int>(tok0), batch);
+                    tma_store_4d(&tmO, sO, 0, head, static_cast<int>(tok0), batch);  // columns past the head dim are clipped
+                    if (p.d > 64) tma_store_4d(&tmO, sO + 8192, 64, head, static_cast<int>(tok0), batch);
                     bulk_commit();
                 }
             } else {
-                store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid);
+                store_tile_rows<128>(sO, p.out, batch, tok0, head, n, otid, p.d >> 3);
             }
         }
         if (otid == 0) bulk_wait_read<0>();
@@ -554,6 +556,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
                 const uint8_t* blk = p.blocks + (static_cast<size_t>(gchunk0 + c) * p.vh + head) * kZPBlockBytes;
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
+                    if (a * 64 >= p.d) break;  // nothing in memory behind the second half of a small head
                     tma_prefetch_4d(&tmK, a * 64, khead, tok, batch);
                     tma_prefetch_4d(&tmV, a * 64, head, tok, batch);
                     if (emit_o) tma_prefetch_4d(&tmQ, a * 64, khead, tok, batch);

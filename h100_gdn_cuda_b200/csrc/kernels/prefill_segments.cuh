@@ -22,8 +22,9 @@ struct SegCombineParams {
     float* seg_start;      // [slot][head][128][128]
     ChunkMap map;
     int seg_chunks;
-    const __nv_bfloat16* state_in;  // or NULL
+    const __nv_bfloat16* state_in;  // or NULL; d x d per (sequence, head), zero outside when d < 128
     long long si_ss, si_sh;
+    int d;
     int vh, num_segments;
     int* status;
 };
@@ -67,7 +68,9 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
     float acc[R], nxt[R];  // nxt: the N rows of the coming segment, fetched one iteration ahead
 #pragma unroll
     for (int r = 0; r < R; ++r)
-        acc[r] = p.state_in ? __bfloat162float(p.state_in[seq * p.si_ss + head * p.si_sh + static_cast<long long>(r0 + r) * D + col]) : 0.f;
+        acc[r] = (p.state_in && r0 + r < p.d && col < p.d)
+                     ? __bfloat162float(p.state_in[seq * p.si_ss + head * p.si_sh + static_cast<long long>(r0 + r) * p.d + col])
+                     : 0.f;
     auto load_n = [&](int s) {
         const float* N = p.seg_mn + idx(s) * 2 * (D * D);
 #pragma unroll

@@ -110,9 +110,10 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     const int64_t d = query.size(-1);
     require(key.size(-1) == d && value.size(-1) == d, "chunked kernels need dk == dv");
     require(d > 0 && d <= 256, "chunked_forward supports head dims up to 256");
-    // up to 128: the tensor-core kernels on head dim 128 (zero-padded); 129..256: the library runs
-    // the token recurrence on 192 or 256 columns instead
-    const int64_t D = d <= kPrefillDim ? kPrefillDim : (d + 63) / 64 * 64;
+    // up to 128: the tensor-core kernels, which compute on 128 columns; a head dim that is a multiple of 8 goes
+    // in as it is (the library's tensor maps supply the zero columns), any other is zero-padded to 128 here.
+    // 129..256: the library runs the token recurrence on 192 or 256 columns instead
+    const int64_t D = d <= kPrefillDim ? (d % 8 == 0 ? d : kPrefillDim) : (d + 63) / 64 * 64;
     at::Tensor q = pad_last(query, D), k = pad_last(key, D), v = pad_last(value, D);
     std::optional<at::Tensor> s_in;
     if (initial_state.has_value()) {

@@ -249,7 +249,9 @@ int gdn_compute_o(const GdnComputeOArgs* args, gdn_stream_t stream);
  * v-head) and segment; other packed inputs of 2 to 2048 sequences add 4 bytes per sequence (the
  * sequences ordered by length: the state kernel takes the longest first when there are more
  * (sequence, v-head) pairs than SMs).
- * Head dims: dk = dv = 128 for the tensor-core kernels (callers zero-pad smaller head dims);
+ * Head dims: the tensor-core kernels compute on dk = dv = 128; any dk = dv that is a multiple of 8 up to
+ * 128 is taken as it is (the tensor maps deliver zero columns past it, states are d x d; no padded copies),
+ * callers zero-pad other head dims below 128;
  * dk = dv = 192 or 256 are accepted as well and run on the kernel of gdn_recurrent_forward
  * (no workspace: gdn_chunked_forward_workspace_bytes returns 0; final_state.ptr must be given). */
 typedef struct {

@@ -200,6 +200,29 @@ def test_chunked_forward_varlen(gdn, lens):
     close(s, s_ref, "final state")
 
 
+@pytest.mark.parametrize("d,lens,kh,vh", [(64, [130, 97, 65, 255], 2, 4), (96, [300, 5, 1000, 64, 17], 1, 2),
+                                          (8, [70, 1], 1, 1), (64, [9000, 9100], 1, 2)])
+def test_chunked_forward_small_head_dims_unpadded(gdn, d, lens, kh, vh):
+    """Head dims below 128 that are multiples of 8 go to the kernels as they are (zero columns come from the
+    tensor maps, states are d x d): packed inputs with ragged chunk tails, and one segmented case."""
+    p = synthetic.varlen_inputs(lens, kh, vh, d, seed=d + sum(lens), mild_gate=True)
+    o_ref, s_ref = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(),
+                                   cu_seqlens=p["cu_seqlens"])
+    pd = dev(p)
+    o, s = gdn.chunked_forward(pd["q"], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                               pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    check_status(gdn)
+    assert o.shape == p["v"].shape and s.shape == p["state"].shape and o.is_contiguous()
+    close(o, o_ref, "O")
+    close(s, s_ref, "final states")
+    # a strided view of a wider buffer (the layout of a fused projection): neighbours must stay untouched
+    wide = torch.randn(sum(lens), kh, 3 * d, device="cuda").bfloat16()
+    wide[..., :d], wide[..., d:2 * d] = pd["q"], pd["k"]
+    o2, s2 = gdn.chunked_forward(wide[..., :d], wide[..., d:2 * d], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                                 pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    assert torch.equal(o2, o) and torch.equal(s2, s)
+
+
 def test_varlen_equals_padded_per_sequence(gdn):
     lens = [200, 77]
     p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=4, mild_gate=True)
