@@ -106,9 +106,9 @@ def seq_kernel_bytes_per_unit(kh: int, vh: int, d: int, c: int = CHUNK) -> float
 #   gdn_fused_seq_kernel : same capture, 4096 units
 #   gdn_recurrent_kernel : B=128 capture (gating fused), 128 sequence-tokens
 # (written data still in L2 when a launch ends is not counted by the DRAM counters)
-NCU_ZP_TRAFFIC_PER_UNIT = (68.746752e6 + 43.661312e6) / 4096
-NCU_FUSED_TRAFFIC_PER_UNIT = (238.145792e6 + 46.908928e6) / 4096
-NCU_DECODE_TRAFFIC_PER_TOKEN = (136.383488e6 + 86.052864e6) / 128
+NCU_ZP_TRAFFIC_PER_UNIT = (68.743168e6 + 41.161216e6) / 4096
+NCU_FUSED_TRAFFIC_PER_UNIT = (238.593280e6 + 39.856384e6) / 4096
+NCU_DECODE_TRAFFIC_PER_TOKEN = (136.373248e6 + 84.418816e6) / 128
 
 
 def decode_bytes_per_token(kh, vh, d) -> float:
