@@ -166,7 +166,7 @@ std::pair<at::Tensor, at::Tensor> recurrent_impl(at::Tensor& query, at::Tensor& 
                                                  const Gating* gating, std::optional<at::Tensor>& cu_seqlens,
                                                  std::optional<at::Tensor>& num_accepted_tokens,
                                                  InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
-                                                 std::optional<float> scale) {
+                                                 std::optional<float> scale, const RecurrentExtensions& ext = {}) {
     cuda_bf16(query, "query");
     cuda_bf16(key, "key");
     cuda_bf16(value, "value");
@@ -177,11 +177,21 @@ std::pair<at::Tensor, at::Tensor> recurrent_impl(at::Tensor& query, at::Tensor& 
     const int64_t d_al = align64(d), dv_al = align64(dv_in);
     require(d_al <= 256 && dv_al <= 256, "head dims above 256 are not supported");
     at::Tensor q = pad_last(query, d_al), k = pad_last(key, d_al), v = pad_last(value, dv_al);
+    // the state: bf16, or fp32 when the caller's initial state is fp32 (it then stays fp32); updated where it
+    // lies when the caller asks for that or passes a pool of states with one slot index per sequence
+    const bool in_place = ext.inplace_state || ext.state_indices.has_value();
     std::optional<at::Tensor> s_in;
+    auto state_opts = v.options();
     if (initial_state.has_value()) {
-        cuda_bf16(*initial_state, "initial_state");
-        at::Tensor t = pad_state(*initial_state, dv_al, d_al);
+        const at::Tensor& s0 = *initial_state;
+        require(s0.is_cuda() && (s0.scalar_type() == at::kBFloat16 || s0.scalar_type() == at::kFloat),
+                "initial_state must be a bf16 or fp32 CUDA tensor");
+        state_opts = s0.options();
+        at::Tensor t = pad_state(s0, dv_al, d_al);
         if (!(t.stride(-1) == 1 && t.stride(-2) == d_al)) t = t.contiguous();
+        // a padded or compacted copy would never reach the caller's tensor
+        require(!in_place || t.data_ptr() == s0.data_ptr(),
+                "inplace_state / state_indices need head dims that are multiples of 64 and contiguous (dv, dk) blocks");
         s_in = t;
     }
     GdnRecurrentArgs a{};
@@ -190,12 +200,22 @@ std::pair<at::Tensor, at::Tensor> recurrent_impl(at::Tensor& query, at::Tensor& 
     at::Tensor out = at::empty_like(v);
     at::Tensor s_out;
     if (store_steps) {
-        s_out = packed ? at::empty({q.size(0), vh, dv_al, d_al}, v.options())
-                       : at::empty({q.size(0), q.size(1), vh, dv_al, d_al}, v.options());
+        require(!ext.state_indices.has_value(), "state_indices cannot be combined with per-token states");
+        s_out = packed ? at::empty({q.size(0), vh, dv_al, d_al}, state_opts)
+                       : at::empty({q.size(0), q.size(1), vh, dv_al, d_al}, state_opts);
         a.state_out = GdnState{s_out.data_ptr(), vh * dv_al * d_al, dv_al * d_al};
-    } else {
-        s_out = at::empty({a.shape.batch, vh, dv_al, d_al}, v.options());
+    } else if (in_place) {
+        require(s_in.has_value(), "inplace_state / state_indices need an initial_state");
+        s_out = *s_in;
         a.state_out = st(s_out);
+    } else {
+        s_out = at::empty({a.shape.batch, vh, dv_al, d_al}, state_opts);
+        a.state_out = st(s_out);
+    }
+    a.state_dtype = state_opts.dtype() == at::kFloat ? GDN_F32 : GDN_BF16;
+    if (ext.state_indices.has_value()) {
+        require(ext.state_indices->numel() == a.shape.batch, "state_indices needs one entry per sequence");
+        a.state_indices = i32(ext.state_indices, "state_indices");
     }
     const int64_t tokens = packed ? q.size(0) : q.size(1);
     a.q = tok(q, packed);
@@ -249,6 +269,94 @@ std::pair<at::Tensor, at::Tensor> recurrent_forward_fused_gating(
     Gating g{A_log, dt_bias, a, b};
     return recurrent_impl(query, key, value, initial_state, std::nullopt, std::nullopt, &g, cu_seqlens, num_accepted_tokens,
                           inference_mode, stream, is_qk_norm, scale);
+}
+
+std::pair<at::Tensor, at::Tensor> recurrent_forward_ext(at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                                        std::optional<at::Tensor>& initial_state,
+                                                        std::optional<at::Tensor>& beta, std::optional<at::Tensor>& gate,
+                                                        std::optional<std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor>>& gating,
+                                                        std::optional<at::Tensor>& cu_seqlens,
+                                                        std::optional<at::Tensor>& num_accepted_tokens,
+                                                        InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
+                                                        std::optional<float> scale, const RecurrentExtensions& ext) {
+    if (gating.has_value()) {
+        require(!beta.has_value() && !gate.has_value(), "pass either gating=(A_log, dt_bias, a, b) or beta/gate, not both");
+        Gating g{std::get<0>(*gating), std::get<1>(*gating), std::get<2>(*gating), std::get<3>(*gating)};
+        return recurrent_impl(query, key, value, initial_state, std::nullopt, std::nullopt, &g, cu_seqlens, num_accepted_tokens,
+                              inference_mode, stream, is_qk_norm, scale, ext);
+    }
+    return recurrent_impl(query, key, value, initial_state, beta, gate, nullptr, cu_seqlens, num_accepted_tokens,
+                          inference_mode, stream, is_qk_norm, scale, ext);
+}
+
+std::pair<at::Tensor, std::optional<at::Tensor>> causal_conv1d(at::Tensor& x, at::Tensor& weight,
+                                                               std::optional<at::Tensor>& bias,
+                                                               std::optional<at::Tensor>& initial_state,
+                                                               std::optional<at::Tensor>& cu_seqlens, bool activation,
+                                                               std::optional<at::Tensor>& final_state,
+                                                               bool return_final_state, cudaStream_t stream) {
+    cuda_bf16(x, "x");
+    cuda_bf16(weight, "weight");
+    require(x.stride(-1) == 1, "channels must be contiguous");
+    require(weight.dim() == 2 && x.size(-1) == weight.size(0), "weight must be (channels, width)");
+    const bool packed = cu_seqlens.has_value();
+    const int64_t C = weight.size(0), W = weight.size(1);
+    require(packed ? x.dim() == 2 : x.dim() == 3, packed ? "packed input is (tokens, channels)" : "padded input is (batch, tokens, channels)");
+    const int64_t batch = packed ? cu_seqlens->numel() - 1 : x.size(0);
+    at::Tensor y = at::empty(x.sizes(), x.options());
+    at::Tensor w = weight.contiguous(), b, s_in;
+    if (bias.has_value()) {
+        cuda_bf16(*bias, "bias");
+        b = bias->contiguous();
+    }
+    if (initial_state.has_value()) {
+        cuda_bf16(*initial_state, "initial_state");
+        require(initial_state->dim() == 3 && initial_state->size(0) == batch && initial_state->size(1) == W - 1 &&
+                    initial_state->size(2) == C,
+                "initial_state must be (sequences, W-1, C) bf16");
+        s_in = initial_state->contiguous();
+    }
+    std::optional<at::Tensor> s_out = final_state;
+    if (!s_out.has_value() && return_final_state) s_out = at::empty({batch, W - 1, C}, x.options());
+    if (s_out.has_value())
+        require(s_out->is_contiguous() && s_out->dim() == 3 && s_out->size(0) == batch && s_out->size(1) == W - 1 &&
+                    s_out->size(2) == C && s_out->scalar_type() == at::kBFloat16,
+                "final_state must be contiguous (sequences, W-1, C) bf16");
+    GdnConvArgs a{};
+    a.x = x.data_ptr();
+    a.y = y.data_ptr();
+    a.weight = w.data_ptr();
+    a.bias = b.defined() ? b.data_ptr() : nullptr;
+    a.state_in = s_in.defined() ? s_in.data_ptr() : nullptr;
+    a.state_out = s_out.has_value() ? s_out->data_ptr() : nullptr;
+    a.x_stride_batch = packed ? 0 : x.stride(0);
+    a.x_stride_token = packed ? x.stride(0) : x.stride(1);
+    a.y_stride_batch = packed ? 0 : y.stride(0);
+    a.y_stride_token = packed ? y.stride(0) : y.stride(1);
+    a.batch = static_cast<int32_t>(batch);
+    a.seq_len = packed ? 0 : static_cast<int32_t>(x.size(1));
+    a.total_tokens = packed ? x.size(0) : x.size(0) * x.size(1);
+    a.cu_seqlens = i32(cu_seqlens, "cu_seqlens");
+    a.channels = static_cast<int32_t>(C);
+    a.width = static_cast<int32_t>(W);
+    a.silu = activation ? 1 : 0;
+    check(gdn_causal_conv1d(&a, stream), "causal_conv1d");
+    return {y, s_out};
+}
+
+at::Tensor gated_rmsnorm(at::Tensor& x, at::Tensor& z, at::Tensor& weight, float eps, cudaStream_t stream) {
+    cuda_bf16(x, "x");
+    cuda_bf16(z, "z");
+    cuda_bf16(weight, "weight");
+    require(x.sizes() == z.sizes() && x.size(-1) == weight.numel(),
+            "x and z must have the same shape, weight one entry per column");
+    const int64_t D = x.size(-1);
+    at::Tensor x2 = x.contiguous().view({-1, D}), z2 = z.contiguous().view({-1, D}), w = weight.contiguous();
+    at::Tensor y = at::empty(x2.sizes(), x.options());
+    check(gdn_gated_rmsnorm(x2.data_ptr(), z2.data_ptr(), y.data_ptr(), w.data_ptr(), x2.size(0), static_cast<int32_t>(D),
+                            x2.stride(0), z2.stride(0), y.stride(0), eps, stream),
+          "gated_rmsnorm");
+    return y.view(x.sizes());
 }
 
 void bf16_gdn_recurrent(at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor>& initial_state,

@@ -7,6 +7,7 @@
 
 #include <optional>
 #include <string>
+#include <tuple>
 #include <utility>
 
 namespace gdn_cuda {
@@ -38,6 +39,34 @@ std::pair<at::Tensor, at::Tensor> recurrent_forward_fused_gating(
     at::Tensor& dt_bias, at::Tensor& a, at::Tensor& b, std::optional<at::Tensor>& cu_seqlens,
     std::optional<at::Tensor>& num_accepted_tokens, InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
     std::optional<float> scale);
+
+// Extensions of recurrent_forward beyond the reference's signature (all off by default):
+//   inplace_state  the new state overwrites `initial_state`, which is returned;
+//   state_indices  int32, one entry per sequence: `initial_state` is a pool of states (P, vh, dv, dk), sequence s
+//                  uses and updates slot state_indices[s]; a negative slot marks a padding sequence (skipped).
+// An fp32 `initial_state` (head dims 64 and 128) keeps the state in fp32: read, updated and returned as fp32.
+struct RecurrentExtensions {
+    bool inplace_state = false;
+    std::optional<at::Tensor> state_indices;
+};
+// recurrent_forward with either beta / gate or gating = (A_log, dt_bias, a, b), and the extensions above
+std::pair<at::Tensor, at::Tensor> recurrent_forward_ext(
+    at::Tensor& query, at::Tensor& key, at::Tensor& value, std::optional<at::Tensor>& initial_state,
+    std::optional<at::Tensor>& beta, std::optional<at::Tensor>& gate,
+    std::optional<std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor>>& gating, std::optional<at::Tensor>& cu_seqlens,
+    std::optional<at::Tensor>& num_accepted_tokens, InferenceMode inference_mode, cudaStream_t stream, bool is_qk_norm,
+    std::optional<float> scale, const RecurrentExtensions& ext);
+
+// The two memory-bound steps around the layer in Qwen3-Next-style blocks (no counterpart in the reference, whose
+// callers run them): depthwise causal convolution (+ SiLU) over (B, T, C) or packed (N, C) with an optional carried
+// state (sequences, W-1, C), returning (y, final_state or nothing); and y = rmsnorm(x) * weight * silu(z).
+std::pair<at::Tensor, std::optional<at::Tensor>> causal_conv1d(at::Tensor& x, at::Tensor& weight,
+                                                               std::optional<at::Tensor>& bias,
+                                                               std::optional<at::Tensor>& initial_state,
+                                                               std::optional<at::Tensor>& cu_seqlens, bool activation,
+                                                               std::optional<at::Tensor>& final_state,
+                                                               bool return_final_state, cudaStream_t stream);
+at::Tensor gated_rmsnorm(at::Tensor& x, at::Tensor& z, at::Tensor& weight, float eps, cudaStream_t stream);
 
 // csrc/apis/gdn_forward.hpp:43-49: the recurrence on caller-provided output tensors.  `final_state` is
 // (B, vh, dv, dk), or one state per token when `store_step_state`; head dims must be multiples of 64

@@ -45,27 +45,49 @@ PYBIND11_MODULE(gdn_cuda, m) {
         [](at::Tensor& q, at::Tensor& k, at::Tensor& v, std::optional<at::Tensor> initial_state,
            std::optional<at::Tensor> beta, std::optional<at::Tensor> gate, std::optional<at::Tensor> cu_seqlens,
            std::optional<at::Tensor> num_accepted_tokens, int inference_mode, bool is_qk_norm, std::optional<float> scale,
-           std::optional<std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor>> gating) {
+           std::optional<std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor>> gating, bool inplace_state,
+           std::optional<at::Tensor> state_indices) {
             OnDevice dev(q);
             const auto mode = static_cast<gdn_cuda::InferenceMode>(inference_mode);
-            if (gating.has_value()) {
-                if (beta.has_value() || gate.has_value())
-                    throw std::runtime_error("pass either gating=(A_log, dt_bias, a, b) or beta/gate, not both");
-                auto& [A_log, dt_bias, a, b] = *gating;
-                return gdn_cuda::recurrent_forward_fused_gating(q, k, v, initial_state, A_log, dt_bias, a, b, cu_seqlens,
-                                                                num_accepted_tokens, mode, dev.stream(), is_qk_norm, scale);
-            }
-            if (!beta.has_value()) throw std::runtime_error("beta is required");
-            at::Tensor g = gate.has_value() ? *gate : at::Tensor();
-            return gdn_cuda::recurrent_forward(q, k, v, initial_state, *beta, g, cu_seqlens, num_accepted_tokens, mode,
-                                               dev.stream(), is_qk_norm, scale);
+            if (!gating.has_value() && !beta.has_value()) throw std::runtime_error("beta is required");
+            gdn_cuda::RecurrentExtensions ext;
+            ext.inplace_state = inplace_state;
+            ext.state_indices = state_indices;
+            return gdn_cuda::recurrent_forward_ext(q, k, v, initial_state, beta, gate, gating, cu_seqlens, num_accepted_tokens,
+                                                   mode, dev.stream(), is_qk_norm, scale, ext);
         },
         py::arg("query"), py::arg("key"), py::arg("value"), py::arg("initial_state") = py::none(), py::arg("beta"),
         py::arg("gate"), py::arg("cu_seqlens") = py::none(), py::arg("num_accepted_tokens") = py::none(),
         py::arg("inference_mode") = 0, py::arg("is_qk_norm") = false, py::arg("scale") = py::none(), py::kw_only(),
-        py::arg("gating") = py::none(),
+        py::arg("gating") = py::none(), py::arg("inplace_state") = false, py::arg("state_indices") = py::none(),
         "Token recurrence for decode / speculative verify.  Returns (output, new_state); new_state holds one state "
         "per token when inference_mode == SpecVerify.");
+
+    m.def(
+        "causal_conv1d",
+        [](at::Tensor& x, at::Tensor& weight, std::optional<at::Tensor> bias, std::optional<at::Tensor> initial_state,
+           std::optional<at::Tensor> cu_seqlens, bool activation, std::optional<at::Tensor> final_state,
+           bool return_final_state) -> py::object {
+            OnDevice dev(x);
+            auto r = gdn_cuda::causal_conv1d(x, weight, bias, initial_state, cu_seqlens, activation, final_state,
+                                             return_final_state, dev.stream());
+            if (r.second.has_value()) return py::cast(std::make_pair(r.first, *r.second));
+            return py::cast(r.first);
+        },
+        py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(), py::arg("initial_state") = py::none(),
+        py::arg("cu_seqlens") = py::none(), py::arg("activation") = true, py::arg("final_state") = py::none(),
+        py::arg("return_final_state") = false,
+        "Depthwise causal convolution along the token axis (+ SiLU) over (B,T,C) or packed (N,C); returns y, or "
+        "(y, final_state) when a final state is asked for.  Not part of the reference's module.");
+
+    m.def(
+        "gated_rmsnorm",
+        [](at::Tensor& x, at::Tensor& z, at::Tensor& weight, float eps) {
+            OnDevice dev(x);
+            return gdn_cuda::gated_rmsnorm(x, z, weight, eps, dev.stream());
+        },
+        py::arg("x"), py::arg("z"), py::arg("weight"), py::arg("eps") = 1e-6f,
+        "y = x * rsqrt(mean(x^2) + eps) * weight * silu(z) over the last axis.  Not part of the reference's module.");
 
     m.def(
         "fused_gdn_gating",

@@ -167,3 +167,52 @@ def test_extensions_same_bits(mods):
     o1, s1 = py.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"], is_qk_norm=True)
     o2, s2 = ext.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"], is_qk_norm=True)
     assert torch.equal(o1, o2) and torch.equal(s1, s2)
+
+
+def test_state_pool_fp32_state_and_layer_adjacent_same_bits(mods):
+    """The pybind front end carries the same keyword-only extensions as the ctypes one: an indexed state pool,
+    an in-place state, fp32 states, and the two layer-adjacent kernels."""
+    py, ext = mods
+    d = dev(synthetic.decode_inputs(5, 1, 2, 4, 128, seed=21))
+    gating = (d["A_log"], d["dt_bias"], d["a"], d["b"])
+    # indexed pool: 8 slots, sequence 2 is padding (negative slot)
+    idx = torch.tensor([6, 0, -1, 3, 5], dtype=torch.int32, device="cuda")
+    pool = (torch.randn(8, 4, 128, 128, device="cuda") * 0.05).bfloat16()
+    pool1, pool2 = pool.clone(), pool.clone()
+    o1, r1 = py.recurrent_forward(d["q"], d["k"], d["v"], pool1, None, None, inference_mode=1, is_qk_norm=True, gating=gating,
+                                  state_indices=idx)
+    o2, r2 = ext.recurrent_forward(d["q"], d["k"], d["v"], pool2, None, None, inference_mode=1, is_qk_norm=True, gating=gating,
+                                   state_indices=idx)
+    assert r1.data_ptr() == pool1.data_ptr() and r2.data_ptr() == pool2.data_ptr()
+    keep = [i for i in range(5) if i != 2]
+    assert torch.equal(o1[keep], o2[keep]) and torch.equal(pool1, pool2)
+    assert torch.equal(pool2[[1, 2, 4, 7]], pool[[1, 2, 4, 7]]) and not torch.equal(pool2[6], pool[6])
+    # in-place state
+    s1, s2 = d["state"].clone(), d["state"].clone()
+    py.recurrent_forward(d["q"], d["k"], d["v"], s1, None, None, inference_mode=1, gating=gating, inplace_state=True)
+    _, r2 = ext.recurrent_forward(d["q"], d["k"], d["v"], s2, None, None, inference_mode=1, gating=gating, inplace_state=True)
+    assert r2.data_ptr() == s2.data_ptr() and torch.equal(s1, s2) and not torch.equal(s2, d["state"])
+    with pytest.raises(RuntimeError):
+        ext.recurrent_forward(d["q"], d["k"], d["v"], d["state"].transpose(-1, -2), None, None, inference_mode=1, gating=gating,
+                              inplace_state=True)
+    # fp32 state stays fp32
+    f1, f2 = d["state"].float(), d["state"].float()
+    o1, r1 = py.recurrent_forward(d["q"], d["k"], d["v"], f1, None, None, inference_mode=1, gating=gating)
+    o2, r2 = ext.recurrent_forward(d["q"], d["k"], d["v"], f2, None, None, inference_mode=1, gating=gating)
+    assert r2.dtype == torch.float32 and torch.equal(o1, o2) and torch.equal(r1, r2)
+    # causal conv1d (+ SiLU) with a carried state, and the gated RMS norm
+    x = torch.randn(2, 100, 256, device="cuda").bfloat16()
+    w = (torch.randn(256, 4, device="cuda") * 0.5).bfloat16()
+    b = torch.randn(256, device="cuda").bfloat16()
+    s0 = torch.randn(2, 3, 256, device="cuda").bfloat16()
+    y1, t1 = py.causal_conv1d(x, w, b, s0, return_final_state=True)
+    y2, t2 = ext.causal_conv1d(x, w, b, s0, return_final_state=True)
+    assert torch.equal(y1, y2) and torch.equal(t1, t2)
+    assert torch.equal(ext.causal_conv1d(x, w, activation=False), py.causal_conv1d(x, w, activation=False))
+    cu = torch.tensor([0, 37, 200], dtype=torch.int32, device="cuda")
+    xp = x.reshape(200, 256)
+    assert torch.equal(ext.causal_conv1d(xp, w, b, cu_seqlens=cu), py.causal_conv1d(xp, w, b, cu_seqlens=cu))
+    z = torch.randn(3, 50, 4, 128, device="cuda").bfloat16()
+    xo = torch.randn(3, 50, 4, 128, device="cuda").bfloat16()
+    g = torch.randn(128, device="cuda").bfloat16()
+    assert torch.equal(ext.gated_rmsnorm(xo, z, g, 1e-5), py.gated_rmsnorm(xo, z, g, 1e-5))
