@@ -23,6 +23,7 @@ The printed JSON line carries:
              one launch per step) and its HBM roofline fraction
   spec_verify   speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, qk-norm, fused gating)
   decode_sharded  a decode batch of B=1024 split by sequence over the N ranks (strong scaling)
+  decode_small_batch  B=8 decode steps issued one by one against the same steps replayed as a CUDA graph
   layer_adjacent  the causal conv1d + SiLU in front of the layer and the gated RMS norm behind it (HBM-bound)
   packed     packed (varlen) prefill of 16 sequences with log-normal lengths, 32768 tokens per GPU
   long_context  the B=2, T=131072 layer with the value heads sharded over the N ranks (strong scaling)
@@ -524,6 +525,35 @@ def main():
     ms_dec, ms_dec_all = timed(step_decode, dsteps)
     del states
 
+    # ---------------- small-batch decode (B=8): the step is bound by launch overhead, so a serving loop captures
+    # it.  16 consecutive in-place steps, issued one by one from Python and replayed as one CUDA graph.
+    gB, gsteps = 8, 16
+    gp = synthetic.decode_inputs(gB, 1, kh, vh, d, seed=150 + rank)
+    gd = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in gp.items()}
+    g_gating = (gd["A_log"], gd["dt_bias"], gd["a"], gd["b"])
+    g_state = gd["state"].clone()
+
+    def steps_small(i=0):
+        for _ in range(gsteps):
+            gdn.recurrent_forward(gd["q"], gd["k"], gd["v"], g_state, None, None, inference_mode=1, is_qk_norm=True,
+                                  gating=g_gating, inplace_state=True)
+    steps_small()
+    ms_small_eager, _ = timed(steps_small, 5, repeats=3)
+    cap = torch.cuda.Stream()
+    cap.wait_stream(torch.cuda.current_stream())
+    small_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(cap):
+        steps_small()
+        with torch.cuda.graph(small_graph, stream=cap):
+            steps_small()
+    torch.cuda.current_stream().wait_stream(cap)
+    small_graph.replay()
+    ms_small_graph, _ = timed(lambda i=0: small_graph.replay(), 5, repeats=3)
+    decode_small = {"config": "B=%d T=1 kh=16 vh=32 d=128, qk-norm, gating inside, state in place; %d steps per measurement" % (gB, gsteps),
+                    "eager_us_per_step": 1e3 * ms_small_eager / gsteps, "cuda_graph_us_per_step": 1e3 * ms_small_graph / gsteps,
+                    "note": "eager: one Python call (ctypes) per step; graph: the same launches replayed"}
+    del small_graph, g_state
+
     # ---------------- speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, one state per sequence out)
     sB, sT = SPEC["B"], SPEC["T"]
     sp = synthetic.decode_inputs(sB, sT, kh, vh, d, seed=300 + rank, spec=True)
@@ -760,6 +790,7 @@ def main():
                                      "qk-norm, fused gating" % (world, nB),
                            "ms_per_step": ms_dsh, "spread": spread(ms_dsh_all),
                            "roofline": hbm_roof(dsh_bytes, ms_dsh, "gdn_recurrent_kernel (rank 0's share)")},
+        "decode_small_batch": decode_small,
         "layer_adjacent": {
             "causal_conv1d_silu": {"config": "B=4 T=4096 channels=8192 (q, k, v projections) width=4, bias, SiLU, per GPU",
                                    "value": world * tokens / (ms_conv * 1e-3), "unit": "tokens/s", "ms_per_step": ms_conv,

@@ -293,3 +293,48 @@ def test_gated_rmsnorm(gdn, shape):
     w = (1 + 0.1 * torch.randn(shape[-1], generator=gen)).bfloat16()
     y = gdn.api.gated_rmsnorm(x.cuda(), z.cuda(), w.cuda(), 1e-6)
     close(y, O.gated_rmsnorm_ref(x, z, w, 1e-6), "y")
+
+
+def test_cuda_graph_replay_of_decode_and_prefill(gdn):
+    """Launch-bound loops are meant to be captured: a decode step (gating inside, state updated in place) and a
+    prefill call are recorded into CUDA graphs after one eager warm-up call each and replayed; the replays must
+    give the bits of the eager calls (nothing is allocated, synchronised or compiled inside the entry points)."""
+    d = dev(synthetic.decode_inputs(8, 1, 2, 4, 128, seed=31))
+    gating = (d["A_log"], d["dt_bias"], d["a"], d["b"])
+    steps = 3
+    qs = [torch.nn.functional.normalize(torch.randn_like(d["q"].float()), dim=-1).bfloat16() for _ in range(steps)]
+    # eager reference: three in-place steps
+    s_eager = d["state"].clone()
+    o_eager = []
+    for q in qs:
+        o, _ = gdn.recurrent_forward(q, d["k"], d["v"], s_eager, None, None, inference_mode=1, is_qk_norm=True,
+                                     gating=gating, inplace_state=True)
+        o_eager.append(o.clone())
+    # captured: static input and state buffers, one graph, replayed per step
+    q_buf, s_graph = qs[0].clone(), d["state"].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up on the capture stream, on a scratch state
+        gdn.recurrent_forward(q_buf, d["k"], d["v"], d["state"].clone(), None, None, inference_mode=1, is_qk_norm=True,
+                              gating=gating, inplace_state=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_buf, _ = gdn.recurrent_forward(q_buf, d["k"], d["v"], s_graph, None, None, inference_mode=1, is_qk_norm=True,
+                                         gating=gating, inplace_state=True)
+    for i, q in enumerate(qs):
+        q_buf.copy_(q)
+        graph.replay()
+        assert torch.equal(o_buf, o_eager[i]), "decode step %d" % i
+    assert torch.equal(s_graph, s_eager)
+    # prefill (two kernels, the second launched with programmatic stream serialization)
+    p = dev(synthetic.prefill_inputs(2, 300, 2, 4, 128, seed=32, mild_gate=True))
+    o_ref, s_ref = gdn.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"])
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        o_g, s_g = gdn.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, p["state"])
+    o_g.zero_()
+    graph2.replay()
+    graph2.replay()
+    assert torch.equal(o_g, o_ref) and torch.equal(s_g, s_ref)
+    check_status(gdn)
