@@ -27,82 +27,129 @@ struct ConvParams {
     long long total_tokens;
 };
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
-
-__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+// Both kernels are bound by instruction issue before they are bound by HBM, so the arithmetic runs on
+// packed pairs of fp32 values (one 64-bit register pair, f32x2 instructions) and SiLU costs one approximate
+// special-function operation per element.
+namespace la {
+using f2 = unsigned long long;
+__device__ __forceinline__ f2 pk(float a, float b) {
+    f2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ void unpk(f2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) {
+    f2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f2 mul2(f2 a, f2 b) {
+    f2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f2 add2(f2 a, f2 b) {
+    f2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// v -> silu(v) = v * sigmoid(v) = v * (0.5 + 0.5 tanh(v / 2)) on a pair: ONE special-function operation per
+// element (the exp + reciprocal form takes two, and the special-function unit, 4 lanes per cycle and scheduler,
+// was the busiest pipe of both kernels).  tanh.approx is good to about 2^-11, well inside bf16.
+__device__ __forceinline__ f2 silu2(f2 v) {
+    float a, b;
+    unpk(mul2(v, pk(0.5f, 0.5f)), a, b);
+    return mul2(v, fma2(pk(tanh_approx(a), tanh_approx(b)), pk(0.5f, 0.5f), pk(0.5f, 0.5f)));
+}
+// eight bf16 values (16 bytes) <-> four packed fp32 pairs
+__device__ __forceinline__ void unpack8(const uint4& u, f2* f) {
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        f[2 * e] = __uint_as_float(w[e] << 16);
-        f[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-    }
+    for (int e = 0; e < 4; ++e) f[e] = pk(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xFFFF0000u));
 }
-__device__ __forceinline__ uint4 pack8(const float* f) {
+__device__ __forceinline__ uint4 pack8(const f2* f) {
     uint32_t w[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+        float a, b;
+        unpk(f[e], a, b);
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
         w[e] = *reinterpret_cast<uint32_t*>(&v);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
+}  // namespace la
 
 // One thread: 8 adjacent channels, kConvTokBlock consecutive tokens; the last width - 1 inputs slide
 // along in registers, so every input is loaded once (plus width - 1 tokens of halo per block).
 // blockIdx.x: channel groups, blockIdx.y: token blocks, blockIdx.z: batch entry (padded mode).
+// Token positions inside the kernel are 32-bit offsets from the block's first token and addresses advance
+// by pointer increments: the kernel is bound by instruction issue, and 64-bit index arithmetic per token was a
+// good part of it.  (Unrolling all 32 tokens, which makes ring slots constants, is slower: 3 k instructions
+// per thread no longer sit in the instruction cache.)
 template <int W>
-__global__ void __launch_bounds__(128) gdn_causal_conv1d_kernel(const ConvParams p) {
+__global__ void __launch_bounds__(128, 5) gdn_causal_conv1d_kernel(const ConvParams p) {
     static_assert(W >= 2 && W <= kConvMaxWidth, "filter widths 2 .. 4");
+    using namespace la;
     const int cg = blockIdx.x * blockDim.x + threadIdx.x;
     if (cg * 8 >= p.channels) return;
     const int c0 = cg * 8;
-    float wt[W][8], bs[8];
+    f2 wt[W][4], bs[4];  // channel pairs
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        bs[e] = p.bias ? __bfloat162float(p.bias[c0 + e]) : 0.f;
+    for (int e = 0; e < 4; ++e) {
+        bs[e] = p.bias ? pk(__bfloat162float(p.bias[c0 + 2 * e]), __bfloat162float(p.bias[c0 + 2 * e + 1])) : pk(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < W; ++i) wt[i][e] = __bfloat162float(p.w[static_cast<long long>(c0 + e) * W + i]);
+        for (int i = 0; i < W; ++i)
+            wt[i][e] = pk(__bfloat162float(p.w[static_cast<long long>(c0 + 2 * e) * W + i]),
+                          __bfloat162float(p.w[static_cast<long long>(c0 + 2 * e + 1) * W + i]));
     }
-    // token range of this thread and the sequence it starts in
-    long long t0, t_end;   // global token positions (packed) or positions inside the batch entry (padded)
+    // the thread's token block [t0, t0 + n_tok) and the sequence it starts in
+    const bool packed = p.cu_seqlens != nullptr;
+    const long long t0 = static_cast<long long>(blockIdx.y) * kConvTokBlock;
+    const long long limit = packed ? p.total_tokens : static_cast<long long>(p.seq_len);
+    if (t0 >= limit) return;
+    const int n_tok = static_cast<int>(min(static_cast<long long>(kConvTokBlock), limit - t0));
     int seq;
-    long long bos, eos;
     const __nv_bfloat16* xb;
     __nv_bfloat16* yb;
-    if (p.cu_seqlens) {
-        t0 = static_cast<long long>(blockIdx.y) * kConvTokBlock;
-        if (t0 >= p.total_tokens) return;
-        t_end = min(t0 + kConvTokBlock, p.total_tokens);
+    constexpr int kFar = 1 << 20;
+    int bos_rel, eos_rel;  // start and end of the current sequence relative to t0 (clipped far away)
+    auto set_sequence = [&](int s_) {
+        seq = s_;
+        const long long b = packed ? p.cu_seqlens[s_] : 0, e = packed ? p.cu_seqlens[s_ + 1] : p.seq_len;
+        bos_rel = static_cast<int>(max(b - t0, static_cast<long long>(-kFar)));
+        eos_rel = static_cast<int>(min(e - t0, static_cast<long long>(kFar)));
+    };
+    if (packed) {
         int lo = 0, hi = p.batch;  // last sequence whose start is <= t0
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (p.cu_seqlens[mid] <= t0) lo = mid; else hi = mid;
         }
-        seq = lo;
-        bos = p.cu_seqlens[seq];
-        eos = p.cu_seqlens[seq + 1];
+        set_sequence(lo);
         xb = p.x;
         yb = p.y;
     } else {
-        seq = blockIdx.z;
-        t0 = static_cast<long long>(blockIdx.y) * kConvTokBlock;
-        if (t0 >= p.seq_len) return;
-        t_end = min(t0 + kConvTokBlock, static_cast<long long>(p.seq_len));
-        bos = 0;
-        eos = p.seq_len;
+        set_sequence(static_cast<int>(blockIdx.z));
         xb = p.x + seq * p.x_sb;
         yb = p.y + seq * p.y_sb;
     }
-    // the input at position t of the current sequence; positions before its start come from the state, or are zero
-    auto load_input = [&](long long t) {
-        if (t >= bos) return *reinterpret_cast<const uint4*>(xb + t * p.x_st + c0);
-        if (p.state_in && bos - t <= W - 1) {
-            const long long row = (W - 1) - (bos - t);  // state row W-2 is the input right before the sequence
+    const __nv_bfloat16* const x0 = xb + t0 * p.x_st + c0;  // this thread's channels of token t0
+    // the input at offset j (from t0) of the current sequence; positions before its start come from the state, or are zero
+    auto load_input = [&](int j) {
+        if (j >= bos_rel) return *reinterpret_cast<const uint4*>(x0 + j * p.x_st);
+        if (p.state_in && bos_rel - j <= W - 1) {
+            const int row = (W - 1) - (bos_rel - j);  // state row W-2 is the input right before the sequence
             return *reinterpret_cast<const uint4*>(p.state_in + (static_cast<long long>(seq) * (W - 1) + row) * p.channels + c0);
         }
         return make_uint4(0u, 0u, 0u, 0u);
     };
-    auto store_state = [&](long long last) {  // the sequence's final width - 1 inputs, `last` = its last token
+    auto store_state = [&](int last) {  // the sequence's final width - 1 inputs, `last` = offset of its last token
         if (!p.state_out) return;
 #pragma unroll
         for (int r = 0; r < W - 1; ++r) {
@@ -114,57 +161,65 @@ __global__ void __launch_bounds__(128) gdn_causal_conv1d_kernel(const ConvParams
     // memory, filled by asynchronous copies issued kConvRing tokens ahead: that many loads per thread are in
     // flight without costing registers (a thread with one load in flight at a time cannot keep HBM busy).
     __shared__ uint4 ring[kConvRing][128];
-    auto request = [&](long long t) {
-        if (t < t_end) {
-            const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(&ring[static_cast<int>(t - t0) % kConvRing][threadIdx.x]));
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(xb + t * p.x_st + c0) : "memory");
-        }
+    const uint32_t ring0 = static_cast<uint32_t>(__cvta_generic_to_shared(&ring[0][threadIdx.x]));
+    constexpr uint32_t kSlotBytes = 128 * sizeof(uint4);
+    const __nv_bfloat16* xreq = x0;  // source of the next request
+    auto request = [&](int j) {      // j: offset of the token
+        if (j < n_tok)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring0 + (j % kConvRing) * kSlotBytes), "l"(xreq) : "memory");
+        xreq += p.x_st;
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per token, empty past the end
     };
 #pragma unroll
-    for (int u = 0; u < kConvRing; ++u) request(t0 + u);
+    for (int u = 0; u < kConvRing; ++u) request(u);
     // The last W inputs are kept unpacked in W register sets used as a ring: step R of every W consecutive
     // tokens finds tap i in set (R + i) % W and puts the new token into set (R + W - 1) % W, so nothing is
     // ever moved or unpacked twice.
-    float win[W][8];
-    auto step = [&](auto rot, long long t) {
-        constexpr int R = decltype(rot)::value;
-        bool refill = t == t0;
-        if (t >= eos) {  // packed mode: the block runs into the next sequence(s); empty ones are skipped
-            do {
-                ++seq;
-                bos = p.cu_seqlens[seq];
-                eos = p.cu_seqlens[seq + 1];
-            } while (t >= eos);
-            refill = true;
-        }
-        if (refill) {
+    f2 win[W][4];
 #pragma unroll
-            for (int i = 0; i < W - 1; ++i) unpack8(load_input(t - (W - 1) + i), win[(R + i) % W]);
+    for (int i = 0; i < W - 1; ++i) unpack8(load_input(i - (W - 1)), win[i]);
+    __nv_bfloat16* yp = yb + t0 * p.y_st + c0;
+    auto step = [&](auto rot, int j) {
+        constexpr int R = decltype(rot)::value;
+        if (j >= eos_rel) {  // packed mode: the block runs into the next sequence(s); empty ones are skipped
+            int s_ = seq;
+            do {
+                ++s_;
+                set_sequence(s_);
+            } while (j >= eos_rel);
+#pragma unroll
+            for (int i = 0; i < W - 1; ++i) unpack8(load_input(j - (W - 1) + i), win[(R + i) % W]);
         }
         asm volatile("cp.async.wait_group %0;" ::"n"(kConvRing - 1) : "memory");  // the oldest request has landed
-        unpack8(ring[static_cast<int>(t - t0) % kConvRing][threadIdx.x], win[(R + W - 1) % W]);
-        request(t + kConvRing);  // (the slot's value is in registers: it may be handed to the next copy)
-        float acc[8];
+        uint4 raw;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "r"(ring0 + (j % kConvRing) * kSlotBytes)
+                     : "memory");
+        unpack8(raw, win[(R + W - 1) % W]);
+        request(j + kConvRing);  // (the slot's value is in registers: it may be handed to the next copy)
+        f2 acc[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = bs[e];
+        for (int e = 0; e < 4; ++e) acc[e] = bs[e];
 #pragma unroll
         for (int i = 0; i < W; ++i) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(wt[i][e], win[(R + i) % W][e], acc[e]);
+            for (int e = 0; e < 4; ++e) acc[e] = fma2(wt[i][e], win[(R + i) % W][e], acc[e]);
         }
         if (p.silu) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = __fdividef(acc[e], 1.f + __expf(-acc[e]));
+            for (int e = 0; e < 4; ++e) acc[e] = silu2(acc[e]);
         }
-        *reinterpret_cast<uint4*>(yb + t * p.y_st + c0) = pack8(acc);
-        if (t == eos - 1) store_state(t);
+        *reinterpret_cast<uint4*>(yp) = pack8(acc);
+        yp += p.y_st;
+        if (j == eos_rel - 1) store_state(j);
     };
-    for (long long t = t0; t < t_end; t += W) {
-        step(std::integral_constant<int, 0>{}, t);
-        if (t + 1 < t_end) step(std::integral_constant<int, 1 % W>{}, t + 1);
-        if (W > 2 && t + 2 < t_end) step(std::integral_constant<int, 2 % W>{}, t + 2);
-        if (W > 3 && t + 3 < t_end) step(std::integral_constant<int, 3 % W>{}, t + 3);
+#pragma unroll 1
+    for (int j = 0; j < n_tok; j += W) {
+        step(std::integral_constant<int, 0>{}, j);
+        if (j + 1 < n_tok && j + 1 < kConvTokBlock) step(std::integral_constant<int, 1 % W>{}, j + 1);
+        if (W > 2 && j + 2 < n_tok && j + 2 < kConvTokBlock) step(std::integral_constant<int, 2 % W>{}, j + 2);
+        if (W > 3 && j + 3 < n_tok && j + 3 < kConvTokBlock) step(std::integral_constant<int, 3 % W>{}, j + 3);
     }
 }
 
@@ -199,13 +254,14 @@ __global__ void __launch_bounds__(256) gdn_gated_rmsnorm_kernel(const NormParams
     const int sub = lane / LPR, l = lane % LPR;
     const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long row0 = warp_id * (kRowsPerWarp * kUnroll) + sub;
-    float xv[kUnroll][kMaxPass][8];
+    using namespace la;
+    f2 xv[kUnroll][kMaxPass][4];
     uint4 zraw[kUnroll][kMaxPass];  // the gate is requested with x, not after the reduction
     float ss[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
         const long long row = row0 + u * kRowsPerWarp;
-        ss[u] = 0.f;
+        f2 sq = pk(0.f, 0.f);
 #pragma unroll
         for (int it = 0; it < kMaxPass; ++it) {
             const int c = (it * LPR + l) * 8;
@@ -213,9 +269,12 @@ __global__ void __launch_bounds__(256) gdn_gated_rmsnorm_kernel(const NormParams
                 unpack8(*reinterpret_cast<const uint4*>(p.x + row * p.x_sr + c), xv[u][it]);
                 zraw[u][it] = *reinterpret_cast<const uint4*>(p.z + row * p.z_sr + c);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) ss[u] = fmaf(xv[u][it][e], xv[u][it][e], ss[u]);
+                for (int e = 0; e < 4; ++e) sq = fma2(xv[u][it][e], xv[u][it][e], sq);
             }
         }
+        float s0, s1;
+        unpk(sq, s0, s1);
+        ss[u] = s0 + s1;
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -230,11 +289,12 @@ __global__ void __launch_bounds__(256) gdn_gated_rmsnorm_kernel(const NormParams
         for (int it = 0; it < kMaxPass; ++it) {
             const int c = (it * LPR + l) * 8;
             if (row < p.rows && c < p.dim) {
-                float zv[8], wv[8], o[8];
+                f2 zv[4], wv[4], o[4];
                 unpack8(zraw[u][it], zv);
                 unpack8(*reinterpret_cast<const uint4*>(p.w + c), wv);
+                const f2 r2 = pk(rstd, rstd);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = xv[u][it][e] * rstd * wv[e] * silu_f(zv[e]);
+                for (int e = 0; e < 4; ++e) o[e] = mul2(mul2(mul2(xv[u][it][e], r2), wv[e]), silu2(zv[e]));
                 *reinterpret_cast<uint4*>(p.y + row * p.y_sr + c) = pack8(o);
             }
         }
