@@ -225,6 +225,9 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
 
     if (warp < 8) {
         // =============================================================== state warps
+        // setmaxnreg moves registers inside the CTA's own pool (threads x the kernel's register count = 512 x 128);
+        // a request the pool cannot serve blocks for ever: 8 state warps at 168, 4 output warps at 88, 4 others at 40.
+        static_assert(32 * (8 * 168 + 4 * 88 + 4 * 40) <= kThreads * 128, "register pool of the CTA");
         reg_inc<168>();
         const int lq = warp & 3, hf = warp >> 2;
         const int row = 32 * lq + lane;
