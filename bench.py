@@ -306,6 +306,22 @@ def run_only(args, gdn, synthetic, dev, peaks):
             run = lambda i: gdn.chunked_forward(f["q"], f["k"], f["v"], f["beta"], f["g"], None, t["state"], m[0], m[1], m[2], nc,
                                                 _workspace=ws)
         work, unit = B * T, "tokens/s"
+    elif args.only == "layer":
+        # the layer-adjacent kernels: conv1d + SiLU over the q/k/v projections, then the gated RMS norm of the output
+        B, T = args.batch or 2, CFG["T"]
+        C_ = (2 * kh + vh) * d
+        gen = torch.Generator(device=dev).manual_seed(11)
+        x = torch.randn(B, T, C_, device=dev, generator=gen).bfloat16()
+        w = (torch.randn(C_, 4, device=dev, generator=gen) * 0.5).bfloat16()
+        bia = torch.randn(C_, device=dev, generator=gen).bfloat16()
+        o = torch.randn(B, T, vh, d, device=dev, generator=gen).bfloat16()
+        z = torch.randn(B, T, vh, d, device=dev, generator=gen).bfloat16()
+        gw = torch.randn(d, device=dev, generator=gen).bfloat16()
+
+        def run(i):
+            gdn.causal_conv1d(x, w, bia)
+            gdn.gated_rmsnorm(o, z, gw)
+        work, unit = B * T, "tokens/s"
     elif args.only == "packed":
         # 16 sequences of log-normal lengths in one packed batch of 32768 tokens
         lens = synthetic.lognormal_lengths(16, 32768, 64, 8192, seed=0)
@@ -346,7 +362,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-long-context", action="store_true", help="skip the B=2 T=131072 head-sharded leg")
     ap.add_argument("--no-packed", action="store_true", help="skip the packed (varlen) prefill leg")
-    ap.add_argument("--only", default=None, choices=["prefill", "decode", "long", "packed"],
+    ap.add_argument("--only", default=None, choices=["prefill", "decode", "long", "packed", "layer"],
                     help="profiling aid: run only this path, resident inputs, reduced JSON line")
     ap.add_argument("--batch", type=int, default=None, help="with --only: override the batch size")
     ap.add_argument("--heads", type=int, default=None, help="with --only long: v-heads of this GPU's share (default 4)")
