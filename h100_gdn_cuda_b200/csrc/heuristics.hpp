@@ -94,8 +94,12 @@ inline SegmentPlan prefill_segments_packed(int num_seqs, int num_v_heads, long l
     double best = 0.8 * static_cast<double>(waves(chains) * (even + kFixed));
     for (int P = 2; P <= 128 && total_chunks / P >= kMinSegment; ++P) {
         const int len = static_cast<int>((total_chunks + P - 1) / P);
-        const long long slots = total_chunks / len + num_seqs;
-        const long long w1 = waves(2 * slots * num_v_heads), w3 = waves(slots * num_v_heads);
+        const long long slots = total_chunks / len + num_seqs;  // launched (and given scratch): the upper bound
+        // CTAs of surplus slots leave at once and free their SM, so the waves are counted for the slots that
+        // hold work when the sequences are about equally long: every sequence end but the last may add one
+        // short segment
+        const long long work = (total_chunks + len - 1) / len + num_seqs - 1;
+        const long long w1 = waves(2 * work * num_v_heads), w3 = waves(work * num_v_heads);
         if (w3 > 1 || w1 > 2) break;
         const double cost = static_cast<double>((w1 + w3) * (len + kFixed));
         if (cost < best) {

@@ -128,7 +128,7 @@ def test_segment_plan_heuristic():
     assert rows[7] == (1, 40)            # too short for 32-chunk segments
     assert rows[8] == (36, 114, 37)      # two long packed sequences of 4 heads: like the padded plan, one CTA wave
     assert rows[8][2] * 4 <= 148
-    assert rows[9][0] == 1               # 32 heads of one sequence: the slack slot would cost a second wave
+    assert rows[9] == (4, 512, 5)        # 32 heads of one sequence: as the padded plan; the slack slot holds no work
     assert rows[10][0] == 1              # the packed benchmark batch (512 chains) is never segmented
     assert rows[11][0] == 1              # more sequences than the lookup scans
     assert rows[12] == (8, 33, 9)        # total // 33 + 2 slots cover any split of 259 chunks over 2 sequences
