@@ -92,6 +92,13 @@ def _shape(batch, seq_len, total_tokens, kh, vh, dk, dv, cu_seqlens=None, chunk_
                       _i32(chunk_indices, "chunk_indices"), _i32(cu_chunks, "cu_chunks"), int(total_chunks))
 
 
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """The prefill kernels read token tensors through TMA: 16-byte aligned base, contiguous head dim, every other
+    stride a multiple of 8 elements.  A view that does not qualify is compacted (a copy), anything else passes."""
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in t.stride()[:-1])
+    return t if ok else t.contiguous()
+
+
 def _pad_last(t: torch.Tensor, to: int) -> torch.Tensor:
     return t if t.shape[-1] == to else torch.nn.functional.pad(t, (0, to - t.shape[-1]))
 
@@ -326,7 +333,7 @@ def chunked_forward(query, key, value, beta, gate, scale: Optional[float] = None
     # goes in as it is (the library's tensor maps supply the zero columns, nothing is copied); any other is
     # zero-padded to 128 here.  129..256: the library runs the token recurrence on 192 or 256 columns instead.
     D = (d if d % 8 == 0 else _PREFILL_D) if d <= _PREFILL_D else _aligned_dim(d)
-    q, k, v = _pad_last(query, D), _pad_last(key, D), _pad_last(value, D)
+    q, k, v = (_tma_ready(_pad_last(t, D)) for t in (query, key, value))
     s_in = _pad_state(initial_state, D)
     if s_in is not None:
         _cuda_bf16(s_in, "initial_state")

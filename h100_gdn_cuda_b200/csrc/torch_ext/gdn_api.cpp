@@ -61,6 +61,13 @@ const int32_t* i32(const std::optional<at::Tensor>& o, const char* name) {
             std::string(name) + " must be a contiguous int32 CUDA tensor");
     return o->data_ptr<int32_t>();
 }
+// The prefill kernels read token tensors through TMA: 16-byte aligned base, contiguous head dim, every other
+// stride a multiple of 8 elements.  A view that does not qualify is compacted (a copy), anything else passes.
+at::Tensor tma_ready(const at::Tensor& t) {
+    bool ok = t.stride(-1) == 1 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0;
+    for (int64_t i = 0; ok && i + 1 < t.dim(); ++i) ok = t.stride(i) % 8 == 0;
+    return ok ? t : t.contiguous();
+}
 at::Tensor pad_last(const at::Tensor& t, int64_t to) {
     return t.size(-1) == to ? t : at::constant_pad_nd(t, {0, to - t.size(-1)}, 0);
 }
@@ -114,7 +121,7 @@ std::pair<at::Tensor, at::Tensor> chunked_forward(at::Tensor& query, at::Tensor&
     // in as it is (the library's tensor maps supply the zero columns), any other is zero-padded to 128 here.
     // 129..256: the library runs the token recurrence on 192 or 256 columns instead
     const int64_t D = d <= kPrefillDim ? (d % 8 == 0 ? d : kPrefillDim) : (d + 63) / 64 * 64;
-    at::Tensor q = pad_last(query, D), k = pad_last(key, D), v = pad_last(value, D);
+    at::Tensor q = tma_ready(pad_last(query, D)), k = tma_ready(pad_last(key, D)), v = tma_ready(pad_last(value, D));
     std::optional<at::Tensor> s_in;
     if (initial_state.has_value()) {
         cuda_bf16(*initial_state, "initial_state");

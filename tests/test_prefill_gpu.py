@@ -221,6 +221,12 @@ def test_chunked_forward_small_head_dims_unpadded(gdn, d, lens, kh, vh):
     o2, s2 = gdn.chunked_forward(wide[..., :d], wide[..., d:2 * d], pd["v"], pd["beta"], pd["g"], None, pd["state"],
                                  pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
     assert torch.equal(o2, o) and torch.equal(s2, s)
+    # a view TMA cannot address (head stride not a multiple of 8 elements) is compacted by the front end, not refused
+    odd = torch.zeros(sum(lens), kh, d + 4, device="cuda", dtype=torch.bfloat16)
+    odd[..., :d] = pd["q"]
+    o3, s3 = gdn.chunked_forward(odd[..., :d], pd["k"], pd["v"], pd["beta"], pd["g"], None, pd["state"],
+                                 pd["cu_seqlens"], pd["chunk_indices"], pd["cu_chunks"], p["total_chunks"])
+    assert torch.equal(o3, o) and torch.equal(s3, s)
 
 
 def test_varlen_equals_padded_per_sequence(gdn):
