@@ -294,10 +294,13 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
             db = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.dt_bias) + head)
                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.dt_bias)[head]);
         }
+        // softplus and sigmoid on the fast exponential, logarithm and reciprocal (a few ulp, far inside what a bf16
+        // beta or an e^gate can show); log(1 + e) switches to e where 1 + e would round to 1
         const float x = gt + db;
-        const float sp = x > 20.f ? x : log1pf(__expf(x));
+        const float e = __expf(x);
+        const float sp = x > 20.f ? x : (x < -15.f ? e : __logf(1.f + e));
         gt = -__expf(al) * sp;
-        bt = 1.f / (1.f + __expf(-bt));
+        bt = __fdividef(1.f, 1.f + __expf(-bt));
     };
 
     // The producer walks (unit, rb) pairs kStages-1 iterations ahead of the consumers.
