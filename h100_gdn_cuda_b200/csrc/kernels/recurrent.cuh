@@ -101,6 +101,24 @@ constexpr int recurrent_smem_bytes() {
     return recurrent_stages<kRing, kF32>() * RecStage<DK, kRing, kF32>::kBytes + 128 + (kRing ? 2 * RecTokSlot<DK>::kBytes : 0);
 }
 
+// Multi-token units of the decode instance (speculative verify, short runs): the per-token inputs that every
+// 32-row tile of a (sequence, v-head) unit needs - the normalised k and q, k.q, beta, the gate and the head's v -
+// are prepared ONCE per unit by the CTA's warps (one token each) and kept here for the unit's tiles; without it every
+// tile, and in it every warp, reloaded and re-normalised every token (a third of the instructions of such a step).
+constexpr int kRecPrepTok = 8;     // units with 2 .. 8 tokens use the buffer, longer ones the per-tile path
+constexpr int kRecPrepRows = 256;  // v rows of a unit that fit (dv <= 256)
+template <int DK, bool kEnable>
+struct RecPrepBuf {
+    float k[kRecPrepTok][DK];
+    float q[kRecPrepTok][DK];
+    float sc[kRecPrepTok][4];  // beta, gate, k.q
+    __nv_bfloat16 v[kRecPrepTok][kRecPrepRows];
+};
+template <int DK>
+struct RecPrepBuf<DK, false> {
+    int unused;
+};
+
 namespace rec {
 using f2 = unsigned long long;  // two packed fp32 values
 __device__ __forceinline__ f2 pk(float lo, float hi) {
@@ -172,6 +190,8 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     // dt_bias staged here once per CTA (heads beyond the table are read from global memory).
     constexpr int kGateTable = 128;
     __shared__ float s_alog[kGateTable], s_dtb[kGateTable];
+    constexpr bool kPrep = !kRing && !kLean;
+    __shared__ __align__(16) RecPrepBuf<DK, kPrep> prep;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -356,6 +376,81 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
         f2 k2[NQ], q2[NQ];
         float kq = 0.f;
 
+        auto prep_kq = [&](const uint2* kw_, const uint2* qw_) {
+                // unpack, optional L2 normalisation, k.q
+#pragma unroll
+                for (int pc = 0; pc < NQ / 2; ++pc) {
+                    k2[2 * pc] = bf2_to_f2(kw_[pc].x);
+                    k2[2 * pc + 1] = bf2_to_f2(kw_[pc].y);
+                    q2[2 * pc] = bf2_to_f2(qw_[pc].x);
+                    q2[2 * pc + 1] = bf2_to_f2(qw_[pc].y);
+                }
+                f2 akk = 0ull, aqq = 0ull, akq = 0ull;
+#pragma unroll
+                for (int c = 0; c < NQ; ++c) {
+                    akk = fma2(k2[c], k2[c], akk);
+                    aqq = fma2(q2[c], q2[c], aqq);
+                    akq = fma2(k2[c], q2[c], akq);
+                }
+                float skk = hsum(akk), sqq = hsum(aqq), skq = hsum(akq);
+#pragma unroll
+                for (int m = 1; m < 16; m <<= 1) {
+                    skk += __shfl_xor_sync(0xffffffffu, skk, m);
+                    sqq += __shfl_xor_sync(0xffffffffu, sqq, m);
+                    skq += __shfl_xor_sync(0xffffffffu, skq, m);
+                }
+                kq = skq;
+                if (p.is_qk_norm) {
+                    const float inv_k = rsqrtf(skk + 1e-6f), inv_q = rsqrtf(sqq + 1e-6f);
+                    const f2 ik2 = pk(inv_k, inv_k), iq2 = pk(inv_q, inv_q);
+#pragma unroll
+                    for (int c = 0; c < NQ; ++c) {
+                        k2[c] = mul2(k2[c], ik2);
+                        q2[c] = mul2(q2[c], iq2);
+                    }
+                    kq = skq * inv_k * inv_q;
+                }
+                        };
+        // ---- multi-token unit: prepare the tokens once for all tiles (see RecPrepBuf)
+        bool use_prep = false;
+        if constexpr (kPrep) {
+            use_prep = T.ntok > 1 && T.ntok <= kRecPrepTok && tpu * kRecTileRows <= kRecPrepRows;
+            if (use_prep) {
+                __syncthreads();  // the previous unit's tiles have read the buffer
+                for (int t = warp; t < T.ntok; t += kRecThreads / 32) {
+                    const long long tok = T.tok0 + t;
+                    const __nv_bfloat16* kp = p.k + T.bidx * p.k_sb + tok * p.k_st + T.khead * p.k_sh;
+                    const __nv_bfloat16* qp = p.q + T.bidx * p.q_sb + tok * p.q_st + T.khead * p.q_sh;
+                    uint2 kk[NQ / 2], qq[NQ / 2];
+#pragma unroll
+                    for (int pc = 0; pc < NQ / 2; ++pc) {
+                        kk[pc] = __ldg(reinterpret_cast<const uint2*>(kp + pc * 64 + l16 * 4));
+                        qq[pc] = __ldg(reinterpret_cast<const uint2*>(qp + pc * 64 + l16 * 4));
+                    }
+                    float bt, gt;
+                    load_scalars(T, t, bt, gt);
+                    if (p.fused_gating) apply_gating(T.head, bt, gt);
+                    prep_kq(kk, qq);
+                    if (half == 0) {
+#pragma unroll
+                        for (int pc = 0; pc < NQ / 2; ++pc) {
+                            float a0, a1, a2, a3;
+                            unpk(k2[2 * pc], a0, a1);
+                            unpk(k2[2 * pc + 1], a2, a3);
+                            *reinterpret_cast<float4*>(&prep.k[t][pc * 64 + l16 * 4]) = make_float4(a0, a1, a2, a3);
+                            unpk(q2[2 * pc], a0, a1);
+                            unpk(q2[2 * pc + 1], a2, a3);
+                            *reinterpret_cast<float4*>(&prep.q[t][pc * 64 + l16 * 4]) = make_float4(a0, a1, a2, a3);
+                        }
+                    }
+                    if (lane == 0) *reinterpret_cast<float4*>(prep.sc[t]) = make_float4(bt, gt, kq, 0.f);
+                    const __nv_bfloat16* vp = p.v + T.bidx * p.v_sb + tok * p.v_st + T.head * p.v_sh + T.rb0 * kRecTileRows;
+                    for (int i = lane; i < tpu * kRecTileRows; i += 32) prep.v[t][i] = vp[i];
+                }
+                __syncthreads();
+            }
+        }
+
         for (int r = 0; r < tpu; ++r, ++it) {
             const int rb = T.rb0 + r;
             const int stage = it % kStages;
@@ -423,41 +518,6 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 load_scalars(T, t, bt, gt);
             };
 
-            auto prep_kq = [&](const uint2* kw_, const uint2* qw_) {
-                    // unpack, optional L2 normalisation, k.q
-#pragma unroll
-                    for (int pc = 0; pc < NQ / 2; ++pc) {
-                        k2[2 * pc] = bf2_to_f2(kw_[pc].x);
-                        k2[2 * pc + 1] = bf2_to_f2(kw_[pc].y);
-                        q2[2 * pc] = bf2_to_f2(qw_[pc].x);
-                        q2[2 * pc + 1] = bf2_to_f2(qw_[pc].y);
-                    }
-                    f2 akk = 0ull, aqq = 0ull, akq = 0ull;
-#pragma unroll
-                    for (int c = 0; c < NQ; ++c) {
-                        akk = fma2(k2[c], k2[c], akk);
-                        aqq = fma2(q2[c], q2[c], aqq);
-                        akq = fma2(k2[c], q2[c], akq);
-                    }
-                    float skk = hsum(akk), sqq = hsum(aqq), skq = hsum(akq);
-#pragma unroll
-                    for (int m = 1; m < 16; m <<= 1) {
-                        skk += __shfl_xor_sync(0xffffffffu, skk, m);
-                        sqq += __shfl_xor_sync(0xffffffffu, sqq, m);
-                        skq += __shfl_xor_sync(0xffffffffu, skq, m);
-                    }
-                    kq = skq;
-                    if (p.is_qk_norm) {
-                        const float inv_k = rsqrtf(skk + 1e-6f), inv_q = rsqrtf(sqq + 1e-6f);
-                        const f2 ik2 = pk(inv_k, inv_k), iq2 = pk(inv_q, inv_q);
-#pragma unroll
-                        for (int c = 0; c < NQ; ++c) {
-                            k2[c] = mul2(k2[c], ik2);
-                            q2[c] = mul2(q2[c], iq2);
-                        }
-                        kq = skq * inv_k * inv_q;
-                    }
-                            };
             auto token_step = [&](int t, const float* vr_, float beta_t, float g_t) {
                 // ---- S.k and S.q for the thread's 4 rows
                 f2 ak[4], aq[4];
@@ -632,6 +692,26 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
                 if (T.ntok == 1) {
                     if (fresh_qk) prep_kq(kw, qw);
                     token_step(0, vr, beta_t, g_t);
+                }
+            } else if (kPrep && use_prep) {
+                if constexpr (kPrep) {
+                    for (int t = 0; t < T.ntok; ++t) {
+#pragma unroll
+                        for (int pc = 0; pc < NQ / 2; ++pc) {
+                            const float4 a = *reinterpret_cast<const float4*>(&prep.k[t][pc * 64 + l16 * 4]);
+                            const float4 b = *reinterpret_cast<const float4*>(&prep.q[t][pc * 64 + l16 * 4]);
+                            k2[2 * pc] = pk(a.x, a.y);
+                            k2[2 * pc + 1] = pk(a.z, a.w);
+                            q2[2 * pc] = pk(b.x, b.y);
+                            q2[2 * pc + 1] = pk(b.z, b.w);
+                        }
+                        const float4 sc = *reinterpret_cast<const float4*>(prep.sc[t]);
+                        kq = sc.z;
+                        float vt[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) vt[j] = __bfloat162float(prep.v[t][r * kRecTileRows + warp * 8 + 2 * j + half]);
+                        token_step(t, vt, sc.x, sc.y);
+                    }
                 }
             } else
             for (int t = 0; t < T.ntok; ++t) {

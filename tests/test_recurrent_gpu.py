@@ -270,3 +270,23 @@ def test_errors_raise(gdn):
         gdn.recurrent_forward(p["q"][:, :, :, ::2], p["k"], p["v"], p["state"], beta, None)
     with pytest.raises(RuntimeError):
         gdn.transpose_to_mn_major(torch.zeros(4, dtype=torch.float32, device="cuda"))
+
+
+def test_many_multi_token_units_per_cta(gdn):
+    """More (sequence, v-head) units than CTAs, with 0 .. 17 tokens each in no particular order: every CTA walks
+    several units, some through the once-per-unit token buffer (2 .. 8 tokens), some through the per-tile path
+    (1, or 9 and more), some empty; q/k norm on, fp32 and bf16 gates."""
+    lens = [(7 * i + 3) % 18 for i in range(220)]
+    p = synthetic.varlen_inputs(lens, 2, 4, 128, seed=77, mild_gate=True, normalize=False)
+    pd = dev(p)
+    for g in (pd["g"], pd["g"].bfloat16()):
+        o, s = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], pd["beta"], g,
+                                     cu_seqlens=pd["cu_seqlens"], is_qk_norm=True)
+        o_ref, s_ref = O.recurrent_ref(p["q"].float(), p["k"].float(), p["v"].float(), p["beta"].float(), g.float().cpu(),
+                                       p["state"].float(), cu_seqlens=p["cu_seqlens"], is_qk_norm=True)
+        close(o, o_ref, "o")
+        close(s, s_ref, "state")
+    # the same launch twice gives the same bits (no stale token buffer between units)
+    o2, s2 = gdn.recurrent_forward(pd["q"], pd["k"], pd["v"], pd["state"], pd["beta"], pd["g"].bfloat16(),
+                                   cu_seqlens=pd["cu_seqlens"], is_qk_norm=True)
+    assert torch.equal(o2, o) and torch.equal(s2, s)
