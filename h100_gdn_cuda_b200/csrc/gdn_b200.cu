@@ -395,9 +395,6 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     p.scale = a->scale;
     p.is_qk_norm = a->is_qk_norm; p.store_step = a->store_step_state;
     p.num_tiles = static_cast<long long>(s.batch) * s.num_v_heads * (s.head_dim_v / kRecTileRows);
-    // more than one token per sequence: tiles become work units of their own (the per-unit sharing
-    // of the q/k normalisation only pays for single-token decode)
-    p.split_tiles = s.cu_seqlens ? (s.total_tokens > s.batch) : (s.seq_len > 1);
     GDN_REQUIRE(p.num_tiles < (1ll << 31), "gdn_recurrent_forward: too many state tiles");
     p.status = d->status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -407,6 +404,15 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     const int force_jit = g_force_jit.load(std::memory_order_relaxed);
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
                                    : (s.seq_len > ring_min);
+    // Work units.  The ring instance (long token runs) makes every 32-row tile a unit of its own.  The decode
+    // instance keeps the tiles of a (sequence, v-head) together, which shares the q/k normalisation and the
+    // prepared tokens among them - unless there are fewer such units than CTA slots: a small decode batch is
+    // bound by latency, and spreading its tiles over four times as many CTAs shortens the step.
+    {
+        const RecurrentConfig cfg = recurrent_config(s.head_dim_k, p.num_tiles, d->sms, ring);
+        const long long units = static_cast<long long>(s.batch) * s.num_v_heads;
+        p.split_tiles = ring ? 1 : (units < static_cast<long long>(d->sms) * cfg.ctas_per_sm);
+    }
     if (force_jit && a->state_dtype != GDN_F32) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
     if (a->state_dtype == GDN_F32) {
         // fp32 states: the two head dims serving configurations use, on the decode and the multi-token instance
