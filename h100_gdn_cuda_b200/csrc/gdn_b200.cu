@@ -404,15 +404,11 @@ int gdn_recurrent_forward(const GdnRecurrentArgs* a, gdn_stream_t stream) {
     const int force_jit = g_force_jit.load(std::memory_order_relaxed);
     const bool ring = s.cu_seqlens ? (s.total_tokens > static_cast<long long>(ring_min) * s.batch)
                                    : (s.seq_len > ring_min);
-    // Work units.  The ring instance (long token runs) makes every 32-row tile a unit of its own.  The decode
+    // Work units: the ring instance (long token runs) makes every 32-row tile a unit of its own; the decode
     // instance keeps the tiles of a (sequence, v-head) together, which shares the q/k normalisation and the
-    // prepared tokens among them - unless there are fewer such units than CTA slots: a small decode batch is
-    // bound by latency, and spreading its tiles over four times as many CTAs shortens the step.
-    {
-        const RecurrentConfig cfg = recurrent_config(s.head_dim_k, p.num_tiles, d->sms, ring);
-        const long long units = static_cast<long long>(s.batch) * s.num_v_heads;
-        p.split_tiles = ring ? 1 : (units < static_cast<long long>(d->sms) * cfg.ctas_per_sm);
-    }
+    // prepared tokens among them.  (Splitting the tiles of small decode batches over more CTAs as well was
+    // tried: 3 % at B = 8, and the run-time unit decode it needs cost the large batches 2 %.)
+    p.split_tiles = ring ? 1 : 0;
     if (force_jit && a->state_dtype != GDN_F32) return launch_recurrent_jit(p, s.head_dim_k, d->sms, st, ring);
     if (a->state_dtype == GDN_F32) {
         // fp32 states: the two head dims serving configurations use, on the decode and the multi-token instance

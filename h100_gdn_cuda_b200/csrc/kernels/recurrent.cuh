@@ -57,8 +57,7 @@ struct RecurrentParams {
     int fused_gating, gating_param_f32;
     const void* A_log;
     const void* dt_bias;
-    int split_tiles;  // 1: every 32-row tile is a work unit (multi-token runs of the ring instance; decode batches too small to
-                      // give every CTA a unit); 0: a unit = all tiles of a (sequence, v-head)
+    int split_tiles;  // 1: every 32-row tile is a work unit (multi-token runs of the ring instance); 0: a unit = all tiles of a (sequence, v-head)
     long long num_tiles;
     int* status;
 };
@@ -201,7 +200,7 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     const bool has_in = kLean || p.state_in != nullptr;
     const bool store_step = !kLean && p.store_step != 0;
     const int rep = p.vh / p.kh;
-    const int tpu = p.split_tiles ? 1 : rblocks;  // tiles per work unit
+    const int tpu = (kRing && p.split_tiles) ? 1 : rblocks;  // tiles per work unit
     const int upg = rblocks / tpu;                // work units per (sequence, v-head)
     const int num_units = static_cast<int>(p.num_tiles / tpu);
     const int stride = static_cast<int>(gridDim.x);
