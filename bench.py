@@ -555,6 +555,19 @@ def main():
                                   gating=g_gating, inplace_state=True)
     steps_small()
     ms_small_eager, _ = timed(steps_small, 5, repeats=3)
+    ms_small_ext = None
+    try:  # the same steps through the pybind front end (built in-tree; optional)
+        from h100_gdn_cuda_b200 import gdn_cuda as gdn_ext
+        gdn_ext.init(os.path.dirname(os.path.abspath(__file__)), os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+
+        def steps_small_ext(i=0):
+            for _ in range(gsteps):
+                gdn_ext.recurrent_forward(gd["q"], gd["k"], gd["v"], g_state, None, None, inference_mode=1, is_qk_norm=True,
+                                          gating=g_gating, inplace_state=True)
+        steps_small_ext()
+        ms_small_ext, _ = timed(steps_small_ext, 5, repeats=3)
+    except ImportError:
+        pass
     cap = torch.cuda.Stream()
     cap.wait_stream(torch.cuda.current_stream())
     small_graph = torch.cuda.CUDAGraph()
@@ -566,8 +579,10 @@ def main():
     small_graph.replay()
     ms_small_graph, _ = timed(lambda i=0: small_graph.replay(), 5, repeats=3)
     decode_small = {"config": "B=%d T=1 kh=16 vh=32 d=128, qk-norm, gating inside, state in place; %d steps per measurement" % (gB, gsteps),
-                    "eager_us_per_step": 1e3 * ms_small_eager / gsteps, "cuda_graph_us_per_step": 1e3 * ms_small_graph / gsteps,
-                    "note": "eager: one Python call (ctypes) per step; graph: the same launches replayed"}
+                    "eager_us_per_step": 1e3 * ms_small_eager / gsteps,
+                    "eager_pybind_us_per_step": None if ms_small_ext is None else 1e3 * ms_small_ext / gsteps,
+                    "cuda_graph_us_per_step": 1e3 * ms_small_graph / gsteps,
+                    "note": "eager: one Python call per step through the ctypes / the pybind front end; graph: the same launches replayed"}
     del small_graph, g_state
 
     # ---------------- speculative verify (B=64, T=4, accepted-token caps ~ U{1..4}, one state per sequence out)
