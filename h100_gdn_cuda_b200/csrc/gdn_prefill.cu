@@ -147,14 +147,25 @@ int launch_zp(const GdnShape& s, const GdnTokenTensor& q, const GdnTokenTensor& 
     p.status = d->status;
     constexpr int smem = ZPSmem::kBytes;
     const int grid = zp_grid(static_cast<long long>(nc) * s.num_k_heads, d->sms);
+    // launched as a programmatic dependent of the preceding work in the stream (the kernel waits before its
+    // first global read): its launch and set-up overlap that work's tail
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(zp::kThreads);
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (norms) {
         if (int rc = set_smem(gdn_zp_kernel<true>, smem)) return rc;
-        gdn_zp_kernel<true><<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
+        GDN_CUDA(cudaLaunchKernelEx(&cfg, gdn_zp_kernel<true>, tmK, tmQ, p));
     } else {
         if (int rc = set_smem(gdn_zp_kernel<false>, smem)) return rc;
-        gdn_zp_kernel<false><<<grid, zp::kThreads, smem, st>>>(tmK, tmQ, p);
+        GDN_CUDA(cudaLaunchKernelEx(&cfg, gdn_zp_kernel<false>, tmK, tmQ, p));
     }
-    GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
 

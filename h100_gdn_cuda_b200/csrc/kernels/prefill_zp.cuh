@@ -127,6 +127,9 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     // never beside a CTA of this kernel) and do its set-up there; it reads this kernel's results only
     // after its own grid_dep_wait.
     if (tid == 0) grid_dep_launch();
+    // This kernel itself is launched as a programmatic dependent of whatever precedes it in the stream: it is
+    // placed and set up while that work drains and waits here, before its first read of global memory.
+    grid_dep_wait();
 
     const int rep = p.vh / p.kh;               // v-heads per k-head
     const int rounds = (rep + 1) >> 1;         // head pairs per unit
