@@ -87,8 +87,17 @@ static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st
     }
     const int per_sm = recurrent_ctas_per_sm<DK, kRing, kF32>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
-    gdn_recurrent_kernel<DK, kRing, kLean, kF32><<<static_cast<unsigned>(grid), kRecThreads, smem, st>>>(p);
-    GDN_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kRecThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];  // programmatic dependent of the preceding work: see the wait at the kernel's top
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GDN_CUDA(cudaLaunchKernelEx(&cfg, gdn_recurrent_kernel<DK, kRing, kLean, kF32>, p));
     return GDN_OK;
 }
 

@@ -205,6 +205,9 @@ __device__ __forceinline__ void gdn_recurrent_body(const RecurrentParams& p) {
     const int num_units = static_cast<int>(p.num_tiles / tpu);
     const int stride = static_cast<int>(gridDim.x);
 
+    // The kernel is launched as a programmatic dependent of the preceding work in the stream: its CTAs are placed
+    // while that work drains and wait here, before the first access to global memory (a no-op for an ordinary launch).
+    grid_dep_wait();
     if (p.fused_gating) {
         for (int h = threadIdx.x; h < min(p.vh, kGateTable); h += blockDim.x) {
             s_alog[h] = p.gating_param_f32 ? __ldg(reinterpret_cast<const float*>(p.A_log) + h)
