@@ -123,13 +123,15 @@ __global__ void __launch_bounds__(zp::kThreads, 2) gdn_zp_kernel(const __grid_co
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    // This kernel is launched as a programmatic dependent of whatever precedes it in the stream: it is placed
+    // and set up while that work drains and waits here, before its first read of global memory.
+    grid_dep_wait();
     // The state kernel that follows may be placed on SMs as this grid drains (it takes a whole SM, so
     // never beside a CTA of this kernel) and do its set-up there; it reads this kernel's results only
-    // after its own grid_dep_wait.
+    // after its own grid_dep_wait.  The release comes AFTER the wait above: the state kernel loads its initial
+    // state (which the work before this kernel may have produced: a state handed over from the previous call)
+    // without waiting, so it must not be able to start before that work has completed.
     if (tid == 0) grid_dep_launch();
-    // This kernel itself is launched as a programmatic dependent of whatever precedes it in the stream: it is
-    // placed and set up while that work drains and waits here, before its first read of global memory.
-    grid_dep_wait();
 
     const int rep = p.vh / p.kh;               // v-heads per k-head
     const int rounds = (rep + 1) >> 1;         // head pairs per unit

@@ -386,3 +386,35 @@ def test_compute_o_stage(gdn, varlen):
     o_rec, s_rec = O.recurrent_ref(*f32(p, "q", "k", "v", "beta"), p["g"], p["state"].float(), cu_seqlens=cu)
     close(o2, o_rec, "O (three stages)")
     close(final, s_rec, "final state (three stages)")
+
+
+def test_back_to_back_calls_hand_the_state_over(gdn):
+    """The kernels are launched as programmatic dependents of the work before them (they are placed and set up while it
+    drains).  A state produced by one call and consumed by the next, with nothing in between, must still be the
+    finished state: chains of prefill and decode calls issued without any synchronisation give the bits of the same
+    chains run with a device synchronisation after every call.  Small problems, so that a following kernel could start
+    while most of the GPU is still free."""
+    for (B, T, kh, vh) in ((1, 130, 2, 4), (2, 64, 1, 2), (1, 700, 2, 4)):
+        p = dev(synthetic.prefill_inputs(B, T, kh, vh, 128, seed=T, mild_gate=True))
+        dq, dk, dv = (p[n][:, :1].contiguous() for n in ("q", "k", "v"))
+        db, dg = p["beta"][:, :1].contiguous(), p["g"][:, :1].contiguous()
+
+        def chain(sync):
+            s = p["state"]
+            outs = []
+            for it in range(12):
+                o, s = gdn.chunked_forward(p["q"], p["k"], p["v"], p["beta"], p["g"], None, s)
+                if sync:
+                    torch.cuda.synchronize()
+                o2, s = gdn.recurrent_forward(dq, dk, dv, s, db, dg)
+                if sync:
+                    torch.cuda.synchronize()
+                outs.append((o[:, -1].clone(), o2.clone()))
+            torch.cuda.synchronize()
+            return s, outs
+        s_sync, outs_sync = chain(True)
+        for _ in range(3):
+            s_async, outs_async = chain(False)
+            assert torch.equal(s_async, s_sync)
+            assert all(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) for a, b in zip(outs_async, outs_sync))
+    check_status(gdn)
