@@ -75,6 +75,23 @@ __global__ void gdn_selftest_wait_kernel(long long limit_cycles, int* status) {
 }
 
 // ------------------------------------------------------------------ recurrent
+// Launch with programmatic stream serialization: the kernel's CTAs may be placed while the preceding work in the
+// stream drains; every kernel launched this way waits (griddepcontrol.wait) before its first global access.
+template <typename P>
+static cudaError_t launch_dependent(void (*kernel)(P), dim3 grid, int threads, size_t smem, cudaStream_t st, const P& params) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 template <int DK, bool kRing, bool kLean = false, bool kF32 = false>
 static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st) {
     constexpr int smem = recurrent_smem_bytes<DK, kRing, kF32>();
@@ -87,17 +104,7 @@ static int launch_recurrent_t(const RecurrentParams& p, int sms, cudaStream_t st
     }
     const int per_sm = recurrent_ctas_per_sm<DK, kRing, kF32>();
     const long long grid = std::min<long long>(p.num_tiles, static_cast<long long>(sms) * per_sm);
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(kRecThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];  // programmatic dependent of the preceding work: see the wait at the kernel's top
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    GDN_CUDA(cudaLaunchKernelEx(&cfg, gdn_recurrent_kernel<DK, kRing, kLean, kF32>, p));
+    GDN_CUDA(launch_dependent(gdn_recurrent_kernel<DK, kRing, kLean, kF32>, dim3(static_cast<unsigned>(grid)), kRecThreads, smem, st, p));
     return GDN_OK;
 }
 
@@ -301,11 +308,10 @@ int gdn_causal_conv1d(const GdnConvArgs* a, gdn_stream_t stream) {
     if (tblocks > 0) {
         dim3 grid(static_cast<unsigned>((a->channels / 8 + 127) / 128), static_cast<unsigned>(tblocks), packed ? 1u : static_cast<unsigned>(a->batch));
         switch (a->width) {
-            case 2: gdn_causal_conv1d_kernel<2><<<grid, 128, 0, st>>>(p); break;
-            case 3: gdn_causal_conv1d_kernel<3><<<grid, 128, 0, st>>>(p); break;
-            default: gdn_causal_conv1d_kernel<4><<<grid, 128, 0, st>>>(p); break;
+            case 2: GDN_CUDA(launch_dependent(gdn_causal_conv1d_kernel<2>, grid, 128, 0, st, p)); break;
+            case 3: GDN_CUDA(launch_dependent(gdn_causal_conv1d_kernel<3>, grid, 128, 0, st, p)); break;
+            default: GDN_CUDA(launch_dependent(gdn_causal_conv1d_kernel<4>, grid, 128, 0, st, p)); break;
         }
-        GDN_CUDA(cudaGetLastError());
     }
     if (packed && p.state_out && p.state_in && p.state_out != p.state_in) {
         gdn_conv_state_passthrough_kernel<<<a->batch, 128, 0, st>>>(p);
@@ -334,12 +340,11 @@ int gdn_gated_rmsnorm(const void* x, const void* z, void* y, const void* weight,
     GDN_REQUIRE(blocks < (1ll << 31), "gdn_gated_rmsnorm: too many rows");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (lpr) {
-        case 4: gdn_gated_rmsnorm_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
-        case 8: gdn_gated_rmsnorm_kernel<8><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
-        case 16: gdn_gated_rmsnorm_kernel<16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
-        default: gdn_gated_rmsnorm_kernel<32><<<static_cast<unsigned>(blocks), 256, 0, st>>>(p); break;
+        case 4: GDN_CUDA(launch_dependent(gdn_gated_rmsnorm_kernel<4>, dim3(static_cast<unsigned>(blocks)), 256, 0, st, p)); break;
+        case 8: GDN_CUDA(launch_dependent(gdn_gated_rmsnorm_kernel<8>, dim3(static_cast<unsigned>(blocks)), 256, 0, st, p)); break;
+        case 16: GDN_CUDA(launch_dependent(gdn_gated_rmsnorm_kernel<16>, dim3(static_cast<unsigned>(blocks)), 256, 0, st, p)); break;
+        default: GDN_CUDA(launch_dependent(gdn_gated_rmsnorm_kernel<32>, dim3(static_cast<unsigned>(blocks)), 256, 0, st, p)); break;
     }
-    GDN_CUDA(cudaGetLastError());
     return GDN_OK;
 }
 

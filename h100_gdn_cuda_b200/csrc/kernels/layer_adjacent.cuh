@@ -31,6 +31,9 @@ struct ConvParams {
 // packed pairs of fp32 values (one 64-bit register pair, f32x2 instructions) and SiLU costs one approximate
 // special-function operation per element.
 namespace la {
+// Both kernels are launched as programmatic dependents of the preceding work in the stream and wait here before
+// their first access to global memory (a no-op for an ordinary launch).
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 using f2 = unsigned long long;
 __device__ __forceinline__ f2 pk(float a, float b) {
     f2 d;
@@ -96,6 +99,7 @@ template <int W>
 __global__ void __launch_bounds__(128, 5) gdn_causal_conv1d_kernel(const ConvParams p) {
     static_assert(W >= 2 && W <= kConvMaxWidth, "filter widths 2 .. 4");
     using namespace la;
+    grid_dep_wait();
     const int cg = blockIdx.x * blockDim.x + threadIdx.x;
     if (cg * 8 >= p.channels) return;
     const int c0 = cg * 8;
@@ -255,6 +259,7 @@ __global__ void __launch_bounds__(256) gdn_gated_rmsnorm_kernel(const NormParams
     const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long row0 = warp_id * (kRowsPerWarp * kUnroll) + sub;
     using namespace la;
+    grid_dep_wait();
     f2 xv[kUnroll][kMaxPass][4];
     uint4 zraw[kUnroll][kMaxPass];  // the gate is requested with x, not after the reduction
     float ss[kUnroll];
