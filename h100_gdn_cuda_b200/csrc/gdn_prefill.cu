@@ -482,11 +482,22 @@ int gdn_chunked_forward(const GdnChunkedArgs* a, gdn_stream_t stream) {
             cp.map = p.map;
             cp.seg_chunks = plan.seg_chunks;
             cp.status = d->status;
-            gdn_seg_combine_kernel<<<dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R), 128, SegCombineSmem::kBytes, st>>>(cp);
-            GDN_CUDA(cudaGetLastError());
+            {
+                // a programmatic dependent of the composite-transition launch (it waits before its first global access)
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3(static_cast<unsigned>(chains), kD / SegCombineSmem::R);
+                cfg.blockDim = dim3(128);
+                cfg.dynamicSmemBytes = SegCombineSmem::kBytes;
+                cfg.stream = st;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                GDN_CUDA(cudaLaunchKernelEx(&cfg, gdn_seg_combine_kernel, cp));
+            }
             p.mode = 2;
-            gdn_fused_seq_kernel<<<dim3(plan.slots, s.num_v_heads), fused::kThreads, smem, st>>>(tmQ, tmK, tmV, tmO, p);
-            GDN_CUDA(cudaGetLastError());
+            GDN_CUDA(launch_fused_after_zp(dim3(plan.slots, s.num_v_heads), smem, st, tmQ, tmK, tmV, tmO, p));
         }
     }
     if (ev) GDN_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev[2]), st));

@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(fused::kThreads, 1)
             uoff8[k] = static_cast<uint32_t>((row >> 6) * 8192 + ((((row & 63) >> 3) ^ k) << 4) + (row & 7) * 2);
         float S[64];
         if (p.mode == 2) {
+            grid_dep_wait();  // the start states come from the kernel launched just before this one
             const float4* src = reinterpret_cast<const float4*>(p.seg_start + seg_idx * (D * D) +
                                                                 static_cast<long long>(row) * D + 64 * hf);
 #pragma unroll

@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(128) gdn_seg_combine_kernel(const SegCombinePa
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     int* abort_flag = reinterpret_cast<int*>(bar + 2);
 
+    ptx::grid_dep_wait();  // launched as a programmatic dependent of the composite-transition launch
     const long long chain = blockIdx.x;
     const int r0 = blockIdx.y * R, col = threadIdx.x;
     const int seq = static_cast<int>(chain / p.vh), head = static_cast<int>(chain % p.vh);
